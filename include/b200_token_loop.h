@@ -1,0 +1,214 @@
+/*
+ * b200_token_loop.h — C ABI of the B200 (sm_100a) per-step token loop.
+ *
+ * This library replaces the device side of sglang.cpp's per-step forward pass
+ * (Engine::forward_batch, src/engine/engine.cc:495-544 of the reference) with
+ * hand-written sm_100a kernels.  Every entry point takes plain device pointers,
+ * sizes, strides (in elements) and a CUDA stream; none allocates or touches
+ * LibTorch types.  Each declaration cites the reference interface it stands in
+ * for, by the file's path inside the reference project.
+ *
+ * Conventions
+ *   - All entry points return B200_OK (0) or a B200_ERR_* code;
+ *     b200_last_error() gives the text for the calling thread.
+ *   - bf16 tensors are raw uint16 storage ("bf16*" below means const void* /
+ *     void* pointing at __nv_bfloat16 data).  Index tensors are int32.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *     stream.  Calls are asynchronous unless stated otherwise.
+ *   - Nothing here synchronises the device unless stated otherwise.
+ */
+#ifndef B200_TOKEN_LOOP_H_
+#define B200_TOKEN_LOOP_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+typedef void* b200_stream_t;
+
+enum {
+    B200_OK = 0,
+    B200_ERR_INVALID_ARGUMENT = 1, /* the reference would TORCH_CHECK-fail here */
+    B200_ERR_CUDA = 2,             /* a CUDA runtime / driver call failed */
+    B200_ERR_TIMEOUT = 3,          /* a bounded in-kernel wait ran out */
+    B200_ERR_UNSUPPORTED = 4,      /* shape / dtype outside what the kernels cover */
+    B200_ERR_STATE = 5             /* object used in the wrong state */
+};
+
+/* ---- library ------------------------------------------------------------- */
+
+/* Text of the last error returned to the calling thread ("" if none). */
+B200_API const char* b200_last_error(void);
+
+/* ABI version of this header (bumped on incompatible change). */
+B200_API int b200_abi_version(void);
+
+/* Reads (synchronously) and clears the device status words that kernels with
+ * bounded waits or index checks write: out[0] = wait site that timed out (0 =
+ * none), out[1] = offending index + 1 (0 = none).  Synchronises `stream`. */
+B200_API int b200_read_device_status(int32_t out[2], b200_stream_t stream);
+
+/* ---- normalisation (include/sglang/layers/normalization.h:6-22) ---------- */
+
+/* RMSNorm::forward / forward_inplace (src/layers/normalization.cu:236-269):
+ * out[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * weight, fp32 math, bf16
+ * storage.  out may alias x.  x, out: [rows, hidden] contiguous. */
+B200_API int b200_rmsnorm(void* out, const void* x, const void* weight, int rows, int hidden,
+                          float eps, b200_stream_t stream);
+
+/* RMSNorm::fused_add_forward_inplace (src/layers/normalization.cu:386-416):
+ * residual <- x + residual (fp32 add, stored bf16); x <- rmsnorm(fp32 sum) * weight. */
+B200_API int b200_fused_add_rmsnorm(void* x, void* residual, const void* weight, int rows,
+                                    int hidden, float eps, b200_stream_t stream);
+
+/* fused_qk_rmsnorm_inplace_3d_strided and RMSNorm::forward_inplace_3d_strided
+ * (src/layers/normalization.cu:271-384): per-(token, head) RMSNorm over head_dim,
+ * in place, on strided views q [tokens, q_heads, head_dim] and k [tokens,
+ * k_heads, head_dim].  Either of q / k may be NULL (with 0 heads) for the
+ * single-tensor form.  Strides are in elements. */
+B200_API int b200_qk_rmsnorm_strided(void* q, void* k, const void* q_weight, const void* k_weight,
+                                     int tokens, int q_heads, int k_heads, int head_dim,
+                                     int64_t q_stride_token, int64_t q_stride_head,
+                                     int64_t k_stride_token, int64_t k_stride_head, float eps,
+                                     b200_stream_t stream);
+
+/* ---- rotary embedding (include/sglang/layers/rotary_embedding.h:11-22) ---- */
+
+/* RotaryEmbedding::forward_inplace (src/layers/rotary_embedding.cu:96-190):
+ * NeoX (rotate-half) RoPE applied in place to q [tokens, q_heads, head_dim] and
+ * k [tokens, k_heads, head_dim] from fp32 tables cos/sin [max_pos, rotary_dim/2]
+ * and int32 positions [tokens].  fp32 math, bf16 storage. */
+B200_API int b200_rope_neox_inplace(void* q, void* k, const float* cos_table,
+                                    const float* sin_table, const int32_t* positions, int tokens,
+                                    int q_heads, int k_heads, int head_dim, int rotary_dim,
+                                    int max_pos, int64_t q_stride_token, int64_t q_stride_head,
+                                    int64_t k_stride_token, int64_t k_stride_head,
+                                    b200_stream_t stream);
+
+/* ---- KV pool (include/sglang/kvcache/base.h:78-90) ------------------------ */
+
+/* MHAKVCache::store_kv (src/kvcache/mha_kvcache.cu:12-41,113-155):
+ * k_cache[out_loc[t], :, :] = k[t, :, :] and the same for v.  k_cache / v_cache:
+ * one layer's [slots, kv_heads, head_dim] contiguous; k / v: strided rows of
+ * kv_heads*head_dim elements. */
+B200_API int b200_store_kv(void* k_cache, void* v_cache, const void* k, const void* v,
+                           const int32_t* out_loc, int tokens, int kv_heads, int head_dim,
+                           int64_t k_stride_token, int64_t v_stride_token, int64_t num_slots,
+                           b200_stream_t stream);
+
+/* The three steps AttentionLayer::forward runs before attention
+ * (src/layers/attention_layer.cc:17-47), as one pass over the packed qkv rows
+ * [tokens, (q_heads + 2*kv_heads)*head_dim]: optional per-head QK RMSNorm
+ * (q_weight/k_weight NULL = none), NeoX RoPE, then the KV-pool store of the
+ * rotated k and of v at out_loc.  q is rewritten in place; with
+ * write_k_back != 0 the k rows are too (as the reference leaves them).
+ * Rounding points match the unfused sequence (bf16 after the norm, bf16 after
+ * the rotation). */
+B200_API int b200_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weight,
+                                    const float* cos_table, const float* sin_table,
+                                    const int32_t* positions, const int32_t* out_loc,
+                                    void* k_cache, void* v_cache, int tokens, int q_heads,
+                                    int kv_heads, int head_dim, int max_pos, int64_t num_slots,
+                                    float eps, int write_k_back, b200_stream_t stream);
+
+/* ---- activation (include/sglang/layers/activation.h:8-11) ----------------- */
+
+/* silu_and_mul / gelu_and_mul (src/layers/activation.cu:15-75):
+ * out[t, j] = act(in[t, j]) * in[t, d + j]; in [tokens, 2*d], out [tokens, d]. */
+B200_API int b200_silu_and_mul(void* out, const void* in, int tokens, int d, b200_stream_t stream);
+B200_API int b200_gelu_and_mul(void* out, const void* in, int tokens, int d, b200_stream_t stream);
+
+/* ---- embedding and index tables ------------------------------------------- */
+
+/* torch::nn::Embedding as used by the models (src/models/qwen3.cc:38-43,56):
+ * out[t, :] = table[ids[t], :].  ids int32; an id outside [0, vocab) writes a
+ * zero row and records the index in the device status word. */
+B200_API int b200_embedding(void* out, const void* table, const int32_t* ids, int tokens,
+                            int hidden, int vocab, b200_stream_t stream);
+
+/* gather_int32_2d (src/kernels/token_pool.cu:31-49,93-133):
+ * out[i] = table[req[i], pos[i]], 0 when either index is out of range. */
+B200_API int b200_gather_int32_2d(int32_t* out, const int32_t* table, int64_t rows, int64_t stride,
+                                  int64_t cols, const int32_t* req_indices,
+                                  const int32_t* positions, int64_t count, b200_stream_t stream);
+
+/* write_token_pool (src/kernels/token_pool.cu:10-29,53-91):
+ * table[req[i], pos[i]] = tokens[i], skipped when either index is out of range. */
+B200_API int b200_write_token_pool(int32_t* table, int64_t rows, int64_t stride, int64_t cols,
+                                   const int32_t* req_indices, const int32_t* positions,
+                                   const int32_t* tokens, int64_t count, b200_stream_t stream);
+
+/* ---- linear (include/sglang/layers/linear.h:7-73) -------------------------- */
+
+enum {
+    B200_EPILOGUE_NONE = 0,
+    /* y[m, j] = silu(bf16(acc[m, j])) * bf16(acc[m, N/2 + j]), j < N/2: the
+     * gate_up projection followed by silu_and_mul (src/models/utils.cc:41-57). */
+    B200_EPILOGUE_SWIGLU = 1,
+    B200_EPILOGUE_GEGLU = 2
+};
+
+/* LinearBase::forward (src/layers/linear.cc:24-26): y = x W^T (+ bias), bf16 in,
+ * fp32 accumulate on the tcgen05 tensor cores, bf16 out.  x [M, K] with row
+ * stride ldx, w [N, K] contiguous, y [M, N_out] contiguous where N_out = N (or
+ * N/2 with a gated epilogue).  K must be a multiple of 64, N of 16. */
+B200_API int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, int N,
+                         int K, int64_t ldx, int epilogue, b200_stream_t stream);
+
+/* ---- attention (include/sglang/attention/backend.h:24-41) ------------------ */
+
+/* Bytes of scratch b200_attention_decode needs for up to max_batch requests
+ * with q_heads / kv_heads local heads. */
+B200_API int64_t b200_attention_decode_workspace_bytes(int max_batch, int q_heads, int kv_heads,
+                                                       int head_dim);
+
+/* FlashInferBackend::forward for a decode batch
+ * (src/attention/flashinfer_backend.cu:553-595): out[b, h, :] = softmax(q[b, h]
+ * . K_b^T / sqrt(d)) V_b over the seq_lens[b] keys whose KV-pool slots are
+ * page_table[table_idx[b], 0 .. seq_lens[b]).  page_table holds one slot per
+ * token position; page_size states that positions [j*page_size, (j+1)*page_size)
+ * of a row are consecutive slots starting at a multiple of page_size (1 = no
+ * such guarantee, as the reference Engine runs).  q [batch, q_heads, head_dim]
+ * with strides; out [batch, q_heads*head_dim] contiguous.  k_cache / v_cache:
+ * one layer's [num_slots, kv_heads, head_dim].  workspace: zero-initialised
+ * once by the caller, then owned by the calls (they leave it zeroed where it
+ * must be).  Split-KV is decided on the device; no host plan. */
+B200_API int b200_attention_decode(void* out, const void* q, int64_t q_stride_token,
+                                   int64_t q_stride_head, const void* k_cache, const void* v_cache,
+                                   int64_t num_slots, const int32_t* page_table,
+                                   int64_t page_table_stride, const int32_t* table_idx,
+                                   const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
+                                   int head_dim, int page_size, float sm_scale, void* workspace,
+                                   int64_t workspace_bytes, b200_stream_t stream);
+
+/* FlashInferBackend::forward for a prefill (extend) batch
+ * (src/attention/flashinfer_backend.cu:596-678): causal attention of ragged
+ * query rows against paged keys.  Request b owns query rows
+ * [qo_indptr[b], qo_indptr[b+1]), which are the LAST extend positions of its
+ * seq_lens[b] keys (the first seq_lens[b] - extend_len are the cached prefix).
+ * max_extend_len bounds the longest request's extend length (grid sizing). */
+B200_API int b200_attention_prefill(void* out, const void* q, int64_t q_stride_token,
+                                    int64_t q_stride_head, const void* k_cache,
+                                    const void* v_cache, int64_t num_slots,
+                                    const int32_t* page_table, int64_t page_table_stride,
+                                    const int32_t* table_idx, const int32_t* seq_lens,
+                                    const int32_t* qo_indptr, int batch, int max_extend_len,
+                                    int q_heads, int kv_heads, int head_dim, int page_size,
+                                    float sm_scale, b200_stream_t stream);
+
+/* ---- sampler (include/sglang/engine/engine.h:36-55) ------------------------- */
+
+/* Sampler::sample, all-greedy branch (src/engine/engine.cc:294-298): argmax over
+ * bf16 logits [rows, vocab] (row stride ld), first index on ties, int32 out. */
+B200_API int b200_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
+                         b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_TOKEN_LOOP_H_ */

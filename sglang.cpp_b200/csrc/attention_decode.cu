@@ -1,0 +1,525 @@
+// Paged-KV GQA decode attention: persistent split-KV flash-decode for sm_100a.
+//
+// The kernel is bound by streaming each request's K and V rows from HBM once.
+// Design, in the order the bytes move:
+//   * KV pool layout (one layer): [slots, kv_heads, 128] bf16, so all heads of a
+//     slot are contiguous and a page of P consecutive slots is one dense block.
+//     A TMA tensor map views it as rows of 128 elements; the producer warp copies
+//     boxes of (keys-per-copy x kv_heads) rows x 64 elements with the 128-byte
+//     swizzle into a 3-stage ring of 64 KB stages (K lo/hi halves, V lo/hi halves).
+//   * a stage always holds 128 (key, head) rows: 128/kv_heads keys x kv_heads.
+//     Eight consumer warps each own one (head, 16-key group) tile of a stage, so a
+//     warp keeps the same KV head for the whole kernel.
+//   * per tile: S = Q K^T with mma.sync m16n8k16 (the G = q_heads/kv_heads query
+//     heads of the group are rows of the 16-row A operand), online softmax in the
+//     exp2 domain, O += P V.  Tensor throughput is irrelevant here; mma + ldmatrix
+//     is used because it needs ~10x fewer issue slots than CUDA-core dot products,
+//     which keeps the SM free to run the copy pipeline.
+//   * work items are (request, run of stages); the split is computed on the
+//     device from seq_lens alone (no host plan, graph-replay safe) so that there
+//     are ~8 items per CTA; CTAs take items round-robin and the stage ring runs
+//     across item boundaries, so there is no pipeline bubble between items.
+//   * every warp writes an (m, l, O) partial; the CTA that finishes a request's
+//     last item merges the partials (threadfence + atomic ticket) and writes bf16.
+#include "common.cuh"
+#include "tensormap.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kStageRows = 128;                      // (key, head) rows per stage
+constexpr uint32_t kHalfBytes = kStageRows * 128;    // one 64-element half tile
+constexpr uint32_t kStageBytes = 4 * kHalfBytes;     // K lo, K hi, V lo, V hi
+constexpr int kStages = 3;
+constexpr int kMaxBatch = 1024;
+constexpr int kSlotTab = 1024;
+constexpr int kItemsPerCta = 8;
+
+struct DecodeParams {
+    __nv_bfloat16* out;
+    const __nv_bfloat16* q;
+    int64_t q_st, q_sh;
+    const int32_t* page_table;
+    int64_t pt_stride;
+    const int32_t* table_idx;
+    const int32_t* seq_lens;
+    int batch, q_heads, kv_heads, group;
+    int stage_keys;     // 128 / kv_heads
+    int kpc;            // keys per TMA copy = min(page_size, stage_keys)
+    int64_t num_slots;
+    float scale_log2;
+    float* ws_o;        // [max_items * KG, q_heads, 128]
+    float* ws_ml;       // [max_items * KG, q_heads, 2]
+    int* counters;      // [kMaxBatch], zero between calls
+    int max_items;
+    int* status;
+};
+
+struct ItemInfo {
+    int b, len, s_begin, s_end, nchunks, item;
+};
+
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ int s_prefix[kMaxBatch + 1];  // exclusive scan of items per request
+    __shared__ int s_slot_tab[kSlotTab];
+    __shared__ int s_red[16];
+    __shared__ int s_chunk_stages;
+    __shared__ int s_ticket;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int B = p.batch;
+    const int SK = p.stage_keys;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kConsumerWarps && lane == 0) {
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+    }
+
+    pdl_wait_prior();
+
+    // ---- device-side split: stages per request -> items per request -> scan ----
+    int my_stages = 0;
+    for (int b = threadIdx.x; b < B; b += kThreads) my_stages += (max(p.seq_lens[b], 0) + SK - 1) / SK;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) my_stages += __shfl_xor_sync(0xffffffffu, my_stages, o);
+    if (lane == 0) s_red[warp] = my_stages;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int w = 0; w < kThreads / 32; ++w) total += s_red[w];
+        const int target = static_cast<int>(gridDim.x) * kItemsPerCta;
+        int cs = (total + target - 1) / target;
+        s_chunk_stages = cs < 2 ? 2 : cs;
+    }
+    __syncthreads();
+    const int chunk_stages = s_chunk_stages;
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < B; base += 32) {
+            const int b = base + lane;
+            int n = 0;
+            if (b < B) {
+                const int st = (max(p.seq_lens[b], 0) + SK - 1) / SK;
+                n = (st + chunk_stages - 1) / chunk_stages;
+            }
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            if (b < B) s_prefix[b] = carry + incl - n;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) s_prefix[B] = carry;
+    }
+    __syncthreads();
+    const int total_items = s_prefix[B];
+    if (total_items > p.max_items) {
+        if (threadIdx.x == 0) atomicExch(&p.status[kStatusBadIndex], total_items + 1);
+        return;
+    }
+
+    auto locate = [&](int w) {
+        ItemInfo it;
+        int lo = 0, hi = B;  // largest b with s_prefix[b] <= w and items(b) > 0
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_prefix[mid] <= w) lo = mid; else hi = mid;
+        }
+        it.b = lo;
+        it.item = w;
+        it.len = p.seq_lens[lo];
+        const int st = (it.len + SK - 1) / SK;
+        it.nchunks = (st + chunk_stages - 1) / chunk_stages;
+        const int per = (st + it.nchunks - 1) / it.nchunks;
+        const int c = w - s_prefix[lo];
+        it.s_begin = c * per;
+        it.s_end = min(it.s_begin + per, st);
+        return it;
+    };
+
+    const int Hkv = p.kv_heads;
+    const int KG = kConsumerWarps / Hkv;  // 16-key groups per stage
+    bool failed = false;
+    uint32_t it_count = 0;  // stages consumed / produced so far by this CTA
+
+    if (warp == kConsumerWarps) {
+        // ================= producer warp =================
+        const uint32_t copy_bytes = static_cast<uint32_t>(p.kpc) * Hkv * 128u;  // one half-tile box
+        for (int w = blockIdx.x; w < total_items && !failed; w += gridDim.x) {
+            const ItemInfo it = locate(w);
+            const int32_t* pt_row = p.page_table + static_cast<int64_t>(p.table_idx[it.b]) * p.pt_stride;
+            const int first_key = it.s_begin * SK;
+            const int item_keys = min(it.len, it.s_end * SK) - first_key;
+            const int item_copies = (item_keys + p.kpc - 1) / p.kpc;
+            // Slot of the first key of every copy of this item (the previous item's
+            // table is no longer needed: all of its copies have been issued).
+            __syncwarp();
+            for (int c = lane; c < min(item_copies, kSlotTab); c += 32)
+                s_slot_tab[c] = pt_row[first_key + c * p.kpc];
+            __syncwarp();
+            for (int st = it.s_begin; st < it.s_end; ++st, ++it_count) {
+                const uint32_t slot = it_count % kStages;
+                const uint32_t parity = ((it_count / kStages) & 1u) ^ 1u;
+                if (!mbar_wait_bounded(smem_u32(&empty_bar[slot]), parity, p.status, 201)) {
+                    failed = true;
+                    break;
+                }
+                const int k0 = st * SK;
+                const int valid = min(SK, it.len - k0);
+                const int ncopies = (valid + p.kpc - 1) / p.kpc;
+                const uint32_t bar = smem_u32(&full_bar[slot]);
+                if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ncopies) * 4u * copy_bytes);
+                __syncwarp();
+                const uint32_t stage_base = smem_base + slot * kStageBytes;
+                for (int ci = lane; ci < ncopies * 4; ci += 32) {
+                    const int copy = ci >> 2, which = ci & 3;
+                    const int tab = (k0 - first_key) / p.kpc + copy;
+                    int64_t sl = tab < kSlotTab ? s_slot_tab[tab] : pt_row[k0 + copy * p.kpc];
+                    if (sl < 0 || sl + p.kpc > p.num_slots) {
+                        atomicExch(&p.status[kStatusBadIndex], static_cast<int>(sl) + 1);
+                        sl = 0;
+                    }
+                    const uint32_t dst = stage_base + which * kHalfBytes + copy * copy_bytes;
+                    tma_load_2d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
+                                static_cast<int>(sl) * Hkv, bar);
+                }
+            }
+        }
+        return;
+    }
+
+    // ================= consumer warps =================
+    const int h = warp % Hkv;       // KV head of this warp
+    const int kg = warp / Hkv;      // 16-key group inside a stage
+    const int G = p.group;
+    const int g = lane >> 2, t = lane & 3;
+    const int mi = lane >> 3, r8 = lane & 7;
+
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+        const ItemInfo it = locate(w);
+
+        // Query fragments: rows of the A operand are the G heads of this KV group.
+        uint32_t qa[8][4];
+        {
+            const __nv_bfloat16* q0 = p.q + it.b * p.q_st + static_cast<int64_t>(h * G + g) * p.q_sh;
+            const __nv_bfloat16* q1 = q0 + 8 * p.q_sh;
+            const bool r0 = g < G, r1 = (g + 8) < G;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const int d0 = ks * 16 + 2 * t;
+                qa[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0) : 0u;
+                qa[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0 + 8) : 0u;
+                qa[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0) : 0u;
+                qa[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0 + 8) : 0u;
+            }
+        }
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float o[16][4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+        for (int st = it.s_begin; st < it.s_end; ++st, ++it_count) {
+            const uint32_t slot = it_count % kStages;
+            const uint32_t parity = (it_count / kStages) & 1u;
+            if (!failed && !mbar_wait_bounded(smem_u32(&full_bar[slot]), parity, p.status, 202))
+                failed = true;
+            const int nvalid = it.len - (st * SK + kg * 16);  // valid keys in this warp's tile
+            if (!failed && nvalid > 0) {
+                const uint32_t stage_base = smem_base + slot * kStageBytes;
+                const uint32_t tile_row0 = static_cast<uint32_t>(kg * 16) * Hkv + h;
+                if (nvalid < 16) {
+                    // Rows past the end of the sequence hold stale bytes: clear V so
+                    // that 0 * garbage cannot poison the accumulator.
+                    for (int i = lane; i < (16 - nvalid) * 16; i += 32) {
+                        const int j = nvalid + (i >> 4), c16 = i & 15;
+                        const uint32_t a = stage_base + (2 + (c16 >> 3)) * kHalfBytes +
+                                           (tile_row0 + j * Hkv) * 128u + (c16 & 7) * 16u;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                }
+                // ---- S = Q K^T for 16 keys ----
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    const int j = (mi >> 1) * 8 + r8;
+                    const uint32_t rowoff = (tile_row0 + j * Hkv) * 128u;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const int c16 = ks * 2 + (mi & 1);
+                        const uint32_t row_addr = stage_base + (c16 >> 3) * kHalfBytes + rowoff;
+                        uint32_t b00, b01, b10, b11;
+                        ldmatrix_x4(swz128(row_addr, c16 & 7), b00, b01, b10, b11);
+                        mma_bf16_16816(s0, qa[ks], b00, b01);
+                        mma_bf16_16816(s1, qa[ks], b10, b11);
+                    }
+                }
+                // ---- online softmax (exp2 domain) ----
+                float x[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float v = (e < 4 ? s0[e] : s1[e - 4]) * p.scale_log2;
+                    const int key = (e >> 2) * 8 + 2 * t + (e & 1);
+                    x[e] = key < nvalid ? v : -INFINITY;
+                }
+                float mx0 = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[4], x[5]));
+                float mx1 = fmaxf(fmaxf(x[2], x[3]), fmaxf(x[6], x[7]));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: key 0 is valid
+                const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+                m0 = mn0;
+                m1 = mn1;
+                const float p00 = exp2f(x[0] - mn0), p01 = exp2f(x[1] - mn0);
+                const float p02 = exp2f(x[4] - mn0), p03 = exp2f(x[5] - mn0);
+                const float p10 = exp2f(x[2] - mn1), p11 = exp2f(x[3] - mn1);
+                const float p12 = exp2f(x[6] - mn1), p13 = exp2f(x[7] - mn1);
+                l0 = l0 * al0 + (p00 + p01 + p02 + p03);
+                l1 = l1 * al1 + (p10 + p11 + p12 + p13);
+                uint32_t pa[4];
+                pa[0] = pack_bf16(p00, p01);
+                pa[1] = pack_bf16(p10, p11);
+                pa[2] = pack_bf16(p02, p03);
+                pa[3] = pack_bf16(p12, p13);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    o[i][0] *= al0;
+                    o[i][1] *= al0;
+                    o[i][2] *= al1;
+                    o[i][3] *= al1;
+                }
+                // ---- O += P V ----
+                {
+                    const int j = (mi & 1) * 8 + r8;
+                    const uint32_t rowoff = (tile_row0 + j * Hkv) * 128u;
+#pragma unroll
+                    for (int np = 0; np < 8; ++np) {
+                        const int c16 = np * 2 + (mi >> 1);
+                        const uint32_t row_addr = stage_base + (2 + (c16 >> 3)) * kHalfBytes + rowoff;
+                        uint32_t v0, v1, v2, v3;
+                        ldmatrix_x4_trans(swz128(row_addr, c16 & 7), v0, v1, v2, v3);
+                        mma_bf16_16816(o[2 * np], pa, v0, v1);
+                        mma_bf16_16816(o[2 * np + 1], pa, v2, v3);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[slot]));
+        }
+
+        // ---- item epilogue ----
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const int nparts = it.nchunks * KG;
+        const int Hq = p.q_heads;
+        if (nparts == 1) {
+            // Single partial: normalise and store bf16 directly.
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = g + rr * 8;
+                if (row < G) {
+                    const float l = rr ? l1 : l0;
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    __nv_bfloat16* dst = p.out + (static_cast<int64_t>(it.b) * Hq + h * G + row) * kD;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) =
+                            pack_bf16(o[i][2 * rr] * inv, o[i][2 * rr + 1] * inv);
+                }
+            }
+        } else {
+            const int64_t part = static_cast<int64_t>(it.item) * KG + kg;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = g + rr * 8;
+                if (row < G) {
+                    const int64_t ph = part * Hq + h * G + row;
+                    float* dst = p.ws_o + ph * kD;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) =
+                            make_float2(o[i][2 * rr], o[i][2 * rr + 1]);
+                    if (t == 0)
+                        *reinterpret_cast<float2*>(p.ws_ml + ph * 2) =
+                            make_float2(rr ? m1 : m0, rr ? l1 : l0);
+                }
+            }
+            __threadfence();
+            consumer_bar();
+            if (threadIdx.x == 0) s_ticket = atomicAdd(&p.counters[it.b], 1);
+            consumer_bar();
+            const int ticket = s_ticket;
+            if (ticket == it.nchunks - 1) {
+                // This CTA finished the request's last item: merge all partials.
+                __threadfence();
+                const int64_t part0 = static_cast<int64_t>(s_prefix[it.b]) * KG;
+                for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
+                    const int head = idx / (kD / 2), dp = idx % (kD / 2);
+                    float M = -INFINITY;
+                    for (int pp = 0; pp < nparts; ++pp)
+                        M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                    float L = 0.f, a0 = 0.f, a1 = 0.f;
+                    for (int pp = 0; pp < nparts; ++pp) {
+                        const int64_t ph = (part0 + pp) * Hq + head;
+                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
+                        const float wgt = exp2f(ml.x - M);
+                        const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
+                        L += ml.y * wgt;
+                        a0 += ov.x * wgt;
+                        a1 += ov.y * wgt;
+                    }
+                    const float inv = L > 0.f ? 1.f / L : 0.f;
+                    *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
+                        pack_bf16(a0 * inv, a1 * inv);
+                }
+                if (threadIdx.x == 0) p.counters[it.b] = 0;
+            }
+            consumer_bar();  // s_ticket is reused by the next item
+        }
+    }
+}
+
+}  // namespace
+
+int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads) {
+    const int kg = kConsumerWarps / kv_heads;
+    const int64_t items = static_cast<int64_t>(sm_count()) * kItemsPerCta + max_batch;
+    const int64_t parts = items * kg;
+    return kMaxBatch * 4 + parts * q_heads * (kD + 2) * 4 + 256;
+}
+
+int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,
+                            const CUtensorMap& tmap_k, const CUtensorMap& tmap_v, int64_t num_slots,
+                            const int32_t* page_table, int64_t pt_stride, const int32_t* table_idx,
+                            const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
+                            int page_size, float sm_scale, void* workspace, int64_t workspace_bytes,
+                            int* status, cudaStream_t stream) {
+    const int kg = kConsumerWarps / kv_heads;
+    const int grid = sm_count();
+    // Workspace layout: counters | ws_ml | ws_o
+    const int64_t avail = workspace_bytes - kMaxBatch * 4 - 256;
+    const int64_t per_item = static_cast<int64_t>(kg) * q_heads * (kD + 2) * 4;
+    const int64_t max_items = avail / per_item;
+    if (max_items < static_cast<int64_t>(grid) * kItemsPerCta + batch) {
+        set_last_error("attention_decode: workspace of %lld bytes is too small (need %lld)",
+                       static_cast<long long>(workspace_bytes),
+                       static_cast<long long>(decode_workspace_bytes(batch, q_heads, kv_heads)));
+        return B200_ERR_INVALID_ARGUMENT;
+    }
+    DecodeParams p;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.q_st = q_st;
+    p.q_sh = q_sh;
+    p.page_table = page_table;
+    p.pt_stride = pt_stride;
+    p.table_idx = table_idx;
+    p.seq_lens = seq_lens;
+    p.batch = batch;
+    p.q_heads = q_heads;
+    p.kv_heads = kv_heads;
+    p.group = q_heads / kv_heads;
+    p.stage_keys = kStageRows / kv_heads;
+    p.kpc = page_size < p.stage_keys ? page_size : p.stage_keys;
+    p.num_slots = num_slots;
+    p.scale_log2 = sm_scale * 1.4426950408889634f;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    p.counters = reinterpret_cast<int*>(ws);
+    uint8_t* f = ws + kMaxBatch * 4;
+    f = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(f) + 255) & ~uintptr_t(255));
+    p.ws_ml = reinterpret_cast<float*>(f);
+    p.ws_o = p.ws_ml + max_items * kg * q_heads * 2;
+    p.max_items = static_cast<int>(max_items < (1 << 30) ? max_items : (1 << 30));
+    p.status = status;
+
+    const int smem = kStages * kStageBytes + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        B200_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    attention_decode_kernel<<<grid, kThreads, smem, stream>>>(tmap_k, tmap_v, p);
+    B200_CHECK_LAUNCH();
+    return B200_OK;
+}
+
+int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size) {
+    const int stage_keys = kStageRows / kv_heads;
+    const int kpc = page_size < stage_keys ? page_size : stage_keys;
+    return make_tmap_2d_bf16_sw128(out, cache, kD, static_cast<uint64_t>(num_slots) * kv_heads,
+                                   kD * 2, 64, static_cast<uint32_t>(kpc * kv_heads));
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int64_t b200_attention_decode_workspace_bytes(int max_batch, int q_heads, int kv_heads, int head_dim) {
+    if (max_batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim != b200::kD) return -1;
+    if (kv_heads > 8 || (8 % kv_heads) != 0) return -1;
+    return b200::decode_workspace_bytes(max_batch, q_heads, kv_heads);
+}
+
+int b200_attention_decode(void* out, const void* q, int64_t q_stride_token, int64_t q_stride_head,
+                          const void* k_cache, const void* v_cache, int64_t num_slots,
+                          const int32_t* page_table, int64_t page_table_stride,
+                          const int32_t* table_idx, const int32_t* seq_lens, int batch, int q_heads,
+                          int kv_heads, int head_dim, int page_size, float sm_scale, void* workspace,
+                          int64_t workspace_bytes, b200_stream_t stream) {
+    B200_CHECK_ARG(out && q && k_cache && v_cache && page_table && table_idx && seq_lens && workspace,
+                   "attention_decode: NULL tensor");
+    B200_CHECK_ARG(head_dim == b200::kD, "attention_decode: head_dim must be 128");
+    B200_CHECK_ARG(batch >= 0 && batch <= b200::kMaxBatch, "attention_decode: batch must be in [0, 1024]");
+    B200_CHECK_ARG(kv_heads >= 1 && kv_heads <= 8 && (8 % kv_heads) == 0,
+                   "attention_decode: kv_heads (per rank) must be 1, 2, 4 or 8");
+    B200_CHECK_ARG(q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
+                   "attention_decode: q_heads must be a multiple of kv_heads with group size <= 16");
+    B200_CHECK_ARG(page_size >= 1 && (page_size & (page_size - 1)) == 0,
+                   "attention_decode: page_size must be a power of two");
+    B200_CHECK_ARG(q_stride_token % 2 == 0 && q_stride_head % 2 == 0,
+                   "attention_decode: q strides must be even");
+    B200_CHECK_ARG(num_slots > 0, "attention_decode: num_slots must be positive");
+    if (batch == 0) return B200_OK;
+    int err = B200_OK;
+    int* status = b200::device_status_words(&err);
+    if (err != B200_OK) return err;
+    CUtensorMap tk, tv;
+    err = b200::make_kv_tmap(&tk, k_cache, num_slots, kv_heads, page_size);
+    if (err != B200_OK) return err;
+    err = b200::make_kv_tmap(&tv, v_cache, num_slots, kv_heads, page_size);
+    if (err != B200_OK) return err;
+    return b200::launch_attention_decode(out, q, q_stride_token, q_stride_head, tk, tv, num_slots,
+                                         page_table, page_table_stride, table_idx, seq_lens, batch,
+                                         q_heads, kv_heads, page_size, sm_scale, workspace,
+                                         workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,516 @@
+// y = x W^T for few rows (decode batches, M <= 256): a weight-streaming GEMM on
+// the tcgen05 tensor cores.
+//
+// The kernel is bound by reading W once from HBM, so the layout is chosen for
+// bytes in flight rather than for tensor-core occupancy:
+//   * swap-AB: the MMA "A" operand is a 128-row tile of W (output features run
+//     along the TMEM lanes), the "B" operand is the whole activation block
+//     x[0:NT, k-slice] (tokens run along TMEM columns).  A stage of shared
+//     memory is then 2/3 weight bytes instead of mostly padding rows of x.
+//   * split-K across a thread-block cluster: (feature tiles) x (K slices) CTAs
+//     so that about one CTA per SM issues TMA loads at once; each CTA usually
+//     holds its whole K slice in shared memory, i.e. the entire weight matrix
+//     is requested at t=0.
+//   * partial sums are exchanged through distributed shared memory in fixed
+//     rank order (deterministic), then bias / gated activation / bf16 rounding
+//     are applied by the CTA that owns that slice of features.
+//   * weight tiles do not depend on the previous kernel, so they are requested
+//     before griddepcontrol.wait; only the x loads wait for the producer of x.
+//
+// Gated epilogue (gate_up projection + SwiGLU): two accumulators share the x
+// operand, one fed by a gate-row tile of W and one by the matching up-row tile,
+// so a thread holds gate[n][m] and up[n][m] for the same (n, m).
+#include "common.cuh"
+#include "tensormap.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kTileN = 128;  // output features per CTA (UMMA M)
+constexpr int kBlockK = 64;  // bf16 elements per k-block (one 128-byte swizzle row)
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kChunkCols = 32;  // token columns exchanged per cluster round
+
+// ---- tcgen05 wrappers --------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 128
+// bytes (64 elements) under the 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);  // start address / 16
+    d |= static_cast<uint64_t>(1) << 16;                     // leading byte offset (unused here)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset / 16
+    d |= static_cast<uint64_t>(1) << 46;                     // descriptor version for sm_100
+    d |= static_cast<uint64_t>(2) << 61;                     // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M=128.
+__device__ __forceinline__ uint32_t idesc_bf16_m128(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+// ---- cluster helpers ----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+}
+
+struct SkinnyParams {
+    __nv_bfloat16* y;          // [M, n_out]
+    const __nv_bfloat16* bias; // [n_out] or NULL (plain epilogue only)
+    int M;                     // rows of x / y
+    int n_out;                 // output features (N, or N/2 with a gated epilogue)
+    int up_row_offset;         // row of W where the "up" half starts (gated only)
+    int kb_total;              // K / 64
+    int nt;                    // token columns of the accumulator (multiple of 32, >= M)
+    int stages;                // shared-memory stages in the ring
+    int epilogue;              // B200_EPILOGUE_*
+    int* status;
+};
+
+template <int NUM_A>
+__global__ void __launch_bounds__(kThreads, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tmem_full_bar;
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int nt = p.nt;
+    const uint32_t a_bytes = kTileN * kBlockK * 2;            // 16 KB per weight tile
+    const uint32_t b_bytes = static_cast<uint32_t>(nt) * kBlockK * 2;
+    const uint32_t stage_bytes = NUM_A * a_bytes + b_bytes;
+
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t split = cluster_nctarank();
+    const int kbp = (p.kb_total + static_cast<int>(split) - 1) / static_cast<int>(split);
+    const int kb_begin = static_cast<int>(rank) * kbp;
+    const int my_kb = max(0, min(kb_begin + kbp, p.kb_total) - kb_begin);
+    const int n0 = blockIdx.x * kTileN;
+
+    // TMEM columns: NUM_A accumulators of nt columns, rounded up to a power of two >= 32.
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < static_cast<uint32_t>(NUM_A * nt)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&tmem_full_bar), 1);
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // Weight tiles first: they do not depend on the kernel before this one.
+            const int early = min(my_kb, p.stages);
+            for (int i = 0; i < early; ++i) {
+                const uint32_t bar = smem_u32(&full_bar[i]);
+                const uint32_t dst = smem_base + i * stage_bytes;
+                const int kc = (kb_begin + i) * kBlockK;
+                mbar_arrive_expect_tx(bar, stage_bytes);
+                tma_load_2d(dst, &tmap_w, kc, n0, bar);
+                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, p.up_row_offset + n0, bar);
+            }
+            pdl_wait_prior();
+            for (int i = 0; i < my_kb && !failed; ++i) {
+                const int s = i % p.stages;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                const uint32_t dst = smem_base + s * stage_bytes;
+                const int kc = (kb_begin + i) * kBlockK;
+                if (i >= p.stages) {
+                    const uint32_t par = static_cast<uint32_t>((i / p.stages) - 1) & 1u;
+                    if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), par, p.status, 101)) {
+                        failed = true;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(bar, stage_bytes);
+                    tma_load_2d(dst, &tmap_w, kc, n0, bar);
+                    if (NUM_A == 2)
+                        tma_load_2d(dst + a_bytes, &tmap_w, kc, p.up_row_offset + n0, bar);
+                }
+                tma_load_2d(dst + NUM_A * a_bytes, &tmap_x, kc, 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        pdl_wait_prior();
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16_m128(nt);
+            for (int i = 0; i < my_kb; ++i) {
+                const int s = i % p.stages;
+                const uint32_t par = static_cast<uint32_t>(i / p.stages) & 1u;
+                if (!mbar_wait_bounded(smem_u32(&full_bar[s]), par, p.status, 102)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a0 = smem_base + s * stage_bytes;
+                const uint32_t b0 = a0 + NUM_A * a_bytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k) {
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    const uint64_t bdesc = kmajor_sw128_desc(b0 + k * 32);
+                    tc_mma_bf16(tmem_base, kmajor_sw128_desc(a0 + k * 32), bdesc, idesc, acc);
+                    if (NUM_A == 2)
+                        tc_mma_bf16(tmem_base + nt, kmajor_sw128_desc(a0 + a_bytes + k * 32), bdesc,
+                                    idesc, acc);
+                }
+                tc_commit(smem_u32(&empty_bar[s]));
+            }
+            if (my_kb > 0 && !failed)
+                tc_commit(smem_u32(&tmem_full_bar));
+            else
+                mbar_arrive(smem_u32(&tmem_full_bar));
+        }
+    } else {
+        pdl_wait_prior();
+    }
+    __syncwarp();
+
+    // ---- epilogue: every warp walks the same sequence of cluster barriers ----
+    const bool is_epi = warp >= 2;
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int feat_local = q * 32 + lane;         // feature row inside the tile
+    float* xbuf = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+    const uint32_t xbuf_addr = smem_base;
+    const int nchunks = nt / kChunkCols;
+    const int chunk_floats = NUM_A * kChunkCols * kTileN;
+
+    if (is_epi) {
+        if (!mbar_wait_bounded(smem_u32(&tmem_full_bar), 0, p.status, 103)) failed = true;
+        tc_fence_after();
+    }
+    pdl_launch_dependents();
+
+    for (int c = 0; c < nchunks; ++c) {
+        uint32_t g[32], u[32];
+        if (is_epi) {
+            if (my_kb > 0 && !failed) {
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                       static_cast<uint32_t>(c * kChunkCols);
+                tmem_ld_32x32b_x32(taddr, g);
+                if (NUM_A == 2) tmem_ld_32x32b_x32(taddr + nt, u);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    g[j] = 0u;
+                    u[j] = 0u;
+                }
+            }
+        }
+        if (split == 1) {
+            if (is_epi) {
+                const int n = n0 + feat_local;
+                if (n < p.n_out) {
+                    const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = c * kChunkCols + j;
+                        if (m < p.M) {
+                            float r;
+                            if (NUM_A == 2) {
+                                const float gv = round_bf16(__uint_as_float(g[j]));
+                                const float uv = round_bf16(__uint_as_float(u[j]));
+                                r = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                            } else {
+                                r = __uint_as_float(g[j]) + bias;
+                            }
+                            p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(r);
+                        }
+                    }
+                }
+            }
+            continue;
+        }
+
+        // Multi-CTA K split: publish this CTA's partial chunk, then reduce the
+        // slice of features this rank owns over all ranks in rank order.
+        float* buf = xbuf + (c & 1) * chunk_floats;
+        if (is_epi) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                buf[j * kTileN + feat_local] = __uint_as_float(g[j]);
+                if (NUM_A == 2) buf[(kChunkCols + j) * kTileN + feat_local] = __uint_as_float(u[j]);
+            }
+        }
+        cluster_sync_all();
+        if (is_epi) {
+            const int F = kTileN / static_cast<int>(split);  // features owned by this rank
+            const int te = (warp - 2) * 32 + lane;           // 0..127
+            const int f = static_cast<int>(rank) * F + (te % F);
+            const int n = n0 + f;
+            const int cols_per_pass = kTileN / F;
+            const uint32_t cbase = xbuf_addr + static_cast<uint32_t>((c & 1) * chunk_floats) * 4u;
+            const float bias = (p.bias && n < p.n_out) ? __bfloat162float(p.bias[n]) : 0.f;
+            for (int j = te / F; j < kChunkCols; j += cols_per_pass) {
+                float sg = 0.f, su = 0.f;
+                for (uint32_t r = 0; r < split; ++r) {
+                    sg += ld_dsmem_f32(cbase + static_cast<uint32_t>(j * kTileN + f) * 4u, r);
+                    if (NUM_A == 2)
+                        su += ld_dsmem_f32(
+                            cbase + static_cast<uint32_t>((kChunkCols + j) * kTileN + f) * 4u, r);
+                }
+                const int m = c * kChunkCols + j;
+                if (m < p.M && n < p.n_out) {
+                    float r;
+                    if (NUM_A == 2) {
+                        const float gv = round_bf16(sg), uv = round_bf16(su);
+                        r = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                    } else {
+                        r = sg + bias;
+                    }
+                    p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(r);
+                }
+            }
+        }
+    }
+    if (split > 1) cluster_sync_all();  // nobody leaves while a peer may still read its chunk
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+struct TmapCacheEntry {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    uint32_t box_inner, box_outer;
+    CUtensorMap map;
+};
+
+// Small per-thread cache: the same weights and activation buffers come back
+// every layer and every step, and encoding a tensor map costs about a microsecond.
+int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                uint32_t box_inner, uint32_t box_outer) {
+    constexpr int kEntries = 1024;
+    thread_local TmapCacheEntry cache[kEntries];
+    thread_local bool used[kEntries] = {};
+    uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+    h ^= (outer * 0x100000001B3ull) ^ (inner << 20) ^ (static_cast<uint64_t>(box_outer) << 44);
+    const int idx = static_cast<int>((h >> 17) % kEntries);
+    TmapCacheEntry& e = cache[idx];
+    if (used[idx] && e.base == base && e.inner == inner && e.outer == outer && e.pitch == pitch &&
+        e.box_inner == box_inner && e.box_outer == box_outer) {
+        *out = e.map;
+        return B200_OK;
+    }
+    int err = make_tmap_2d_bf16_sw128(out, base, inner, outer, pitch, box_inner, box_outer);
+    if (err != B200_OK) return err;
+    e = TmapCacheEntry{base, inner, outer, pitch, box_inner, box_outer, *out};
+    used[idx] = true;
+    return B200_OK;
+}
+
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+}  // namespace
+
+// One slab of at most 256 rows.
+int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, int M, int N,
+                       int K, int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
+    const bool gated = epilogue != B200_EPILOGUE_NONE;
+    const int n_out = gated ? N / 2 : N;
+    const int nt = div_ceil(M, 32) * 32;
+    const int kb_total = K / kBlockK;
+    const int n_tiles = div_ceil(n_out, kTileN);
+    const int num_a = gated ? 2 : 1;
+
+    // K split: about 1.5 CTAs per SM in total, at most 8 ranks (portable cluster size).
+    int split = 1;
+    const int forced = env_int("B200_GEMM_SPLIT", 0);
+    if (forced > 0) {
+        split = forced;
+    } else {
+        const int budget = sm_count() * 3 / 2;
+        while (split < 8 && n_tiles * split * 2 <= budget && split * 2 <= kb_total) split *= 2;
+    }
+    const int kbp = div_ceil(kb_total, split);
+
+    const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt * kBlockK * 2;
+    const uint32_t exch_bytes = split > 1 ? 2u * num_a * kChunkCols * kTileN * 4u : 0u;
+    const uint32_t smem_limit = 200 * 1024;
+    int stages = kbp < kMaxStages ? kbp : kMaxStages;
+    while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
+    uint32_t smem_bytes = stages * stage_bytes;
+    if (smem_bytes < exch_bytes) smem_bytes = exch_bytes;
+    smem_bytes += 1024;  // alignment slack
+    if (stage_bytes > smem_limit) {
+        set_last_error("linear: one pipeline stage (%u bytes) does not fit in shared memory",
+                       stage_bytes);
+        return B200_ERR_UNSUPPORTED;
+    }
+
+    CUtensorMap tmap_w, tmap_x;
+    int err = cached_tmap(&tmap_w, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
+                          static_cast<uint64_t>(K) * 2, kBlockK, kTileN);
+    if (err != B200_OK) return err;
+    err = cached_tmap(&tmap_x, x, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                      static_cast<uint64_t>(ldx) * 2, kBlockK, static_cast<uint32_t>(nt));
+    if (err != B200_OK) return err;
+
+    SkinnyParams p;
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.M = M;
+    p.n_out = n_out;
+    p.up_row_offset = N / 2;
+    p.kb_total = kb_total;
+    p.nt = nt;
+    p.stages = stages;
+    p.epilogue = epilogue;
+    p.status = status;
+
+    auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem_bytes)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, split, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int nattr = 0;
+    attrs[nattr].id = cudaLaunchAttributeClusterDimension;
+    attrs[nattr].val.clusterDim.x = 1;
+    attrs[nattr].val.clusterDim.y = split;
+    attrs[nattr].val.clusterDim.z = 1;
+    ++nattr;
+    cfg.attrs = attrs;
+    cfg.numAttrs = nattr;
+    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_x, p));
+    return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
+                int64_t ldx, int epilogue, b200_stream_t stream) {
+    B200_CHECK_ARG(y && x && w, "linear: NULL tensor");
+    B200_CHECK_ARG(M >= 0 && N > 0 && K > 0, "linear: bad shape");
+    B200_CHECK_ARG(K % 64 == 0, "linear: K must be a multiple of 64");
+    B200_CHECK_ARG(ldx >= K && ldx % 8 == 0, "linear: ldx must be >= K and a multiple of 8");
+    B200_CHECK_ARG(epilogue >= B200_EPILOGUE_NONE && epilogue <= B200_EPILOGUE_GEGLU,
+                   "linear: unknown epilogue");
+    const bool gated = epilogue != B200_EPILOGUE_NONE;
+    B200_CHECK_ARG(!gated || (N % 2 == 0), "linear: a gated epilogue needs an even N");
+    B200_CHECK_ARG(!gated || bias == nullptr, "linear: bias is not supported with a gated epilogue");
+    B200_CHECK_ARG((gated ? N / 2 : N) % 8 == 0, "linear: output width must be a multiple of 8");
+    if (M == 0) return B200_OK;
+    int err = B200_OK;
+    int* status = b200::device_status_words(&err);
+    if (err != B200_OK) return err;
+    const int n_out = gated ? N / 2 : N;
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+    for (int m0 = 0; m0 < M; m0 += 256) {
+        const int rows = (M - m0) < 256 ? (M - m0) : 256;
+        err = b200::launch_skinny_gemm(yp + static_cast<int64_t>(m0) * n_out,
+                                       xp + static_cast<int64_t>(m0) * ldx, w, bias, rows, N, K, ldx,
+                                       epilogue, status, static_cast<cudaStream_t>(stream));
+        if (err != B200_OK) return err;
+    }
+    return B200_OK;
+}
+
+}  // extern "C"
