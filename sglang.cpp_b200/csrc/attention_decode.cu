@@ -494,7 +494,7 @@ int b200_attention_decode(void* out, const void* q, int64_t q_stride_token, int6
                           const int32_t* table_idx, const int32_t* seq_lens, int batch, int q_heads,
                           int kv_heads, int head_dim, int page_size, float sm_scale, void* workspace,
                           int64_t workspace_bytes, b200_stream_t stream) {
-    B200_CHECK_ARG(out && q && k_cache && v_cache && page_table && table_idx && seq_lens && workspace,
+    B200_CHECK_ARG(batch == 0 || (out && q && k_cache && v_cache && page_table && table_idx && seq_lens && workspace),
                    "attention_decode: NULL tensor");
     B200_CHECK_ARG(head_dim == b200::kD, "attention_decode: head_dim must be 128");
     B200_CHECK_ARG(batch >= 0 && batch <= b200::kMaxBatch, "attention_decode: batch must be in [0, 1024]");

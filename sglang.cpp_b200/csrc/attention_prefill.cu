@@ -353,7 +353,8 @@ int b200_attention_prefill(void* out, const void* q, int64_t q_stride_token, int
                            const int32_t* qo_indptr, int batch, int max_extend_len, int q_heads,
                            int kv_heads, int head_dim, int page_size, float sm_scale,
                            b200_stream_t stream) {
-    B200_CHECK_ARG(out && q && k_cache && v_cache && page_table && table_idx && seq_lens && qo_indptr,
+    B200_CHECK_ARG(batch == 0 || max_extend_len == 0 ||
+                       (out && q && k_cache && v_cache && page_table && table_idx && seq_lens && qo_indptr),
                    "attention_prefill: NULL tensor");
     B200_CHECK_ARG(head_dim == b200::kD, "attention_prefill: head_dim must be 128");
     B200_CHECK_ARG(batch >= 0 && batch <= 65535, "attention_prefill: batch must be in [0, 65535]");

@@ -107,21 +107,21 @@ int launch_embedding(void* out, const void* table, const int32_t* ids, int token
 extern "C" {
 
 int b200_silu_and_mul(void* out, const void* in, int tokens, int d, b200_stream_t stream) {
-    B200_CHECK_ARG(out && in, "silu_and_mul: NULL tensor");
     B200_CHECK_ARG(tokens >= 0 && d > 0 && d % 8 == 0, "silu_and_mul: d must be a positive multiple of 8");
+    B200_CHECK_ARG(tokens == 0 || (out && in), "silu_and_mul: NULL tensor");
     return b200::launch_act_and_mul(out, in, tokens, d, false, static_cast<cudaStream_t>(stream));
 }
 
 int b200_gelu_and_mul(void* out, const void* in, int tokens, int d, b200_stream_t stream) {
-    B200_CHECK_ARG(out && in, "gelu_and_mul: NULL tensor");
     B200_CHECK_ARG(tokens >= 0 && d > 0 && d % 8 == 0, "gelu_and_mul: d must be a positive multiple of 8");
+    B200_CHECK_ARG(tokens == 0 || (out && in), "gelu_and_mul: NULL tensor");
     return b200::launch_act_and_mul(out, in, tokens, d, true, static_cast<cudaStream_t>(stream));
 }
 
 int b200_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
                    int vocab, b200_stream_t stream) {
-    B200_CHECK_ARG(out && table && ids, "embedding: NULL tensor");
     B200_CHECK_ARG(tokens >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0, "embedding: bad size");
+    B200_CHECK_ARG(tokens == 0 || (out && table && ids), "embedding: NULL tensor");
     int err = B200_OK;
     int* status = b200::device_status_words(&err);
     if (err != B200_OK) return err;
@@ -132,10 +132,9 @@ int b200_embedding(void* out, const void* table, const int32_t* ids, int tokens,
 int b200_gather_int32_2d(int32_t* out, const int32_t* table, int64_t rows, int64_t stride,
                          int64_t cols, const int32_t* req_indices, const int32_t* positions,
                          int64_t count, b200_stream_t stream) {
-    B200_CHECK_ARG(table && req_indices && positions, "gather_int32_2d: NULL tensor");
     B200_CHECK_ARG(count >= 0 && rows >= 0 && cols >= 0, "gather_int32_2d: negative size");
     if (count == 0) return B200_OK;
-    B200_CHECK_ARG(out, "gather_int32_2d: out is NULL");
+    B200_CHECK_ARG(out && table && req_indices && positions, "gather_int32_2d: NULL tensor");
     const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
     b200::gather_int32_2d_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         out, table, rows, stride, cols, req_indices, positions, count);
@@ -146,9 +145,9 @@ int b200_gather_int32_2d(int32_t* out, const int32_t* table, int64_t rows, int64
 int b200_write_token_pool(int32_t* table, int64_t rows, int64_t stride, int64_t cols,
                           const int32_t* req_indices, const int32_t* positions,
                           const int32_t* tokens, int64_t count, b200_stream_t stream) {
-    B200_CHECK_ARG(table && req_indices && positions && tokens, "write_token_pool: NULL tensor");
     B200_CHECK_ARG(count >= 0 && rows >= 0 && cols >= 0, "write_token_pool: negative size");
     if (count == 0) return B200_OK;
+    B200_CHECK_ARG(table && req_indices && positions && tokens, "write_token_pool: NULL tensor");
     const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
     b200::write_token_pool_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         table, rows, stride, cols, req_indices, positions, tokens, count);

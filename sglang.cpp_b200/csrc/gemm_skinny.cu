@@ -486,8 +486,8 @@ extern "C" {
 
 int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                 int64_t ldx, int epilogue, b200_stream_t stream) {
-    B200_CHECK_ARG(y && x && w, "linear: NULL tensor");
     B200_CHECK_ARG(M >= 0 && N > 0 && K > 0, "linear: bad shape");
+    B200_CHECK_ARG(M == 0 || (y && x && w), "linear: NULL tensor");
     B200_CHECK_ARG(K % 64 == 0, "linear: K must be a multiple of 64");
     B200_CHECK_ARG(ldx >= K && ldx % 8 == 0, "linear: ldx must be >= K and a multiple of 8");
     B200_CHECK_ARG(epilogue >= B200_EPILOGUE_NONE && epilogue <= B200_EPILOGUE_GEGLU,

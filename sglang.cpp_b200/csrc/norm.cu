@@ -208,8 +208,8 @@ extern "C" {
 
 int b200_rmsnorm(void* out, const void* x, const void* weight, int rows, int hidden, float eps,
                  b200_stream_t stream) {
-    B200_CHECK_ARG(out && x && weight, "rmsnorm: NULL tensor");
     B200_CHECK_ARG(rows >= 0, "rmsnorm: rows must be >= 0");
+    B200_CHECK_ARG(rows == 0 || (out && x && weight), "rmsnorm: NULL tensor");
     B200_CHECK_ARG(hidden > 0, "RMSNorm last dimension must be positive");
     B200_CHECK_ARG(hidden % 8 == 0, "rmsnorm: hidden must be a multiple of 8 (16-byte rows)");
     return b200::launch_rmsnorm(out, x, weight, rows, hidden, eps, static_cast<cudaStream_t>(stream));
@@ -217,8 +217,8 @@ int b200_rmsnorm(void* out, const void* x, const void* weight, int rows, int hid
 
 int b200_fused_add_rmsnorm(void* x, void* residual, const void* weight, int rows, int hidden,
                            float eps, b200_stream_t stream) {
-    B200_CHECK_ARG(x && residual && weight, "fused_add_rmsnorm: NULL tensor");
     B200_CHECK_ARG(rows >= 0, "fused_add_rmsnorm: rows must be >= 0");
+    B200_CHECK_ARG(rows == 0 || (x && residual && weight), "fused_add_rmsnorm: NULL tensor");
     B200_CHECK_ARG(hidden > 0, "RMSNorm last dimension must be positive");
     B200_CHECK_ARG(hidden % 8 == 0, "fused_add_rmsnorm: hidden must be a multiple of 8");
     return b200::launch_fused_add_rmsnorm(x, residual, weight, rows, hidden, eps,
@@ -231,8 +231,8 @@ int b200_qk_rmsnorm_strided(void* q, void* k, const void* q_weight, const void* 
                             int64_t k_stride_head, float eps, b200_stream_t stream) {
     B200_CHECK_ARG(tokens >= 0 && q_heads >= 0 && k_heads >= 0, "qk_rmsnorm: negative size");
     B200_CHECK_ARG(head_dim > 0 && head_dim % 2 == 0, "qk_rmsnorm: head_dim must be even");
-    B200_CHECK_ARG(q_heads == 0 || (q && q_weight), "qk_rmsnorm: q / q_weight is NULL");
-    B200_CHECK_ARG(k_heads == 0 || (k && k_weight), "qk_rmsnorm: k / k_weight is NULL");
+    B200_CHECK_ARG(tokens == 0 || q_heads == 0 || (q && q_weight), "qk_rmsnorm: q / q_weight is NULL");
+    B200_CHECK_ARG(tokens == 0 || k_heads == 0 || (k && k_weight), "qk_rmsnorm: k / k_weight is NULL");
     B200_CHECK_ARG((q_stride_token % 2 == 0) && (q_stride_head % 2 == 0) &&
                        (k_stride_token % 2 == 0) && (k_stride_head % 2 == 0),
                    "qk_rmsnorm: strides must be even (4-byte aligned rows)");

@@ -211,8 +211,9 @@ int b200_rope_neox_inplace(void* q, void* k, const float* cos_table, const float
                            int head_dim, int rotary_dim, int max_pos, int64_t q_stride_token,
                            int64_t q_stride_head, int64_t k_stride_token, int64_t k_stride_head,
                            b200_stream_t stream) {
-    B200_CHECK_ARG(cos_table && sin_table && positions, "rope: NULL table or positions");
     B200_CHECK_ARG(tokens >= 0 && q_heads >= 0 && k_heads >= 0, "rope: negative size");
+    if (tokens == 0) return B200_OK;
+    B200_CHECK_ARG(cos_table && sin_table && positions, "rope: NULL table or positions");
     B200_CHECK_ARG(rotary_dim % 2 == 0, "rotary_dim must be even");
     B200_CHECK_ARG(rotary_dim > 0 && rotary_dim <= head_dim, "rope: rotary_dim out of range");
     B200_CHECK_ARG(q_heads == 0 || q, "rope: q is NULL");
@@ -237,8 +238,9 @@ int b200_store_kv(void* k_cache, void* v_cache, const void* k, const void* v,
                   const int32_t* out_loc, int tokens, int kv_heads, int head_dim,
                   int64_t k_stride_token, int64_t v_stride_token, int64_t num_slots,
                   b200_stream_t stream) {
-    B200_CHECK_ARG(k_cache && v_cache && k && v && out_loc, "store_kv: NULL tensor");
     B200_CHECK_ARG(tokens >= 0 && kv_heads > 0 && head_dim > 0, "store_kv: bad size");
+    if (tokens == 0) return B200_OK;
+    B200_CHECK_ARG(k_cache && v_cache && k && v && out_loc, "store_kv: NULL tensor");
     const int64_t elems = static_cast<int64_t>(kv_heads) * head_dim;
     B200_CHECK_ARG(elems % 8 == 0 && k_stride_token % 8 == 0 && v_stride_token % 8 == 0,
                    "store_kv: rows must be 16-byte aligned");
@@ -261,6 +263,8 @@ int b200_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weight
                            void* v_cache, int tokens, int q_heads, int kv_heads, int head_dim,
                            int max_pos, int64_t num_slots, float eps, int write_k_back,
                            b200_stream_t stream) {
+    B200_CHECK_ARG(tokens >= 0, "qknorm_rope_store: tokens must be >= 0");
+    if (tokens == 0) return B200_OK;
     B200_CHECK_ARG(qkv && cos_table && sin_table && positions && out_loc && k_cache && v_cache,
                    "qknorm_rope_store: NULL tensor");
     B200_CHECK_ARG((q_weight == nullptr) == (k_weight == nullptr),

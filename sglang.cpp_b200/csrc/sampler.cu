@@ -77,8 +77,8 @@ extern "C" {
 
 int b200_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                 b200_stream_t stream) {
-    B200_CHECK_ARG(out && logits, "argmax: NULL tensor");
     B200_CHECK_ARG(rows >= 0 && vocab > 0 && ld >= vocab, "argmax: bad shape");
+    B200_CHECK_ARG(rows == 0 || (out && logits), "argmax: NULL tensor");
     B200_CHECK_ARG(ld % 8 == 0, "argmax: row stride must be a multiple of 8 (16-byte rows)");
     return b200::launch_argmax(out, logits, rows, vocab, ld, static_cast<cudaStream_t>(stream));
 }

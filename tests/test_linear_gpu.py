@@ -60,7 +60,9 @@ def test_gate_up_swiglu_epilogue(L, pkg, M, I, K):
     gu = L.linear(x.cuda(), w.cuda())
     out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
     L.silu_and_mul(out, gu)
-    assert_close_bf16(y, out, 1e-3, RTOL, "fused vs unfused SwiGLU")
+    # (the two GEMMs split K differently, so gate or up may differ by one bf16 step before the
+    # product is rounded again)
+    assert_close_bf16(y, out, 4e-3, 3 * RTOL, "fused vs unfused SwiGLU")
 
 
 def test_linear_split_k_variants_agree(L, monkeypatch):
