@@ -1,0 +1,403 @@
+"""Decode-throughput benchmark of the B200 token loop (and of the CPU oracle beside it).
+
+Workload ("c2"): Qwen3-0.6B architecture, bf16, random-init weights N(0, 0.02) from seed 0,
+batch 64, prompt lengths uniform in [512, 2048] from seed 2 with token ids uniform over the
+vocabulary, every 4 requests sharing a 256-token prefix, paged KV cache with page size 16, greedy
+decode.  A "step" is one decode step of the whole batch: every per-token quantity derived on the
+device, 28 layers, lm_head, argmax, token write-back.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  `value` is decode tokens/s with the steps enqueued back to back (device
+time, CUDA events); `e2e` is the same loop driven the way a scheduler drives it — per step the
+host arrays go through the C ABI from host memory, the step's metadata is copied host-to-device
+from pinned memory and the sampled tokens are copied device-to-host and waited for.  With
+--gpus N > 1 (launched under torchrun) every rank runs an independent replica of the workload
+(the 0.6B model does not shard); the job's time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PAGE_SIZE = 16
+BATCH = 64
+PROMPT_LO, PROMPT_HI = 512, 2048
+SHARED_PREFIX = 256
+MAX_EXTEND_TOKENS = 8192
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_prompts(vocab: int):
+    """Seed 2: lengths uniform in [512, 2048], ids uniform over the vocabulary, groups of 4 requests
+    share their first 256 ids."""
+    rng = np.random.default_rng(2)
+    lens = rng.integers(PROMPT_LO, PROMPT_HI + 1, size=BATCH)
+    prompts = []
+    for b in range(BATCH):
+        if b % 4 == 0:
+            shared = rng.integers(0, vocab, size=SHARED_PREFIX)
+        body = rng.integers(0, vocab, size=int(lens[b]) - SHARED_PREFIX)
+        prompts.append(np.concatenate([shared, body]).astype(np.int32))
+    return prompts
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [l.strip().split(", ") for l in Path(self.tmp.name).read_text().splitlines() if l.strip()]
+        os.unlink(self.tmp.name)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        # The clock under load is what matters: take the median of the upper half of the samples.
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def algorithmic_bytes(cfg, ctx_lens):
+    """HBM bytes one decode step must move: every layer weight and the lm_head once, K and V of
+    every cached token once, the new token's K/V written, the logits written."""
+    d, L = cfg.head_dim, cfg.num_layers
+    per_layer = ((cfg.num_qo_heads + 2 * cfg.num_kv_heads) * d * cfg.hidden_size
+                 + cfg.hidden_size * cfg.num_qo_heads * d + 3 * cfg.intermediate_size * cfg.hidden_size)
+    weights = 2 * (L * per_layer + cfg.vocab_size * cfg.hidden_size)
+    kv_tok = 2 * cfg.num_kv_heads * d * L * 2
+    kv = int(sum(ctx_lens)) * kv_tok
+    out = len(ctx_lens) * (kv_tok + cfg.vocab_size * 2)
+    return weights + kv + out, kv // L
+
+
+def run_gpu(args):
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    pkg = entry.load_package()
+    pkg.load_library()
+    from sglang_cpp_b200.engine import Engine, EngineConfig
+    from sglang_cpp_b200.host_batch import HostBatcher
+
+    cfg = O.qwen3_0_6b()
+    K, W = args.steps, args.warmup
+    total_new = 2 * (K + W) + 24
+    prompts = make_prompts(cfg.vocab_size)
+    max_len = max(len(p) for p in prompts) + total_new + 1
+    num_pages = sum(math.ceil((len(p) + total_new + 1) / PAGE_SIZE) for p in prompts) + 8
+    engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, BATCH, max_len, MAX_EXTEND_TOKENS))
+    engine.load_weights(O.init_weights(cfg, seed=0, std=0.02))
+    cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
+    engine.load_rope_tables(cos, sin)
+    hb = HostBatcher(engine, num_pages, PAGE_SIZE, BATCH)
+
+    # ---- prefill through the engine, in scheduler-sized batches; prefixes are cached as they finish
+    reqs, batch, tokens = [], [], 0
+    t_prefill0 = time.perf_counter()
+    prefill_tokens = 0
+
+    def flush():
+        nonlocal batch, tokens, prefill_tokens
+        if batch:
+            hb.prefill(batch).synchronize()
+            prefill_tokens += tokens
+            for r in batch:
+                hb.cache_prefix(r)
+            batch, tokens = [], 0
+
+    for p in prompts:
+        probe = len(p)
+        if tokens + probe > MAX_EXTEND_TOKENS:
+            flush()
+        r = hb.add_request(p, total_new)
+        reqs.append(r)
+        batch.append(r)
+        tokens += r.extend_len()
+    flush()
+    prefill_s = time.perf_counter() - t_prefill0
+    engine.capture_graphs([BATCH])
+    state0 = [(r.cached_len, r.device_len) for r in reqs]
+
+    def reset():
+        for r, (c, dl) in zip(reqs, state0):
+            r.cached_len, r.device_len = c, dl
+
+    def barrier():
+        engine.synchronize()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.ExternalStream(pkg.load_library().b200_engine_stream(engine._h))
+    sampler = ClockSampler(local_rank)
+
+    # ---- phase A: device-timed, steps enqueued back to back ----
+    reset()
+    for _ in range(W):
+        hb.decode(reqs)
+    barrier()
+    ctx_a = [r.device_len for r in reqs]
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(K):
+        hb.decode(reqs)
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    _, _, launches_per_step = engine.read_profile()
+
+    # ---- phase B: end to end, the host waits for every step's tokens ----
+    reset()
+    for _ in range(W):
+        hb.decode(reqs).synchronize()
+    barrier()
+    step_ms = []
+    t0 = time.perf_counter()
+    for _ in range(K):
+        ts = time.perf_counter()
+        out = hb.decode(reqs)
+        out.synchronize()
+        _ = out.next_tokens_cpu[0].item()
+        step_ms.append((time.perf_counter() - ts) * 1e3)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+
+    # ---- phase C: attention launches timed one by one (eager steps, event pair per launch) ----
+    reset()
+    for _ in range(W + K // 2):
+        hb.decode(reqs)
+    engine.set_profiling(True)
+    hb.decode(reqs).synchronize()  # warm the eager path
+    attn_ms, attn_n, ctx_c = 0.0, 0, []
+    for _ in range(8):
+        ctx_c.append(sum(r.device_len for r in reqs))
+        hb.decode(reqs).synchronize()
+        ms, n, _k = engine.read_profile()
+        attn_ms += ms
+        attn_n += n
+    engine.set_profiling(False)
+
+    if dist is not None:
+        t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+
+    peak, peak_kind = measured_peaks()
+    mean_ctx = [c + (K - 1) / 2 for c in ctx_a]  # context grows by one per step
+    step_bytes, _ = algorithmic_bytes(cfg, mean_ctx)
+    kv_layer_bytes = statistics.mean(ctx_c) * 2 * cfg.num_kv_heads * cfg.head_dim * 2
+    attn_launch_ms = attn_ms / max(attn_n, 1)
+    attn_gbs = kv_layer_bytes / (attn_launch_ms * 1e-3) / 1e9 if attn_launch_ms > 0 else 0.0
+    value = world * BATCH * K / (dev_ms * 1e-3)
+    e2e_value = world * BATCH * K / (e2e_ms * 1e-3)
+    line = {
+        "metric": "decode tokens/s at bs=64 (Qwen3-0.6B, ctx 512-2048 + generated, page 16)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts U[512,2048] seed 2, "
+                               "256-token shared prefix per 4 requests, page size 16, greedy",
+                   "l2": "inputs larger than L2: each step streams ~%.1f GB of KV and 1.19 GB of weights"
+                         % (sum(mean_ctx) * 114688 / 1e9),
+                   "parallelism": "replicas" if world > 1 else "single GPU",
+                   "mean_context": round(statistics.mean(mean_ctx), 1),
+                   "prefix_cache_hit_tokens": hb.prefix_hits},
+        "p50_tpot_ms": round(statistics.median(step_ms), 4),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": (4 * BATCH + 1) * 4, "d2h_bytes_per_step": BATCH * 4,
+                "ms_per_step": round(e2e_ms / K, 4)},
+        "gpu_launches": int(launches_per_step) * K,
+        "roofline": {"bound": "hbm", "kernel": "attention_decode_kernel",
+                     "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(attn_gbs / peak, 4), "peak_kind": peak_kind + " (copy bandwidth)",
+                     "traffic": None, "launch_ms": round(attn_launch_ms, 5),
+                     "algorithmic_bytes_per_launch": int(kv_layer_bytes), "launches_timed": attn_n},
+        "step_roofline": {"algorithmic_bytes_per_step": int(step_bytes),
+                          "achieved_gbs": round(step_bytes / (dev_ms / K * 1e-3) / 1e9, 1),
+                          "frac_of_measured_hbm": round(step_bytes / (dev_ms / K * 1e-3) / 1e9 / peak, 4),
+                          "frac_of_nominal_8tbs": round(step_bytes / (dev_ms / K * 1e-3) / 1e9 / 8000.0, 4)},
+        "prefill": {"tokens": prefill_tokens, "seconds": round(prefill_s, 3),
+                    "tokens_per_s": round(prefill_tokens / prefill_s, 1)},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
+    engine.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------- CPU side
+CPU_SAMPLE_REQS = 8
+
+
+def cpu_decode_sample(steps: int, warmup: int):
+    """Times the CPU oracle (a port: the reference has no CPU forward) on a bounded sample of the
+    workload: the first CPU_SAMPLE_REQS requests of the batch at their real context lengths, KV
+    contents random (the cost does not depend on the values), `steps` decode steps."""
+    from oracle import token_loop_oracle as O
+
+    cfg = O.qwen3_0_6b()
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = O.init_weights(cfg, seed=0, std=0.02)
+    model = O.OracleModel(cfg, w, O.store_bf16)
+    prompts = make_prompts(cfg.vocab_size)[:CPU_SAMPLE_REQS]
+    lens = np.array([len(p) for p in prompts], dtype=np.int32)
+    n_slots = int(lens.sum()) + (steps + warmup + 1) * CPU_SAMPLE_REQS
+    gen = torch.Generator().manual_seed(0)
+    kv = O.KVState(torch.randn(cfg.num_layers, n_slots, cfg.num_kv_heads, cfg.head_dim, generator=gen),
+                   torch.randn(cfg.num_layers, n_slots, cfg.num_kv_heads, cfg.head_dim, generator=gen))
+    cols = int(lens.max()) + steps + warmup + 2
+    pt = np.zeros((CPU_SAMPLE_REQS, cols), dtype=np.int32)
+    cur = 0
+    for b in range(CPU_SAMPLE_REQS):
+        n = int(lens[b]) + steps + warmup + 1
+        pt[b, :n] = np.arange(cur, cur + n)
+        cur += n
+    tok = np.array([int(p[-1]) for p in prompts], dtype=np.int32)
+    times = []
+    for s in range(warmup + steps):
+        pos = lens + s
+        batch = O.StepBatch(tok, pos.astype(np.int32), pt[np.arange(CPU_SAMPLE_REQS), pos].copy(),
+                            np.arange(CPU_SAMPLE_REQS, dtype=np.int32), (pos + 1).astype(np.int32),
+                            np.arange(CPU_SAMPLE_REQS + 1, dtype=np.int32), False)
+        t0 = time.perf_counter()
+        logits = model.forward(batch, kv, pt)
+        tok = logits.argmax(-1).numpy().astype(np.int32)
+        if s >= warmup:
+            times.append(time.perf_counter() - t0)
+    return times, torch.get_num_threads()
+
+
+def cpu_baseline(seconds_budget: float):
+    times, cores = cpu_decode_sample(steps=2, warmup=1)
+    per_step = statistics.mean(times)
+    return {"value": round(CPU_SAMPLE_REQS / per_step, 2), "unit": "tokens/s", "cores": cores,
+            "kind": "port",
+            "sample": f"CPU oracle (torch fp32 restatement; the reference has no CPU forward), first "
+                      f"{CPU_SAMPLE_REQS} of the 64 requests at their real contexts, 2 decode steps after 1 warm-up, "
+                      f"{per_step * 1e3:.0f} ms per step"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 8))
+    warmup = max(1, min(args.warmup, 2))
+    times, cores = cpu_decode_sample(steps, warmup)
+    total = sum(times)
+    value = CPU_SAMPLE_REQS * len(times) / total
+    line = {
+        "impl": "reference",
+        "metric": "decode tokens/s at bs=64 (Qwen3-0.6B, ctx 512-2048 + generated, page 16)",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(times), "warmup": warmup,
+        "ms_per_step": round(total / len(times) * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts U[512,2048] seed 2, "
+                               "256-token shared prefix per 4 requests, page size 16, greedy"},
+        "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"CPU oracle, each step = one decode step of the first {CPU_SAMPLE_REQS} of the 64 "
+                                   f"requests at their real contexts (random KV contents); the reference's own dense "
+                                   f"forward is CUDA-only, so this is a port"},
+        "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

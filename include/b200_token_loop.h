@@ -207,6 +207,117 @@ B200_API int b200_attention_prefill(void* out, const void* q, int64_t q_stride_t
 B200_API int b200_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                          b200_stream_t stream);
 
+/* ---- step runner (include/sglang/engine/engine.h:57-103) -------------------- */
+
+/* The fields of ModelConfig the forward pass reads (include/sglang/models/config.h:15-42). */
+typedef struct b200_model_config {
+    int32_t num_layers;
+    int32_t hidden_size;
+    int32_t num_qo_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;
+    int32_t intermediate_size;
+    int32_t vocab_size;
+    float rms_norm_eps;
+    float rope_theta;
+    int32_t max_position;
+    int32_t tie_word_embeddings;
+    int32_t qk_norm;        /* per-head q/k RMSNorm (Qwen3, Qwen3-MoE) */
+    int32_t fused_residual; /* 1: Qwen3 wiring (src/models/qwen3.cc:21-35); 0: Llama wiring (src/models/llama.cc:15-29) */
+    int32_t attention_bias; /* qkv bias (Qwen2) */
+    int32_t hidden_act;     /* 0 = silu, 1 = gelu */
+    int32_t num_experts;    /* 0 = dense MLP */
+    int32_t num_experts_per_tok;
+    int32_t moe_intermediate_size;
+    int32_t norm_topk_prob;
+} b200_model_config;
+
+/* The fields of EngineConfig that size device state (include/sglang/engine/config.h:13-32). */
+typedef struct b200_engine_config {
+    int32_t page_size;         /* tokens per KV page (the reference Engine runs 1) */
+    int32_t num_pages;         /* usable pages; one more is allocated as the dummy page */
+    int32_t max_running_req;   /* page-table rows; row max_running_req is the dummy request's */
+    int32_t max_seq_len;
+    int32_t max_extend_tokens; /* most tokens one prefill step may carry */
+    int32_t tp_rank;
+    int32_t tp_size;
+} b200_engine_config;
+
+enum { B200_PHASE_PREFILL = 0, B200_PHASE_DECODE = 1 };
+
+/* One scheduler step, as Scheduler::prepare_batch describes it on the host
+ * (src/scheduler/scheduler.cc:275-358): all arrays are HOST memory and are copied
+ * by the call.  Requests [num_reqs, num_padded_reqs) are padding (the dummy
+ * request of GraphRunner::pad_batch, src/engine/engine.cc:628-645). */
+typedef struct b200_step {
+    int32_t phase;
+    int32_t num_reqs;
+    int32_t num_padded_reqs;
+    const int32_t* table_idx;   /* [num_padded_reqs] page-table row (Req::table_idx) */
+    const int32_t* cached_lens; /* [num_padded_reqs] keys already in the pool (Req::cached_len) */
+    const int32_t* extend_lens; /* [num_padded_reqs] tokens run this step (Req::extend_len; 1 in decode) */
+    const int32_t* write_pos;   /* [num_reqs] token-pool column that receives the sampled token, < 0 = none */
+    const float* temperatures;  /* [num_reqs] or NULL = every request greedy (BatchSamplingArgs, engine.h:22-26) */
+    const int32_t* top_k;       /* [num_reqs] or NULL */
+    const float* top_p;         /* [num_reqs] or NULL */
+    const uint64_t* seeds;      /* [num_reqs] or NULL: per-request RNG seed (no counterpart in the reference) */
+    uint64_t step_index;        /* offsets the per-request random stream */
+} b200_step;
+
+typedef struct b200_engine b200_engine;
+
+/* Engine::Engine (src/engine/engine.cc:412-489): allocates weights (uninitialised), the KV
+ * pool [2, L, (num_pages+1)*page_size, kv_heads/tp, head_dim], the page table and token pool
+ * [max_running_req+1, align32(max_seq_len)] (dummy row filled with slot num_pages*page_size),
+ * RoPE tables and activation buffers on the current device. */
+B200_API int b200_engine_create(const b200_model_config* model, const b200_engine_config* config,
+                                b200_engine** out);
+B200_API int b200_engine_destroy(b200_engine* engine);
+
+/* Device address and size of a named tensor: "embed", "lm_head", "final_norm", "rope_cos",
+ * "rope_sin", "page_table", "token_pool", "kv_cache", "logits", "next_tokens", and per layer
+ * "qkv", "qkv_bias", "o", "gate_up", "down", "input_norm", "post_norm", "q_norm", "k_norm",
+ * "router", "experts_gate_up", "experts_down" (layouts: src/models/weight_loader.cc:27-33,455,497). */
+B200_API int b200_engine_tensor(b200_engine* engine, const char* name, int layer, void** device_ptr,
+                                int64_t* nbytes);
+/* Synchronous host-to-device copy into a named tensor (nbytes must equal its size). */
+B200_API int b200_engine_load(b200_engine* engine, const char* name, int layer, const void* host,
+                              int64_t nbytes);
+
+/* CacheManager::write_page_table / the token-pool fill (src/scheduler/prefill.cc:144-187):
+ * table[rows[i], positions[i]] = values[i] from host arrays; which = 0 page table, 1 token pool. */
+B200_API int b200_engine_write_table(b200_engine* engine, int which, const int32_t* rows,
+                                     const int32_t* positions, const int32_t* values, int64_t count);
+
+/* GraphRunner::capture_graphs (src/engine/engine.cc:670-730): captures one CUDA graph per padded
+ * decode batch size; later decode steps whose num_padded_reqs matches replay it. */
+B200_API int b200_engine_capture_graphs(b200_engine* engine, const int32_t* batch_sizes, int count);
+
+/* Engine::forward_batch (src/engine/engine.cc:495-544) together with the device half of
+ * Scheduler::prepare_batch (scheduler.cc:329-334: out_loc / input_ids gathers) and the token
+ * write-back (scheduler.cc:403-412).  Asynchronous: next_tokens_host [num_reqs] (pinned memory
+ * recommended) is valid after b200_engine_synchronize (ForwardOutput::synchronize). */
+B200_API int b200_engine_step(b200_engine* engine, const b200_step* step, int32_t* next_tokens_host);
+B200_API int b200_engine_synchronize(b200_engine* engine);
+
+/* Copies the bf16 logits [rows, vocab] of the last step to host memory (synchronous). */
+B200_API int b200_engine_read_logits(b200_engine* engine, void* host, int rows);
+
+/* The stream the engine enqueues on (Engine::stream_), as a cudaStream_t. */
+B200_API b200_stream_t b200_engine_stream(b200_engine* engine);
+
+/* Measurement aid with no counterpart in the reference (it profiles with steady_clock timers,
+ * src/engine/engine.cc:36-87): while on, steps run eagerly (no graph replay) with a CUDA event
+ * pair around each attention launch.  b200_engine_read_profile synchronises and returns the
+ * summed attention time of the last step, how many attention launches that covers, and the
+ * number of kernels the last step launched (also valid for graph replays, profiling or not). */
+B200_API int b200_engine_set_profiling(b200_engine* engine, int on);
+B200_API int b200_engine_read_profile(b200_engine* engine, float* attention_ms,
+                                      int32_t* attention_launches, int32_t* kernel_launches);
+
+/* Device time of the last step in milliseconds (CUDA events around it); synchronises. */
+B200_API int b200_engine_last_step_ms(b200_engine* engine, float* ms);
+
 #ifdef __cplusplus
 }
 #endif

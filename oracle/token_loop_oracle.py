@@ -342,7 +342,16 @@ class OracleModel:
 
     def __init__(self, cfg: ModelConfig, weights: dict, store: Store = store_bf16):
         self.cfg = cfg
-        self.w = weights
+        # Up-cast the (bf16-rounded) weights to fp32 once; tied tensors stay tied.
+        cache: dict[int, torch.Tensor] = {}
+
+        def up(t):
+            if id(t) not in cache:
+                cache[id(t)] = t.to(f32)
+            return cache[id(t)]
+
+        self.w = {k: (up(v) if torch.is_tensor(v) else v) for k, v in weights.items() if k != "layers"}
+        self.w["layers"] = [{k: up(v) for k, v in L.items()} for L in weights["layers"]]
         self.store = store
         self.cos, self.sin = rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)

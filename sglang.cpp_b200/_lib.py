@@ -62,7 +62,52 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
+    "b200_engine_create": (_I, [_P, _P, POINTER(c_void_p)]),
+    "b200_engine_destroy": (_I, [_P]),
+    "b200_engine_tensor": (_I, [_P, c_char_p, _I, POINTER(c_void_p), POINTER(c_int64)]),
+    "b200_engine_load": (_I, [_P, c_char_p, _I, _P, _L]),
+    "b200_engine_write_table": (_I, [_P, _I, _P, _P, _P, _L]),
+    "b200_engine_capture_graphs": (_I, [_P, _P, _I]),
+    "b200_engine_step": (_I, [_P, _P, _P]),
+    "b200_engine_synchronize": (_I, [_P]),
+    "b200_engine_read_logits": (_I, [_P, _P, _I]),
+    "b200_engine_stream": (c_void_p, [_P]),
+    "b200_engine_last_step_ms": (_I, [_P, POINTER(c_float)]),
+    "b200_engine_set_profiling": (_I, [_P, _I]),
+    "b200_engine_read_profile": (_I, [_P, POINTER(c_float), POINTER(c_int32), POINTER(c_int32)]),
 }
+
+
+class ModelConfigStruct(ctypes.Structure):
+    """b200_model_config."""
+    _fields_ = [
+        ("num_layers", c_int32), ("hidden_size", c_int32), ("num_qo_heads", c_int32),
+        ("num_kv_heads", c_int32), ("head_dim", c_int32), ("intermediate_size", c_int32),
+        ("vocab_size", c_int32), ("rms_norm_eps", c_float), ("rope_theta", c_float),
+        ("max_position", c_int32), ("tie_word_embeddings", c_int32), ("qk_norm", c_int32),
+        ("fused_residual", c_int32), ("attention_bias", c_int32), ("hidden_act", c_int32),
+        ("num_experts", c_int32), ("num_experts_per_tok", c_int32),
+        ("moe_intermediate_size", c_int32), ("norm_topk_prob", c_int32),
+    ]
+
+
+class EngineConfigStruct(ctypes.Structure):
+    """b200_engine_config."""
+    _fields_ = [
+        ("page_size", c_int32), ("num_pages", c_int32), ("max_running_req", c_int32),
+        ("max_seq_len", c_int32), ("max_extend_tokens", c_int32), ("tp_rank", c_int32),
+        ("tp_size", c_int32),
+    ]
+
+
+class StepStruct(ctypes.Structure):
+    """b200_step."""
+    _fields_ = [
+        ("phase", c_int32), ("num_reqs", c_int32), ("num_padded_reqs", c_int32),
+        ("table_idx", c_void_p), ("cached_lens", c_void_p), ("extend_lens", c_void_p),
+        ("write_pos", c_void_p), ("temperatures", c_void_p), ("top_k", c_void_p),
+        ("top_p", c_void_p), ("seeds", c_void_p), ("step_index", ctypes.c_uint64),
+    ]
 
 _lib = None
 

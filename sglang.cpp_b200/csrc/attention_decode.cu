@@ -22,6 +22,7 @@
 //   * every warp writes an (m, l, O) partial; the CTA that finishes a request's
 //     last item merges the partials (threadfence + atomic ticket) and writes bf16.
 #include "common.cuh"
+#include "kernels.h"
 #include "tensormap.cuh"
 
 namespace b200 {

@@ -10,6 +10,7 @@
 // Queries are the LAST extend_len positions of the request, so tiles left of
 // the diagonal need no mask and tiles right of it are never loaded.
 #include "common.cuh"
+#include "kernels.h"
 #include "tensormap.cuh"
 
 namespace b200 {

@@ -1,5 +1,6 @@
 // Gated activations, embedding row gather, and the int32 index-table kernels.
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200 {
 namespace {

@@ -1,0 +1,690 @@
+// Step runner: the device state and per-step driver that stand where the
+// reference's Engine / GraphRunner / model classes do.
+//
+// One object owns the weights (packed exactly as the reference's loader packs
+// them), the KV pool, the page table and token pool, RoPE tables and activation
+// buffers, all from cudaMalloc on the current device.  A step takes the host-side
+// description of a batch (per-request rows and lengths), uploads it in ONE copy
+// from a pinned staging block, derives every per-token quantity on the device,
+// runs the layer stack, selects tokens and writes them back to the token pool.
+// Decode steps replay one CUDA graph per padded batch size.
+#include <math.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+namespace {
+
+static inline int align_ceil(int a, int b) { return (a + b - 1) / b * b; }
+
+// ---- small device kernels that only the step runner needs ----------------------
+
+// Per-token quantities from per-request ones (the host loops of
+// Scheduler::prepare_batch plus its two gathers, moved to the device).
+//   meta layout (int32): table_idx[Bp] | cached[Bp] | qo_indptr[Bp + 1]
+__global__ void prepare_tokens_kernel(const int32_t* __restrict__ meta, int Bp, int T,
+                                      const int32_t* __restrict__ page_table,
+                                      const int32_t* __restrict__ token_pool, int64_t pt_stride,
+                                      int pt_rows, int pt_cols, int32_t* __restrict__ positions,
+                                      int32_t* __restrict__ out_loc, int32_t* __restrict__ input_ids,
+                                      int32_t* __restrict__ seq_lens) {
+    pdl_wait_prior();
+    const int32_t* table_idx = meta;
+    const int32_t* cached = meta + Bp;
+    const int32_t* qo = meta + 2 * Bp;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < Bp) seq_lens[i] = cached[i] + (qo[i + 1] - qo[i]);
+    if (i >= T) return;
+    int lo = 0, hi = Bp;  // request b with qo[b] <= i < qo[b+1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (qo[mid] <= i) lo = mid; else hi = mid;
+    }
+    const int pos = cached[lo] + (i - qo[lo]);
+    const int row = table_idx[lo];
+    const bool ok = row >= 0 && row < pt_rows && pos >= 0 && pos < pt_cols;
+    positions[i] = pos;
+    out_loc[i] = ok ? page_table[row * pt_stride + pos] : 0;
+    input_ids[i] = ok ? token_pool[row * pt_stride + pos] : 0;
+}
+
+// dst[b, :] = src[qo_indptr[b + 1] - 1, :]   (select_lm_head_input, src/models/utils.cc:8-19)
+__global__ void select_last_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                        const int32_t* __restrict__ qo, int vec_per_row) {
+    pdl_wait_prior();
+    const int b = blockIdx.x;
+    const int64_t row = qo[b + 1] - 1;
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x)
+        dst[static_cast<int64_t>(b) * vec_per_row + v] = src[row * vec_per_row + v];
+}
+
+__global__ void scatter_int32_kernel(int32_t* __restrict__ table, int64_t rows, int64_t stride,
+                                     int64_t cols, const int32_t* __restrict__ r,
+                                     const int32_t* __restrict__ p, const int32_t* __restrict__ v,
+                                     int64_t count) {
+    pdl_wait_prior();
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const int64_t rr = r[i], pp = p[i];
+    if (rr < 0 || rr >= rows || pp < 0 || pp >= cols) return;
+    table[rr * stride + pp] = v[i];
+}
+
+__global__ void fill_int32_kernel(int32_t* p, int32_t v, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+struct LayerWeights {
+    __nv_bfloat16 *qkv = nullptr, *qkv_bias = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;
+    __nv_bfloat16 *input_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    __nv_bfloat16 *router = nullptr, *experts_gate_up = nullptr, *experts_down = nullptr;
+    CUtensorMap tmap_k, tmap_v;
+};
+
+struct Tensor {
+    void* ptr;
+    int64_t bytes;
+};
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+struct b200_engine {
+    b200_model_config m;
+    b200_engine_config c;
+    int device = 0;
+    int hq = 0, hkv = 0, inter = 0, qkv_dim = 0;  // per-rank sizes
+    int64_t num_slots = 0;
+    int pt_rows = 0, pt_cols = 0;
+    int max_tokens = 0, max_batch = 0;
+    float sm_scale = 0.f;
+
+    std::vector<void*> allocs;
+    std::map<std::string, Tensor> named;  // "name" or "name.<layer>"
+    std::vector<LayerWeights> layers;
+
+    __nv_bfloat16 *embed = nullptr, *lm_head = nullptr, *final_norm = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    __nv_bfloat16* kv_cache = nullptr;
+    int32_t *page_table = nullptr, *token_pool = nullptr;
+
+    // activations
+    __nv_bfloat16 *x = nullptr, *residual = nullptr, *qkv = nullptr, *attn_out = nullptr, *h = nullptr,
+                  *sel = nullptr, *logits = nullptr;
+    int32_t *positions = nullptr, *out_loc = nullptr, *input_ids = nullptr, *seq_lens = nullptr,
+            *next_tokens = nullptr;
+    void* attn_ws = nullptr;
+    int64_t attn_ws_bytes = 0;
+
+    // per-step metadata: pinned staging + device mirror
+    int32_t* meta_host = nullptr;
+    int32_t* meta_dev = nullptr;
+    int meta_ints = 0;
+    int32_t *scatter_host = nullptr, *scatter_dev = nullptr;
+    int64_t scatter_cap = 0;
+
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_meta_done = nullptr, ev_step_begin = nullptr, ev_step_end = nullptr,
+                ev_scatter_done = nullptr;
+    bool meta_in_flight = false, scatter_in_flight = false;
+    int* status = nullptr;
+
+    std::map<int, cudaGraphExec_t> graphs;  // padded decode batch size -> graph
+    std::map<int, int> graph_launches;      // kernels inside each captured graph
+
+    // Optional per-kernel timing of the attention launches of eager steps.
+    bool profile_attention = false;
+    bool capturing = false;
+    std::vector<cudaEvent_t> prof_events;   // 2 per layer
+    int prof_pairs_recorded = 0;
+    int launches_last_step = 0;
+};
+
+namespace {
+
+int dev_alloc(b200_engine* e, void** out, int64_t bytes, bool zero) {
+    void* p = nullptr;
+    if (bytes <= 0) bytes = 16;
+    B200_CHECK_CUDA(cudaMalloc(&p, static_cast<size_t>(bytes)));
+    e->allocs.push_back(p);
+    if (zero) B200_CHECK_CUDA(cudaMemset(p, 0, static_cast<size_t>(bytes)));
+    *out = p;
+    return B200_OK;
+}
+
+template <typename T>
+int named_alloc(b200_engine* e, T** out, const std::string& name, int64_t elems, bool zero = false) {
+    void* p = nullptr;
+    const int64_t bytes = elems * static_cast<int64_t>(sizeof(T));
+    int err = dev_alloc(e, &p, bytes, zero);
+    if (err != B200_OK) return err;
+    *out = static_cast<T*>(p);
+    e->named[name] = Tensor{p, bytes};
+    return B200_OK;
+}
+
+#define B200_TRY(expr)                  \
+    do {                                \
+        int err__ = (expr);             \
+        if (err__ != B200_OK) return err__; \
+    } while (0)
+
+int build_rope_tables(b200_engine* e) {
+    // cos/sin [max_position, head_dim / 2] in fp32.  Computed here in double and
+    // rounded once; a caller that needs the bit pattern of another generator (the
+    // reference builds them with fp32 torch ops) overwrites "rope_cos"/"rope_sin".
+    const int half = e->m.head_dim / 2;
+    const int64_t n = static_cast<int64_t>(e->m.max_position) * half;
+    std::vector<float> c(n), s(n);
+    std::vector<double> inv(half);
+    for (int j = 0; j < half; ++j)
+        inv[j] = 1.0 / pow(static_cast<double>(e->m.rope_theta), static_cast<double>(2 * j) / e->m.head_dim);
+    for (int64_t t = 0; t < e->m.max_position; ++t)
+        for (int j = 0; j < half; ++j) {
+            const double f = static_cast<double>(t) * inv[j];
+            c[t * half + j] = static_cast<float>(cos(f));
+            s[t * half + j] = static_cast<float>(sin(f));
+        }
+    B200_CHECK_CUDA(cudaMemcpy(e->rope_cos, c.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+    B200_CHECK_CUDA(cudaMemcpy(e->rope_sin, s.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+// The layer stack on `T` tokens of `Bp` requests; everything is enqueued on e->stream.
+int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_extend) {
+    const b200_model_config& m = e->m;
+    cudaStream_t s = e->stream;
+    const int hidden = m.hidden_size, d = m.head_dim;
+    const int32_t* meta_table_idx = e->meta_dev;
+    const int32_t* meta_qo = e->meta_dev + 2 * Bp;
+
+    {
+        const int n = T > Bp ? T : Bp;
+        prepare_tokens_kernel<<<div_ceil(n, 256), 256, 0, s>>>(
+            e->meta_dev, Bp, T, e->page_table, e->token_pool, e->pt_cols, e->pt_rows, e->pt_cols,
+            e->positions, e->out_loc, e->input_ids, e->seq_lens);
+        B200_CHECK_LAUNCH();
+    }
+    B200_TRY(launch_embedding(e->x, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s));
+    B200_CHECK_CUDA(cudaMemsetAsync(e->residual, 0, static_cast<size_t>(T) * hidden * 2, s));
+    const bool round_first = m.fused_residual == 0;
+    const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
+
+    for (int l = 0; l < m.num_layers; ++l) {
+        LayerWeights& L = e->layers[l];
+        B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, L.input_norm, T, hidden, m.rms_norm_eps,
+                                          round_first, s));
+        B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                               B200_EPILOGUE_NONE, e->status, s));
+        __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
+        __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
+        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
+                                          e->positions, e->out_loc, k_cache, v_cache, T, e->hq, e->hkv,
+                                          d, m.max_position, e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        const bool timed = e->profile_attention && !e->capturing;
+        if (timed) {
+            while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
+                cudaEvent_t ev = nullptr;
+                B200_CHECK_CUDA(cudaEventCreate(&ev));
+                e->prof_events.push_back(ev);
+            }
+            B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l], s));
+        }
+        if (phase == B200_PHASE_DECODE) {
+            B200_TRY(launch_attention_decode(e->attn_out, e->qkv, e->qkv_dim, d, L.tmap_k, L.tmap_v,
+                                             e->num_slots, e->page_table, e->pt_cols, meta_table_idx,
+                                             e->seq_lens, Bp, e->hq, e->hkv, e->c.page_size, e->sm_scale,
+                                             e->attn_ws, e->attn_ws_bytes, e->status, s));
+        } else {
+            B200_TRY(launch_attention_prefill(e->attn_out, e->qkv, e->qkv_dim, d, k_cache, v_cache,
+                                              e->num_slots, e->page_table, e->pt_cols, meta_table_idx,
+                                              e->seq_lens, meta_qo, Bp, max_extend, e->hq, e->hkv,
+                                              e->c.page_size, e->sm_scale, e->status, s));
+        }
+        if (timed) {
+            B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
+            e->prof_pairs_recorded = l + 1;
+        }
+        B200_TRY(launch_linear(e->x, e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
+                               B200_EPILOGUE_NONE, e->status, s));
+        B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, L.post_norm, T, hidden, m.rms_norm_eps,
+                                          round_first, s));
+        if (m.num_experts > 0) {
+            set_last_error("engine: MoE layers are not wired into the step runner yet");
+            return B200_ERR_UNSUPPORTED;
+        }
+        B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
+                               e->status, s));
+        B200_TRY(launch_linear(e->x, e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
+                               B200_EPILOGUE_NONE, e->status, s));
+    }
+    B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, e->final_norm, T, hidden, m.rms_norm_eps,
+                                      round_first, s));
+    const __nv_bfloat16* head_in = e->x;
+    if (phase == B200_PHASE_PREFILL) {
+        select_last_rows_kernel<<<Bp, 128, 0, s>>>(reinterpret_cast<uint4*>(e->sel),
+                                                   reinterpret_cast<const uint4*>(e->x), meta_qo,
+                                                   hidden / 8);
+        B200_CHECK_LAUNCH();
+        head_in = e->sel;
+    }
+    B200_TRY(launch_linear(e->logits, head_in, e->lm_head, nullptr, Bp, m.vocab_size, hidden, hidden,
+                           B200_EPILOGUE_NONE, e->status, s));
+    B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s));
+    // Token write-back: token_pool[table_idx[i], write_pos[i]] = next_tokens[i].
+    if (B > 0) {
+        const int32_t* write_pos = e->meta_dev + 3 * Bp + 1;
+        scatter_int32_kernel<<<div_ceil(B, 256), 256, 0, s>>>(e->token_pool, e->pt_rows, e->pt_cols,
+                                                            e->pt_cols, meta_table_idx, write_pos,
+                                                            e->next_tokens, B);
+        B200_CHECK_LAUNCH();
+    }
+    // Kernels launched above: prepare, embedding, per layer 8 (two norms, four GEMMs, the
+    // qk-norm/rope/store pass, attention), final norm, lm_head, argmax, token write-back, plus the
+    // row select in prefill.  A GEMM over more than 256 rows is one launch per 256-row slab.
+    const int slabs = div_ceil(T, 256);
+    e->launches_last_step = 2 + m.num_layers * (4 + 4 * slabs) + 1 + div_ceil(Bp, 256) + 1 +
+                            (B > 0 ? 1 : 0) + (phase == B200_PHASE_PREFILL ? 1 : 0);
+    return B200_OK;
+}
+
+// Fills the pinned staging block for a step; returns T and the longest extend length.
+int stage_step(b200_engine* e, const b200_step* st, int* T_out, int* max_ext_out) {
+    const int Bp = st->num_padded_reqs, B = st->num_reqs;
+    int32_t* mh = e->meta_host;
+    int T = 0, max_ext = 0;
+    for (int i = 0; i < Bp; ++i) {
+        mh[i] = st->table_idx[i];
+        mh[Bp + i] = st->cached_lens[i];
+        mh[2 * Bp + i] = T;
+        const int ext = st->extend_lens[i];
+        if (ext < 0) {
+            set_last_error("step: extend_lens[%d] is negative", i);
+            return B200_ERR_INVALID_ARGUMENT;
+        }
+        if (st->cached_lens[i] < 0 || st->cached_lens[i] + ext > e->pt_cols) {
+            set_last_error("step: request %d needs %d positions, the page table has %d columns", i,
+                           st->cached_lens[i] + ext, e->pt_cols);
+            return B200_ERR_INVALID_ARGUMENT;
+        }
+        T += ext;
+        if (ext > max_ext) max_ext = ext;
+    }
+    mh[3 * Bp] = T;
+    for (int i = 0; i < Bp; ++i) mh[3 * Bp + 1 + i] = (i < B && st->write_pos) ? st->write_pos[i] : -1;
+    *T_out = T;
+    *max_ext_out = max_ext;
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_engine_create(const b200_model_config* model, const b200_engine_config* config,
+                       b200_engine** out) {
+    B200_CHECK_ARG(model && config && out, "engine_create: NULL argument");
+    const b200_model_config& m = *model;
+    const b200_engine_config& c = *config;
+    B200_CHECK_ARG(m.num_layers > 0 && m.hidden_size > 0 && m.vocab_size > 0, "engine_create: bad model size");
+    B200_CHECK_ARG(m.head_dim == 128, "engine_create: head_dim must be 128 (as the reference's attention is)");
+    B200_CHECK_ARG(m.hidden_size % 64 == 0 && m.intermediate_size % 64 == 0,
+                   "engine_create: hidden and intermediate sizes must be multiples of 64");
+    B200_CHECK_ARG(c.tp_size >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "engine_create: bad TP rank/size");
+    B200_CHECK_ARG(m.num_qo_heads % c.tp_size == 0, "num_qo_heads must be divisible by tp_size");
+    B200_CHECK_ARG(m.num_kv_heads % c.tp_size == 0, "num_kv_heads must be divisible by tp_size");
+    B200_CHECK_ARG(m.intermediate_size % (64 * c.tp_size) == 0 || m.num_experts > 0,
+                   "intermediate_size / tp_size must be a multiple of 64");
+    B200_CHECK_ARG(c.page_size >= 1 && (c.page_size & (c.page_size - 1)) == 0,
+                   "engine_create: page_size must be a power of two");
+    B200_CHECK_ARG(c.num_pages >= 1 && c.max_running_req >= 1 && c.max_seq_len >= 1 && c.max_extend_tokens >= 1,
+                   "engine_create: bad engine sizes");
+    const int hkv = m.num_kv_heads / c.tp_size;
+    B200_CHECK_ARG(hkv <= 8 && 8 % hkv == 0, "engine_create: kv heads per rank must be 1, 2, 4 or 8");
+
+    b200_engine* e = new b200_engine();
+    e->m = m;
+    e->c = c;
+    B200_CHECK_CUDA(cudaGetDevice(&e->device));
+    e->hq = m.num_qo_heads / c.tp_size;
+    e->hkv = hkv;
+    e->inter = m.intermediate_size / c.tp_size;
+    e->qkv_dim = (e->hq + 2 * e->hkv) * m.head_dim;
+    e->num_slots = static_cast<int64_t>(c.num_pages + 1) * c.page_size;
+    e->pt_rows = c.max_running_req + 1;
+    e->pt_cols = align_ceil(c.max_seq_len, 32);
+    e->max_batch = c.max_running_req + 1;
+    e->max_tokens = c.max_extend_tokens > e->max_batch ? c.max_extend_tokens : e->max_batch;
+    e->sm_scale = 1.0f / sqrtf(static_cast<float>(m.head_dim));
+    int err = B200_OK;
+    e->status = device_status_words(&err);
+    if (err != B200_OK) { delete e; return err; }
+
+    auto fail = [&](int code) { b200_engine_destroy(e); return code; };
+#define E_TRY(expr) do { int c__ = (expr); if (c__ != B200_OK) return fail(c__); } while (0)
+
+    const int64_t H = m.hidden_size, D = m.head_dim;
+    E_TRY(named_alloc(e, &e->embed, "embed", static_cast<int64_t>(m.vocab_size) * H));
+    if (m.tie_word_embeddings) {
+        e->lm_head = e->embed;
+        e->named["lm_head"] = e->named["embed"];
+    } else {
+        E_TRY(named_alloc(e, &e->lm_head, "lm_head", static_cast<int64_t>(m.vocab_size) * H));
+    }
+    E_TRY(named_alloc(e, &e->final_norm, "final_norm", H));
+    E_TRY(named_alloc(e, &e->rope_cos, "rope_cos", static_cast<int64_t>(m.max_position) * (D / 2)));
+    E_TRY(named_alloc(e, &e->rope_sin, "rope_sin", static_cast<int64_t>(m.max_position) * (D / 2)));
+    E_TRY(build_rope_tables(e));
+    E_TRY(named_alloc(e, &e->kv_cache, "kv_cache", 2 * static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * D, true));
+    E_TRY(named_alloc(e, &e->page_table, "page_table", static_cast<int64_t>(e->pt_rows) * e->pt_cols, true));
+    E_TRY(named_alloc(e, &e->token_pool, "token_pool", static_cast<int64_t>(e->pt_rows) * e->pt_cols, true));
+    {
+        // Dummy request: row max_running_req points every position at the extra page.
+        int32_t* row = e->page_table + static_cast<int64_t>(c.max_running_req) * e->pt_cols;
+        fill_int32_kernel<<<div_ceil(e->pt_cols, 256), 256>>>(row, c.num_pages * c.page_size, e->pt_cols);
+        if (cudaGetLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+            set_last_error("engine_create: initialising the dummy page-table row failed");
+            return fail(B200_ERR_CUDA);
+        }
+    }
+    e->layers.resize(m.num_layers);
+    for (int l = 0; l < m.num_layers; ++l) {
+        LayerWeights& L = e->layers[l];
+        const std::string sfx = "." + std::to_string(l);
+        E_TRY(named_alloc(e, &L.qkv, "qkv" + sfx, static_cast<int64_t>(e->qkv_dim) * H));
+        if (m.attention_bias) E_TRY(named_alloc(e, &L.qkv_bias, "qkv_bias" + sfx, e->qkv_dim));
+        E_TRY(named_alloc(e, &L.o, "o" + sfx, H * e->hq * D));
+        E_TRY(named_alloc(e, &L.input_norm, "input_norm" + sfx, H));
+        E_TRY(named_alloc(e, &L.post_norm, "post_norm" + sfx, H));
+        if (m.qk_norm) {
+            E_TRY(named_alloc(e, &L.q_norm, "q_norm" + sfx, D));
+            E_TRY(named_alloc(e, &L.k_norm, "k_norm" + sfx, D));
+        }
+        if (m.num_experts > 0) {
+            const int64_t ie = m.moe_intermediate_size / c.tp_size;
+            E_TRY(named_alloc(e, &L.router, "router" + sfx, static_cast<int64_t>(m.num_experts) * H));
+            E_TRY(named_alloc(e, &L.experts_gate_up, "experts_gate_up" + sfx, static_cast<int64_t>(m.num_experts) * 2 * ie * H));
+            E_TRY(named_alloc(e, &L.experts_down, "experts_down" + sfx, static_cast<int64_t>(m.num_experts) * H * ie));
+        } else {
+            E_TRY(named_alloc(e, &L.gate_up, "gate_up" + sfx, 2 * static_cast<int64_t>(e->inter) * H));
+            E_TRY(named_alloc(e, &L.down, "down" + sfx, H * e->inter));
+        }
+        const __nv_bfloat16* kc = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * D;
+        const __nv_bfloat16* vc = kc + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * D;
+        E_TRY(make_kv_tmap(&L.tmap_k, kc, e->num_slots, e->hkv, c.page_size));
+        E_TRY(make_kv_tmap(&L.tmap_v, vc, e->num_slots, e->hkv, c.page_size));
+    }
+    const int64_t Tm = e->max_tokens;
+    const int64_t inter_buf = m.num_experts > 0 ? m.moe_intermediate_size : e->inter;
+    E_TRY(named_alloc(e, &e->x, "x", Tm * H));
+    E_TRY(named_alloc(e, &e->residual, "residual", Tm * H));
+    E_TRY(named_alloc(e, &e->qkv, "qkv_act", Tm * e->qkv_dim));
+    E_TRY(named_alloc(e, &e->attn_out, "attn_out", Tm * e->hq * D));
+    E_TRY(named_alloc(e, &e->h, "mlp_act", Tm * inter_buf));
+    E_TRY(named_alloc(e, &e->sel, "sel", static_cast<int64_t>(e->max_batch) * H));
+    E_TRY(named_alloc(e, &e->logits, "logits", static_cast<int64_t>(e->max_batch) * m.vocab_size));
+    E_TRY(named_alloc(e, &e->positions, "positions", Tm));
+    E_TRY(named_alloc(e, &e->out_loc, "out_loc", Tm));
+    E_TRY(named_alloc(e, &e->input_ids, "input_ids", Tm));
+    E_TRY(named_alloc(e, &e->seq_lens, "seq_lens", e->max_batch));
+    E_TRY(named_alloc(e, &e->next_tokens, "next_tokens", e->max_batch, true));
+    e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);
+    E_TRY(dev_alloc(e, &e->attn_ws, e->attn_ws_bytes, true));
+
+    e->meta_ints = 4 * e->max_batch + 8;
+    if (cudaMallocHost(&e->meta_host, e->meta_ints * sizeof(int32_t)) != cudaSuccess) {
+        set_last_error("engine_create: pinned staging allocation failed");
+        return fail(B200_ERR_CUDA);
+    }
+    E_TRY(named_alloc(e, &e->meta_dev, "step_meta", e->meta_ints, true));
+    if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->ev_meta_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->ev_scatter_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreate(&e->ev_step_begin) != cudaSuccess || cudaEventCreate(&e->ev_step_end) != cudaSuccess) {
+        set_last_error("engine_create: stream / event creation failed");
+        return fail(B200_ERR_CUDA);
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        set_last_error("engine_create: device error during initialisation");
+        return fail(B200_ERR_CUDA);
+    }
+#undef E_TRY
+    *out = e;
+    return B200_OK;
+}
+
+int b200_engine_destroy(b200_engine* e) {
+    if (!e) return B200_OK;
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
+    for (void* p : e->allocs) cudaFree(p);
+    if (e->meta_host) cudaFreeHost(e->meta_host);
+    if (e->scatter_host) cudaFreeHost(e->scatter_host);
+    if (e->ev_meta_done) cudaEventDestroy(e->ev_meta_done);
+    if (e->ev_scatter_done) cudaEventDestroy(e->ev_scatter_done);
+    if (e->ev_step_begin) cudaEventDestroy(e->ev_step_begin);
+    if (e->ev_step_end) cudaEventDestroy(e->ev_step_end);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return B200_OK;
+}
+
+int b200_engine_tensor(b200_engine* e, const char* name, int layer, void** device_ptr, int64_t* nbytes) {
+    B200_CHECK_ARG(e && name, "engine_tensor: NULL argument");
+    std::string key(name);
+    auto it = e->named.find(key);
+    if (it == e->named.end()) it = e->named.find(key + "." + std::to_string(layer));
+    if (it == e->named.end()) {
+        set_last_error("engine_tensor: no tensor named '%s' (layer %d)", name, layer);
+        return B200_ERR_INVALID_ARGUMENT;
+    }
+    if (device_ptr) *device_ptr = it->second.ptr;
+    if (nbytes) *nbytes = it->second.bytes;
+    return B200_OK;
+}
+
+int b200_engine_load(b200_engine* e, const char* name, int layer, const void* host, int64_t nbytes) {
+    B200_CHECK_ARG(host, "engine_load: host pointer is NULL");
+    void* p = nullptr;
+    int64_t bytes = 0;
+    int err = b200_engine_tensor(e, name, layer, &p, &bytes);
+    if (err != B200_OK) return err;
+    B200_CHECK_ARG(bytes == nbytes, "engine_load: '%s' holds %lld bytes, got %lld", name,
+                   static_cast<long long>(bytes), static_cast<long long>(nbytes));
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    B200_CHECK_CUDA(cudaMemcpy(p, host, static_cast<size_t>(nbytes), cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+int b200_engine_write_table(b200_engine* e, int which, const int32_t* rows, const int32_t* positions,
+                            const int32_t* values, int64_t count) {
+    B200_CHECK_ARG(e, "engine_write_table: NULL engine");
+    B200_CHECK_ARG(which == 0 || which == 1, "engine_write_table: which must be 0 (page table) or 1 (token pool)");
+    B200_CHECK_ARG(count >= 0, "engine_write_table: negative count");
+    if (count == 0) return B200_OK;
+    B200_CHECK_ARG(rows && positions && values, "engine_write_table: NULL array");
+    if (e->scatter_in_flight) {
+        B200_CHECK_CUDA(cudaEventSynchronize(e->ev_scatter_done));
+        e->scatter_in_flight = false;
+    }
+    if (count > e->scatter_cap) {
+        int64_t cap = 1024;
+        while (cap < count) cap <<= 1;
+        if (e->scatter_host) cudaFreeHost(e->scatter_host);
+        e->scatter_host = nullptr;
+        B200_CHECK_CUDA(cudaMallocHost(&e->scatter_host, 3 * cap * sizeof(int32_t)));
+        void* d = nullptr;
+        B200_TRY(dev_alloc(e, &d, 3 * cap * sizeof(int32_t), false));
+        e->scatter_dev = static_cast<int32_t*>(d);
+        e->scatter_cap = cap;
+    }
+    memcpy(e->scatter_host, rows, count * sizeof(int32_t));
+    memcpy(e->scatter_host + count, positions, count * sizeof(int32_t));
+    memcpy(e->scatter_host + 2 * count, values, count * sizeof(int32_t));
+    B200_CHECK_CUDA(cudaMemcpyAsync(e->scatter_dev, e->scatter_host, 3 * count * sizeof(int32_t),
+                                    cudaMemcpyHostToDevice, e->stream));
+    B200_CHECK_CUDA(cudaEventRecord(e->ev_scatter_done, e->stream));
+    e->scatter_in_flight = true;
+    int32_t* table = which == 0 ? e->page_table : e->token_pool;
+    scatter_int32_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, e->stream>>>(
+        table, e->pt_rows, e->pt_cols, e->pt_cols, e->scatter_dev, e->scatter_dev + count,
+        e->scatter_dev + 2 * count, count);
+    B200_CHECK_LAUNCH();
+    return B200_OK;
+}
+
+int b200_engine_capture_graphs(b200_engine* e, const int32_t* batch_sizes, int count) {
+    B200_CHECK_ARG(e && (count == 0 || batch_sizes), "engine_capture_graphs: NULL argument");
+    for (int i = 0; i < count; ++i) {
+        const int Bp = batch_sizes[i];
+        B200_CHECK_ARG(Bp >= 1 && Bp <= e->max_batch, "engine_capture_graphs: batch size %d out of range", Bp);
+        if (e->graphs.count(Bp)) continue;
+        // Warm-up + capture run on the dummy request only (GraphRunner::capture_graphs does the
+        // same): every row is the dummy row, one key each, nothing is written back.
+        B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+        int32_t* mh = e->meta_host;
+        for (int j = 0; j < Bp; ++j) {
+            mh[j] = e->c.max_running_req;
+            mh[Bp + j] = 0;
+            mh[2 * Bp + j] = j;
+        }
+        mh[3 * Bp] = Bp;
+        for (int j = 0; j < Bp; ++j) mh[3 * Bp + 1 + j] = -1;
+        B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, mh, (4 * Bp + 1) * sizeof(int32_t),
+                                        cudaMemcpyHostToDevice, e->stream));
+        B200_TRY(enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1));  // eager warm-up
+        B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+        cudaGraph_t graph = nullptr;
+        B200_CHECK_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        e->capturing = true;
+        int err = enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1);
+        e->capturing = false;
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+        if (err != B200_OK) {
+            if (graph) cudaGraphDestroy(graph);
+            return err;
+        }
+        B200_CHECK_CUDA(ce);
+        cudaGraphExec_t exec = nullptr;
+        ce = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        B200_CHECK_CUDA(ce);
+        e->graphs[Bp] = exec;
+        e->graph_launches[Bp] = e->launches_last_step;
+    }
+    return B200_OK;
+}
+
+int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_host) {
+    B200_CHECK_ARG(e && st, "engine_step: NULL argument");
+    B200_CHECK_ARG(st->phase == B200_PHASE_PREFILL || st->phase == B200_PHASE_DECODE, "engine_step: bad phase");
+    const int B = st->num_reqs, Bp = st->num_padded_reqs;
+    B200_CHECK_ARG(B >= 0 && Bp >= B && Bp <= e->max_batch, "engine_step: batch size out of range");
+    if (Bp == 0) return B200_OK;
+    B200_CHECK_ARG(st->table_idx && st->cached_lens && st->extend_lens, "engine_step: NULL request arrays");
+    if (st->temperatures != nullptr) {
+        set_last_error("engine_step: stochastic sampling is not wired into the step runner yet");
+        return B200_ERR_UNSUPPORTED;
+    }
+    if (e->meta_in_flight) {  // the staging block of the previous step must have been consumed
+        B200_CHECK_CUDA(cudaEventSynchronize(e->ev_meta_done));
+        e->meta_in_flight = false;
+    }
+    int T = 0, max_ext = 0;
+    B200_TRY(stage_step(e, st, &T, &max_ext));
+    B200_CHECK_ARG(T <= e->max_tokens, "engine_step: %d tokens exceed max_extend_tokens %d", T, e->max_tokens);
+    if (st->phase == B200_PHASE_DECODE)
+        B200_CHECK_ARG(T == Bp, "engine_step: a decode step runs exactly one token per request");
+
+    cudaStream_t s = e->stream;
+    B200_CHECK_CUDA(cudaEventRecord(e->ev_step_begin, s));
+    B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, (4 * Bp + 1) * sizeof(int32_t),
+                                    cudaMemcpyHostToDevice, s));
+    B200_CHECK_CUDA(cudaEventRecord(e->ev_meta_done, s));
+    e->meta_in_flight = true;
+    // A captured graph covers all Bp rows; padded rows carry write_pos = -1 so nothing of
+    // theirs is written back, and only the first B tokens are copied out.
+    auto g = st->phase == B200_PHASE_DECODE ? e->graphs.find(Bp) : e->graphs.end();
+    if (g != e->graphs.end() && !e->profile_attention) {
+        B200_CHECK_CUDA(cudaGraphLaunch(g->second, s));
+        e->launches_last_step = e->graph_launches[Bp];
+    } else {
+        B200_TRY(enqueue_forward(e, st->phase, B, Bp, T, max_ext));
+    }
+    if (next_tokens_host && B > 0)
+        B200_CHECK_CUDA(cudaMemcpyAsync(next_tokens_host, e->next_tokens, B * sizeof(int32_t),
+                                        cudaMemcpyDeviceToHost, s));
+    B200_CHECK_CUDA(cudaEventRecord(e->ev_step_end, s));
+    return B200_OK;
+}
+
+int b200_engine_synchronize(b200_engine* e) {
+    B200_CHECK_ARG(e, "engine_synchronize: NULL engine");
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    int host[2] = {0, 0};
+    B200_CHECK_CUDA(cudaMemcpy(host, e->status, sizeof(host), cudaMemcpyDeviceToHost));
+    if (host[0] != 0) {
+        cudaMemset(e->status, 0, sizeof(host));
+        set_last_error("a bounded wait inside a kernel ran out (site %d)", host[0]);
+        return B200_ERR_TIMEOUT;
+    }
+    if (host[1] != 0) {
+        cudaMemset(e->status, 0, sizeof(host));
+        set_last_error("a kernel saw an out-of-range index (%d)", host[1] - 1);
+        return B200_ERR_INVALID_ARGUMENT;
+    }
+    return B200_OK;
+}
+
+int b200_engine_read_logits(b200_engine* e, void* host, int rows) {
+    B200_CHECK_ARG(e && host, "engine_read_logits: NULL argument");
+    B200_CHECK_ARG(rows >= 0 && rows <= e->max_batch, "engine_read_logits: rows out of range");
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    B200_CHECK_CUDA(cudaMemcpy(host, e->logits, static_cast<size_t>(rows) * e->m.vocab_size * 2,
+                               cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+b200_stream_t b200_engine_stream(b200_engine* e) { return e ? e->stream : nullptr; }
+
+int b200_engine_set_profiling(b200_engine* e, int on) {
+    B200_CHECK_ARG(e, "engine_set_profiling: NULL engine");
+    e->profile_attention = on != 0;
+    e->prof_pairs_recorded = 0;
+    return B200_OK;
+}
+
+int b200_engine_read_profile(b200_engine* e, float* attention_ms, int32_t* attention_launches,
+                             int32_t* kernel_launches) {
+    B200_CHECK_ARG(e, "engine_read_profile: NULL engine");
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    float total = 0.f;
+    for (int i = 0; i < e->prof_pairs_recorded; ++i) {
+        float ms = 0.f;
+        B200_CHECK_CUDA(cudaEventElapsedTime(&ms, e->prof_events[2 * i], e->prof_events[2 * i + 1]));
+        total += ms;
+    }
+    if (attention_ms) *attention_ms = total;
+    if (attention_launches) *attention_launches = e->prof_pairs_recorded;
+    if (kernel_launches) *kernel_launches = e->launches_last_step;
+    return B200_OK;
+}
+
+int b200_engine_last_step_ms(b200_engine* e, float* ms) {
+    B200_CHECK_ARG(e && ms, "engine_last_step_ms: NULL argument");
+    B200_CHECK_CUDA(cudaEventSynchronize(e->ev_step_end));
+    B200_CHECK_CUDA(cudaEventElapsedTime(ms, e->ev_step_begin, e->ev_step_end));
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -21,6 +21,7 @@
 // operand, one fed by a gate-row tile of W and one by the matching up-row tile,
 // so a thread holds gate[n][m] and up[n][m] for the same (n, m).
 #include "common.cuh"
+#include "kernels.h"
 #include "tensormap.cuh"
 
 namespace b200 {
@@ -480,6 +481,21 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     return B200_OK;
 }
 
+int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
+                  int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
+    const int n_out = epilogue != B200_EPILOGUE_NONE ? N / 2 : N;
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+    for (int m0 = 0; m0 < M; m0 += 256) {
+        const int rows = (M - m0) < 256 ? (M - m0) : 256;
+        int err = launch_skinny_gemm(yp + static_cast<int64_t>(m0) * n_out,
+                                     xp + static_cast<int64_t>(m0) * ldx, w, bias, rows, N, K, ldx,
+                                     epilogue, status, stream);
+        if (err != B200_OK) return err;
+    }
+    return B200_OK;
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -500,17 +516,8 @@ int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, 
     int err = B200_OK;
     int* status = b200::device_status_words(&err);
     if (err != B200_OK) return err;
-    const int n_out = gated ? N / 2 : N;
-    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
-    __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
-    for (int m0 = 0; m0 < M; m0 += 256) {
-        const int rows = (M - m0) < 256 ? (M - m0) : 256;
-        err = b200::launch_skinny_gemm(yp + static_cast<int64_t>(m0) * n_out,
-                                       xp + static_cast<int64_t>(m0) * ldx, w, bias, rows, N, K, ldx,
-                                       epilogue, status, static_cast<cudaStream_t>(stream));
-        if (err != B200_OK) return err;
-    }
-    return B200_OK;
+    return b200::launch_linear(y, x, w, bias, M, N, K, ldx, epilogue, status,
+                               static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,48 @@
+// Internal launch interface shared by the C-ABI wrappers and the step runner.
+// Every function enqueues work on `stream` and returns a B200_* status.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+int launch_rmsnorm(void* out, const void* x, const void* weight, int rows, int hidden, float eps,
+                   cudaStream_t stream);
+// round_sum_first: normalise the bf16-rounded sum (separate add then norm, as the Llama wiring
+// does) instead of the fp32 sum (the fused FlashInfer form the Qwen3 wiring uses).
+int launch_fused_add_rmsnorm(void* x, void* residual, const void* weight, int rows, int hidden,
+                             float eps, bool round_sum_first, cudaStream_t stream);
+int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weight,
+                             const float* cos_table, const float* sin_table,
+                             const int32_t* positions, const int32_t* out_loc, void* k_cache,
+                             void* v_cache, int tokens, int q_heads, int kv_heads, int head_dim,
+                             int max_pos, int64_t num_slots, float eps, int write_k_back,
+                             int* status, cudaStream_t stream);
+int launch_act_and_mul(void* out, const void* in, int tokens, int d, bool gelu, cudaStream_t stream);
+int launch_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
+                     int vocab, int* status, cudaStream_t stream);
+int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
+                  cudaStream_t stream);
+
+// y[M, n_out] = x[M, K] w[N, K]^T (+bias / gated epilogue); any M (slabs of 256 rows).
+int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
+                  int64_t ldx, int epilogue, int* status, cudaStream_t stream);
+
+int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
+int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);
+int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,
+                            const CUtensorMap& tmap_k, const CUtensorMap& tmap_v, int64_t num_slots,
+                            const int32_t* page_table, int64_t pt_stride, const int32_t* table_idx,
+                            const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
+                            int page_size, float sm_scale, void* workspace, int64_t workspace_bytes,
+                            int* status, cudaStream_t stream);
+int launch_attention_prefill(void* out, const void* q, int64_t q_st, int64_t q_sh, const void* k_cache,
+                             const void* v_cache, int64_t num_slots, const int32_t* page_table,
+                             int64_t pt_stride, const int32_t* table_idx, const int32_t* seq_lens,
+                             const int32_t* qo_indptr, int batch, int max_extend_len, int q_heads,
+                             int kv_heads, int page_size, float sm_scale, int* status,
+                             cudaStream_t stream);
+
+}  // namespace b200

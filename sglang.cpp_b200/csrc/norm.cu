@@ -5,6 +5,7 @@
 // so every element is read once, warp-shuffle + one shared-memory hop for the
 // block reduction, fp32 arithmetic, bf16 storage.
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200 {
 namespace {
@@ -24,7 +25,7 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 
 // One CTA per row.  FUSED_ADD: residual <- x + residual; x <- norm(sum) * w.
 // Otherwise out <- norm(x) * w.  hidden % 8 == 0.
-template <bool FUSED_ADD>
+template <bool FUSED_ADD, bool ROUND_FIRST>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__nv_bfloat16* out, const __nv_bfloat16* x_in,
                __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ weight, int hidden,
@@ -55,9 +56,9 @@ rmsnorm_kernel(__nv_bfloat16* out, const __nv_bfloat16* x_in,
                 for (int j = 0; j < 4; ++j) {
                     const float lo = bf16_lo(aw[j]) + bf16_lo(rw[j]);
                     const float hi = bf16_hi(aw[j]) + bf16_hi(rw[j]);
-                    vals[i][2 * j] = lo;
-                    vals[i][2 * j + 1] = hi;
                     packed[j] = pack_bf16(lo, hi);
+                    vals[i][2 * j] = ROUND_FIRST ? bf16_lo(packed[j]) : lo;
+                    vals[i][2 * j + 1] = ROUND_FIRST ? bf16_hi(packed[j]) : hi;
                 }
                 rv[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             } else {
@@ -85,6 +86,10 @@ rmsnorm_kernel(__nv_bfloat16* out, const __nv_bfloat16* x_in,
                 f[2 * j] = bf16_lo(aw[j]) + bf16_lo(rw[j]);
                 f[2 * j + 1] = bf16_hi(aw[j]) + bf16_hi(rw[j]);
                 packed[j] = pack_bf16(f[2 * j], f[2 * j + 1]);
+                if (ROUND_FIRST) {
+                    f[2 * j] = bf16_lo(packed[j]);
+                    f[2 * j + 1] = bf16_hi(packed[j]);
+                }
             }
             rv[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         } else {
@@ -183,7 +188,7 @@ int launch_rmsnorm(void* out, const void* x, const void* weight, int rows, int h
                    cudaStream_t stream) {
     if (rows == 0) return B200_OK;
     const int threads = hidden >= 2048 ? 256 : 128;
-    rmsnorm_kernel<false><<<rows, threads, 0, stream>>>(
+    rmsnorm_kernel<false, false><<<rows, threads, 0, stream>>>(
         static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x), nullptr,
         static_cast<const __nv_bfloat16*>(weight), hidden, eps);
     B200_CHECK_LAUNCH();
@@ -191,10 +196,11 @@ int launch_rmsnorm(void* out, const void* x, const void* weight, int rows, int h
 }
 
 int launch_fused_add_rmsnorm(void* x, void* residual, const void* weight, int rows, int hidden,
-                             float eps, cudaStream_t stream) {
+                             float eps, bool round_sum_first, cudaStream_t stream) {
     if (rows == 0) return B200_OK;
     const int threads = hidden >= 2048 ? 256 : 128;
-    rmsnorm_kernel<true><<<rows, threads, 0, stream>>>(
+    auto kernel = round_sum_first ? rmsnorm_kernel<true, true> : rmsnorm_kernel<true, false>;
+    kernel<<<rows, threads, 0, stream>>>(
         static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(x),
         static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(weight), hidden,
         eps);
@@ -221,7 +227,7 @@ int b200_fused_add_rmsnorm(void* x, void* residual, const void* weight, int rows
     B200_CHECK_ARG(rows == 0 || (x && residual && weight), "fused_add_rmsnorm: NULL tensor");
     B200_CHECK_ARG(hidden > 0, "RMSNorm last dimension must be positive");
     B200_CHECK_ARG(hidden % 8 == 0, "fused_add_rmsnorm: hidden must be a multiple of 8");
-    return b200::launch_fused_add_rmsnorm(x, residual, weight, rows, hidden, eps,
+    return b200::launch_fused_add_rmsnorm(x, residual, weight, rows, hidden, eps, false,
                                           static_cast<cudaStream_t>(stream));
 }
 

@@ -4,6 +4,7 @@
 // (token, head) row; a lane holds the two halves of its NeoX pairs so the
 // rotation needs no shuffles, and the norm needs one 5-step shuffle reduction.
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200 {
 namespace {

@@ -1,6 +1,7 @@
 // Token selection from logits: greedy argmax and the single-pass
 // temperature / top-k / top-p sampler.
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200 {
 namespace {

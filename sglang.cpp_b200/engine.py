@@ -1,0 +1,217 @@
+"""Host-side mirror of sglang.cpp's ``Engine`` for the per-step path, over the C ABI.
+
+``Engine`` here keeps the reference's method names where one exists
+(``forward_batch``, ``page_table``; include/sglang/engine/engine.h:57-103) and
+otherwise exposes what the scheduler does either side of the forward pass
+(page-table / token-pool writes).  All device state lives in the C++ step runner
+(``csrc/engine.cu``); this file only marshals host arrays into the C structs.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import B200Error, EngineConfigStruct, ModelConfigStruct, StepStruct, call
+
+PHASE_PREFILL = 0
+PHASE_DECODE = 1
+
+
+@dataclass
+class EngineConfig:
+    """The sizing fields of include/sglang/engine/config.h:13-32."""
+    page_size: int = 1
+    num_pages: int = 1024
+    max_running_req: int = 64
+    max_seq_len: int = 4096
+    max_extend_tokens: int = 8192
+    tp_rank: int = 0
+    tp_size: int = 1
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int32))
+
+
+class ForwardOutput:
+    """include/sglang/engine/engine.h:28-34: tokens on the host after ``synchronize()``."""
+
+    def __init__(self, engine: "Engine", next_tokens_cpu: torch.Tensor, num_reqs: int):
+        self._engine = engine
+        self.next_tokens_cpu = next_tokens_cpu[:num_reqs]
+
+    def synchronize(self) -> None:
+        self._engine.synchronize()
+
+
+class Engine:
+    def __init__(self, model_config, config: EngineConfig):
+        """model_config: any object with the fields of oracle.token_loop_oracle.ModelConfig
+        (the forward-pass subset of include/sglang/models/config.h:15-42)."""
+        self.model_config = model_config
+        self.config = config
+        m = ModelConfigStruct(
+            model_config.num_layers, model_config.hidden_size, model_config.num_qo_heads,
+            model_config.num_kv_heads, model_config.head_dim, model_config.intermediate_size,
+            model_config.vocab_size, model_config.rms_norm_eps, model_config.rope_theta,
+            model_config.max_position, int(model_config.tie_word_embeddings), int(model_config.qk_norm),
+            int(model_config.fused_residual), int(model_config.attention_bias),
+            1 if model_config.hidden_act == "gelu" else 0, model_config.num_experts,
+            model_config.num_experts_per_tok, model_config.moe_intermediate_size,
+            int(model_config.norm_topk_prob))
+        c = EngineConfigStruct(config.page_size, config.num_pages, config.max_running_req,
+                               config.max_seq_len, config.max_extend_tokens, config.tp_rank,
+                               config.tp_size)
+        self._h = ctypes.c_void_p()
+        call("b200_engine_create", ctypes.byref(m), ctypes.byref(c), ctypes.byref(self._h))
+        self._next_tokens_cpu = torch.empty(config.max_running_req + 1, dtype=torch.int32).pin_memory()
+        self.page_size = config.page_size
+        self.dummy_table_idx = config.max_running_req
+        self._step_index = 0
+
+    def close(self) -> None:
+        if self._h:
+            call("b200_engine_destroy", self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ tensors
+    def tensor_info(self, name: str, layer: int = 0) -> tuple[int, int]:
+        ptr, n = ctypes.c_void_p(), ctypes.c_int64()
+        call("b200_engine_tensor", self._h, name.encode(), layer, ctypes.byref(ptr), ctypes.byref(n))
+        return int(ptr.value), int(n.value)
+
+    def load(self, name: str, layer: int, host: torch.Tensor) -> None:
+        host = host.contiguous()
+        call("b200_engine_load", self._h, name.encode(), layer, host.data_ptr(),
+             host.numel() * host.element_size())
+
+    def load_weights(self, w: dict, tp_rank: int = 0, tp_size: int = 1) -> None:
+        """Upload weights given in the reference's packed layouts (full, unsharded tensors as
+        oracle.init_weights makes them), applying the reference's TP shard rules
+        (src/models/weight_loader.cc:284-353) for this rank."""
+        cfg = self.model_config
+        d = cfg.head_dim
+        hq, hkv = cfg.num_qo_heads // tp_size, cfg.num_kv_heads // tp_size
+        self.load("embed", 0, w["embed"])
+        if not cfg.tie_word_embeddings:
+            self.load("lm_head", 0, w["lm_head"])
+        self.load("final_norm", 0, w["final_norm"])
+        for l, L in enumerate(w["layers"]):
+            qd, kd = cfg.num_qo_heads * d, cfg.num_kv_heads * d
+            q, k, v = L["qkv"][:qd], L["qkv"][qd:qd + kd], L["qkv"][qd + kd:]
+            shard = lambda t, n: t[tp_rank * n:(tp_rank + 1) * n]
+            self.load("qkv", l, torch.cat([shard(q, hq * d), shard(k, hkv * d), shard(v, hkv * d)], 0))
+            if cfg.attention_bias:
+                b = L["qkv_bias"]
+                self.load("qkv_bias", l, torch.cat([shard(b[:qd], hq * d), shard(b[qd:qd + kd], hkv * d),
+                                                     shard(b[qd + kd:], hkv * d)], 0))
+            self.load("o", l, L["o"][:, tp_rank * hq * d:(tp_rank + 1) * hq * d])
+            self.load("input_norm", l, L["input_norm"])
+            self.load("post_norm", l, L["post_norm"])
+            if cfg.qk_norm:
+                self.load("q_norm", l, L["q_norm"])
+                self.load("k_norm", l, L["k_norm"])
+            if cfg.num_experts > 0:
+                ie = cfg.moe_intermediate_size
+                il = ie // tp_size
+                gu = L["experts_gate_up"]
+                self.load("router", l, L["router"])
+                self.load("experts_gate_up", l, torch.cat([gu[:, tp_rank * il:(tp_rank + 1) * il],
+                                                            gu[:, ie + tp_rank * il:ie + (tp_rank + 1) * il]], 1))
+                self.load("experts_down", l, L["experts_down"][:, :, tp_rank * il:(tp_rank + 1) * il])
+            else:
+                I = cfg.intermediate_size
+                il = I // tp_size
+                gu = L["gate_up"]
+                self.load("gate_up", l, torch.cat([gu[tp_rank * il:(tp_rank + 1) * il],
+                                                   gu[I + tp_rank * il:I + (tp_rank + 1) * il]], 0))
+                self.load("down", l, L["down"][:, tp_rank * il:(tp_rank + 1) * il])
+
+    def load_rope_tables(self, cos: torch.Tensor, sin: torch.Tensor) -> None:
+        """Overwrite the RoPE tables with ones built elsewhere (e.g. bit-identical to torch's)."""
+        self.load("rope_cos", 0, cos.float())
+        self.load("rope_sin", 0, sin.float())
+
+    # ------------------------------------------------------------------ tables
+    def write_page_table(self, rows, positions, slots) -> None:
+        r, p, v = _i32(rows), _i32(positions), _i32(slots)
+        call("b200_engine_write_table", self._h, 0, r.ctypes.data, p.ctypes.data, v.ctypes.data, len(r))
+
+    def write_token_pool(self, rows, positions, tokens) -> None:
+        r, p, v = _i32(rows), _i32(positions), _i32(tokens)
+        call("b200_engine_write_table", self._h, 1, r.ctypes.data, p.ctypes.data, v.ctypes.data, len(r))
+
+    def read_table(self, which: str) -> np.ndarray:
+        ptr, n = self.tensor_info(which)
+        rows = self.config.max_running_req + 1
+        self.synchronize()
+        return _as_cuda_tensor(ptr, n).view(torch.int32).cpu().numpy().reshape(rows, -1)
+
+    def device_view(self, name: str, layer: int = 0) -> torch.Tensor:
+        """A uint8 torch view of a named device tensor (debugging and tests)."""
+        ptr, n = self.tensor_info(name, layer)
+        return _as_cuda_tensor(ptr, n)
+
+    # ------------------------------------------------------------------ steps
+    def capture_graphs(self, batch_sizes: Sequence[int]) -> None:
+        bs = _i32(batch_sizes)
+        call("b200_engine_capture_graphs", self._h, bs.ctypes.data, len(bs))
+
+    def forward_batch(self, phase: int, table_idx, cached_lens, extend_lens, write_pos=None,
+                      num_reqs: Optional[int] = None) -> ForwardOutput:
+        """Engine::forward_batch (src/engine/engine.cc:495-544).  Arrays are per request over the
+        padded batch; the first ``num_reqs`` are real."""
+        t, c, e = _i32(table_idx), _i32(cached_lens), _i32(extend_lens)
+        bp = len(t)
+        b = bp if num_reqs is None else num_reqs
+        wp = _i32(write_pos) if write_pos is not None else None
+        st = StepStruct(phase, b, bp, t.ctypes.data, c.ctypes.data, e.ctypes.data,
+                        wp.ctypes.data if wp is not None else None, None, None, None, None,
+                        self._step_index)
+        self._step_index += 1
+        call("b200_engine_step", self._h, ctypes.byref(st), self._next_tokens_cpu.data_ptr())
+        return ForwardOutput(self, self._next_tokens_cpu, b)
+
+    def synchronize(self) -> None:
+        call("b200_engine_synchronize", self._h)
+
+    def logits(self, rows: int) -> torch.Tensor:
+        out = torch.empty(rows, self.model_config.vocab_size, dtype=torch.bfloat16)
+        call("b200_engine_read_logits", self._h, out.data_ptr(), rows)
+        return out
+
+    def set_profiling(self, on: bool) -> None:
+        call("b200_engine_set_profiling", self._h, 1 if on else 0)
+
+    def read_profile(self) -> tuple[float, int, int]:
+        """(attention ms of the last profiled step, attention launches, kernels launched by the last step)."""
+        ms, n, k = ctypes.c_float(), ctypes.c_int32(), ctypes.c_int32()
+        call("b200_engine_read_profile", self._h, ctypes.byref(ms), ctypes.byref(n), ctypes.byref(k))
+        return float(ms.value), int(n.value), int(k.value)
+
+    def last_step_ms(self) -> float:
+        ms = ctypes.c_float()
+        call("b200_engine_last_step_ms", self._h, ctypes.byref(ms))
+        return float(ms.value)
+
+
+def _as_cuda_tensor(ptr: int, nbytes: int) -> torch.Tensor:
+    """A uint8 torch view of device memory owned by the C++ engine."""
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {
+        "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+    }
+    return torch.as_tensor(h, device="cuda")

@@ -1,0 +1,155 @@
+"""Host-side request bookkeeping that feeds the step runner.
+
+The reference keeps this logic in its scheduler (TableManager, CacheManager,
+RadixPrefixCache, Req), which stays unchanged behind the drop-in boundary.  This
+module restates just enough of it, with the same allocation order, for the tests
+and the benchmark to drive the engine the way the scheduler would:
+
+* page-table rows are handed out from the BACK of ``[0, max_running_req)``
+  (TableManager::allocate, src/scheduler/prefill.cc:25-30);
+* pages are taken from the FRONT of the free list, which starts as
+  ``0, page_size, 2*page_size, ...`` (CacheManager ctor and allocate_pages,
+  src/scheduler/prefill.cc:55-101);
+* a prompt is matched against cached prefixes on ``input_ids[:-1]``, page-aligned
+  (CacheManager::match_req, src/scheduler/prefill.cc:69-72), and a finished
+  prefill inserts its page-aligned prefix (CacheManager::cache_req, :231-252).
+  The prefix index here is a dictionary keyed by page-aligned token prefixes — a
+  stand-in for the radix tree that gives the same match lengths when no eviction
+  happens (eviction is not modelled).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+
+
+@dataclass
+class Req:
+    """include/sglang/core/req.h:13-58 (the length state machine of src/core/req.cc:5-53)."""
+    input_ids: np.ndarray
+    table_idx: int = -1
+    cached_len: int = 0
+    device_len: int = 0          # tokens whose KV will be in the pool after the current step
+    max_device_len: int = 0
+    output: list = field(default_factory=list)
+
+    def extend_len(self) -> int:
+        return self.device_len - self.cached_len
+
+    def remain_len(self) -> int:
+        return self.max_device_len - self.device_len
+
+    def can_decode(self) -> bool:
+        return self.remain_len() > 0
+
+    def write_pos(self) -> int:
+        """Where the sampled token goes in the token pool (src/scheduler/scheduler.cc:321-325)."""
+        return self.device_len if self.can_decode() else -1
+
+    def complete_one(self) -> None:
+        """Req::complete_one (src/core/req.cc:47-53)."""
+        self.cached_len = self.device_len
+        if self.device_len < self.max_device_len:
+            self.device_len += 1
+
+
+class HostBatcher:
+    def __init__(self, engine, num_pages: int, page_size: int, max_running_req: int,
+                 enable_prefix_cache: bool = True):
+        self.engine = engine
+        self.page_size = page_size
+        self.free_rows = list(range(max_running_req))
+        self.free_pages = [i * page_size for i in range(num_pages)]
+        self.enable_prefix_cache = enable_prefix_cache
+        self.prefix_index: dict[bytes, int] = {}   # key: bytes of the token prefix ending at a page boundary -> page start slot
+        self.page_table = np.zeros((max_running_req + 1, 0), dtype=np.int32)  # host mirror, grown lazily
+        self._mirror: dict[int, list[int]] = {}   # table row -> slots per position
+        self.prefix_hits = 0
+
+    # ---- allocation ---------------------------------------------------------
+    def _match_prefix(self, ids: np.ndarray) -> list[int]:
+        """Slots of the longest cached page-aligned prefix of ids[:-1]."""
+        if not self.enable_prefix_cache:
+            return []
+        P = self.page_size
+        usable = (len(ids) - 1) // P * P
+        slots: list[int] = []
+        for end in range(P, usable + 1, P):
+            start = self.prefix_index.get(ids[:end].tobytes())
+            if start is None:
+                break
+            slots.extend(range(start, start + P))
+        return slots
+
+    def add_request(self, input_ids, max_new_tokens: int) -> Req:
+        ids = np.ascontiguousarray(np.asarray(input_ids, dtype=np.int32))
+        req = Req(ids)
+        req.table_idx = self.free_rows.pop()
+        req.max_device_len = len(ids) + max_new_tokens
+        matched = self._match_prefix(ids)
+        req.cached_len = len(matched)
+        req.device_len = len(ids)
+        self.prefix_hits += len(matched)
+        self._mirror[req.table_idx] = list(matched)
+        rows = np.full(len(ids), req.table_idx, dtype=np.int32)
+        pos = np.arange(len(ids), dtype=np.int32)
+        self.engine.write_token_pool(rows, pos, ids)
+        if matched:
+            self.engine.write_page_table(rows[:len(matched)], pos[:len(matched)], matched)
+        return req
+
+    def allocate(self, reqs) -> None:
+        """CacheManager::allocate_paged: pages for positions [cached_len, device_len) of each request."""
+        P = self.page_size
+        rows, pos, slots = [], [], []
+        for r in reqs:
+            have = len(self._mirror[r.table_idx])
+            first, last = -(-have // P), -(-r.device_len // P)
+            for page in range(first, last):
+                start = self.free_pages.pop(0)
+                for i in range(P):
+                    rows.append(r.table_idx)
+                    pos.append(page * P + i)
+                    slots.append(start + i)
+                    self._mirror[r.table_idx].append(start + i)
+        if rows:
+            self.engine.write_page_table(rows, pos, slots)
+
+    def cache_prefix(self, req: Req) -> None:
+        """Insert the page-aligned prefix of a request whose prefill finished."""
+        if not self.enable_prefix_cache:
+            return
+        P = self.page_size
+        ids, slots = req.input_ids, self._mirror[req.table_idx]
+        for end in range(P, min(req.cached_len, len(ids)) // P * P + 1, P):
+            self.prefix_index.setdefault(ids[:end].tobytes(), slots[end - P])
+
+    def slots_of(self, req: Req) -> list[int]:
+        return self._mirror[req.table_idx]
+
+    # ---- steps --------------------------------------------------------------
+    def prefill(self, reqs):
+        """One prefill step over `reqs` (each runs positions [cached_len, device_len))."""
+        self.allocate(reqs)
+        out = self.engine.forward_batch(
+            0, [r.table_idx for r in reqs], [r.cached_len for r in reqs], [r.extend_len() for r in reqs],
+            write_pos=[r.write_pos() for r in reqs])
+        for r in reqs:
+            r.complete_one()
+        return out
+
+    def decode(self, reqs, padded_size: Optional[int] = None):
+        """One decode step; pads with the dummy request up to `padded_size`."""
+        self.allocate(reqs)
+        n = len(reqs)
+        bp = max(padded_size or n, n)
+        dummy = self.engine.dummy_table_idx
+        out = self.engine.forward_batch(
+            1, [r.table_idx for r in reqs] + [dummy] * (bp - n),
+            [r.cached_len for r in reqs] + [0] * (bp - n), [1] * bp,
+            write_pos=[r.write_pos() for r in reqs], num_reqs=n)
+        for r in reqs:
+            r.complete_one()
+        return out
