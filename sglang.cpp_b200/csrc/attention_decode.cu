@@ -38,7 +38,7 @@ constexpr uint32_t kStageBytes = 4 * kHalfBytes;     // K lo, K hi, V lo, V hi
 constexpr int kStages = 3;
 constexpr int kMaxBatch = 1024;
 constexpr int kSlotTab = 1024;
-constexpr int kItemsPerCta = 8;
+constexpr int kItemsPerCta = 4;
 
 struct DecodeParams {
     __nv_bfloat16* out;
@@ -204,8 +204,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         sl = 0;
                     }
                     const uint32_t dst = stage_base + which * kHalfBytes + copy * copy_bytes;
-                    tma_load_2d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
-                                static_cast<int>(sl) * Hkv, bar);
+                    tma_load_3d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
+                                static_cast<int>(sl), 0, bar);
                 }
             }
         }
@@ -250,14 +250,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const int nvalid = it.len - (st * SK + kg * 16);  // valid keys in this warp's tile
             if (!failed && nvalid > 0) {
                 const uint32_t stage_base = smem_base + slot * kStageBytes;
-                const uint32_t tile_row0 = static_cast<uint32_t>(kg * 16) * Hkv + h;
+                // Row of key j (0..15 of this warp's tile) inside a half tile.  A copy of
+                // kpc keys lands as [head][key] rows, so the keys of one head are adjacent
+                // 128-byte rows and the swizzle spreads an 8-key ldmatrix over all banks.
+                const int kpc = p.kpc;
+                auto tile_row = [&](int j) -> uint32_t {
+                    const int js = kg * 16 + j;
+                    return static_cast<uint32_t>((js & ~(kpc - 1)) * Hkv + h * kpc + (js & (kpc - 1)));
+                };
                 if (nvalid < 16) {
                     // Rows past the end of the sequence hold stale bytes: clear V so
                     // that 0 * garbage cannot poison the accumulator.
                     for (int i = lane; i < (16 - nvalid) * 16; i += 32) {
                         const int j = nvalid + (i >> 4), c16 = i & 15;
                         const uint32_t a = stage_base + (2 + (c16 >> 3)) * kHalfBytes +
-                                           (tile_row0 + j * Hkv) * 128u + (c16 & 7) * 16u;
+                                           tile_row(j) * 128u + (c16 & 7) * 16u;
                         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
                     }
                     fence_proxy_async_smem();
@@ -267,7 +274,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
                 {
                     const int j = (mi >> 1) * 8 + r8;
-                    const uint32_t rowoff = (tile_row0 + j * Hkv) * 128u;
+                    const uint32_t rowoff = tile_row(j) * 128u;
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const int c16 = ks * 2 + (mi & 1);
@@ -317,7 +324,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 // ---- O += P V ----
                 {
                     const int j = (mi & 1) * 8 + r8;
-                    const uint32_t rowoff = (tile_row0 + j * Hkv) * 128u;
+                    const uint32_t rowoff = tile_row(j) * 128u;
 #pragma unroll
                     for (int np = 0; np < 8; ++np) {
                         const int c16 = np * 2 + (mi >> 1);
@@ -473,10 +480,32 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
 }
 
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size) {
+    // 3-D view [heads][slots][128] of the pool's [slots][heads][128] memory (the head
+    // stride is smaller than the slot stride), so that a box of kpc slots x all heads
+    // arrives in shared memory head-major.
     const int stage_keys = kStageRows / kv_heads;
     const int kpc = page_size < stage_keys ? page_size : stage_keys;
-    return make_tmap_2d_bf16_sw128(out, cache, kD, static_cast<uint64_t>(num_slots) * kv_heads,
-                                   kD * 2, 64, static_cast<uint32_t>(kpc * kv_heads));
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        set_last_error("cuTensorMapEncodeTiled is not available from this driver");
+        return B200_ERR_CUDA;
+    }
+    if ((reinterpret_cast<uintptr_t>(cache) & 15u) != 0) {
+        set_last_error("attention_decode: the KV cache must be 16-byte aligned");
+        return B200_ERR_INVALID_ARGUMENT;
+    }
+    const cuuint64_t dims[3] = {kD, static_cast<cuuint64_t>(num_slots), static_cast<cuuint64_t>(kv_heads)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kv_heads) * kD * 2, kD * 2};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(kpc), static_cast<cuuint32_t>(kv_heads)};
+    const cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides,
+                    box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled (KV map) failed with CUresult %d", static_cast<int>(r));
+        return B200_ERR_CUDA;
+    }
+    return B200_OK;
 }
 
 }  // namespace b200

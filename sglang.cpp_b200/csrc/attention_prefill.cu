@@ -40,15 +40,6 @@ struct PrefillParams {
     int* status;
 };
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-        : "memory");
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
