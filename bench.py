@@ -212,11 +212,15 @@ def run_gpu(args):
     ctx_a = [r.device_len for r in reqs]
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profile_region:
+        torch.cuda.profiler.start()
     ev0.record(stream)
     for _ in range(K):
         hb.decode(reqs)
     ev1.record(stream)
     barrier()
+    if args.profile_region:
+        torch.cuda.profiler.stop()
     dev_ms = ev0.elapsed_time(ev1)
     _, _, launches_per_step = engine.read_profile()
 
@@ -390,6 +394,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-region", action="store_true",
+                    help="bracket the device-timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3

@@ -39,6 +39,8 @@ constexpr int kStages = 3;
 constexpr int kMaxBatch = 1024;
 constexpr int kSlotTab = 1024;
 constexpr int kItemsPerCta = 4;
+constexpr int kMergeTab = 2048;   // (head, partial) softmax weights staged for the merge
+constexpr int kMergeHeads = 128;
 
 struct DecodeParams {
     __nv_bfloat16* out;
@@ -79,6 +81,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __shared__ int s_red[16];
     __shared__ int s_chunk_stages;
     __shared__ int s_ticket;
+    __shared__ float s_mw[kMergeTab];
+    __shared__ float s_minv[kMergeHeads];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -379,33 +383,76 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                             make_float2(rr ? m1 : m0, rr ? l1 : l0);
                 }
             }
-            __threadfence();
+            // Release: the barrier orders every thread's partial stores before thread 0's
+            // fence, and the fence orders them before the ticket (fences are cumulative).
             consumer_bar();
-            if (threadIdx.x == 0) s_ticket = atomicAdd(&p.counters[it.b], 1);
+            if (threadIdx.x == 0) {
+                __threadfence();
+                s_ticket = atomicAdd(&p.counters[it.b], 1);
+                __threadfence();
+            }
             consumer_bar();
             const int ticket = s_ticket;
             if (ticket == it.nchunks - 1) {
-                // This CTA finished the request's last item: merge all partials.
-                __threadfence();
+                // This CTA finished the request's last item: merge all partials (read through
+                // L2 with ld.cg; the other CTAs' stores are visible after the ticket).
                 const int64_t part0 = static_cast<int64_t>(s_prefix[it.b]) * KG;
-                for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
-                    const int head = idx / (kD / 2), dp = idx % (kD / 2);
-                    float M = -INFINITY;
-                    for (int pp = 0; pp < nparts; ++pp)
-                        M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                    float L = 0.f, a0 = 0.f, a1 = 0.f;
-                    for (int pp = 0; pp < nparts; ++pp) {
-                        const int64_t ph = (part0 + pp) * Hq + head;
-                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
-                        const float wgt = exp2f(ml.x - M);
-                        const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
-                        L += ml.y * wgt;
-                        a0 += ov.x * wgt;
-                        a1 += ov.y * wgt;
+                if (Hq * nparts <= kMergeTab && Hq <= kMergeHeads) {
+                    // Phase 1: one warp per head computes the softmax weight of every partial.
+                    for (int head = warp; head < Hq; head += kConsumerWarps) {
+                        float mloc = -INFINITY;
+                        for (int pp = lane; pp < nparts; pp += 32)
+                            mloc = fmaxf(mloc, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                        const float M = warp_max(mloc);
+                        float lsum = 0.f;
+                        for (int pp = lane; pp < nparts; pp += 32) {
+                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(
+                                p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                            const float wgt = exp2f(ml.x - M);
+                            s_mw[head * nparts + pp] = wgt;
+                            lsum += ml.y * wgt;
+                        }
+                        const float Lt = warp_sum(lsum);
+                        if (lane == 0) s_minv[head] = Lt > 0.f ? 1.f / Lt : 0.f;
                     }
-                    const float inv = L > 0.f ? 1.f / L : 0.f;
-                    *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
-                        pack_bf16(a0 * inv, a1 * inv);
+                    consumer_bar();
+                    // Phase 2: independent, unrolled loads of the partial outputs.
+                    for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
+                        const int head = idx / (kD / 2), dp = idx % (kD / 2);
+                        const float* wrow = s_mw + head * nparts;
+                        const float* src = p.ws_o + (part0 * Hq + head) * kD + dp * 2;
+                        const int64_t pstride = static_cast<int64_t>(Hq) * kD;
+                        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+                        for (int pp = 0; pp < nparts; ++pp) {
+                            const float2 ov = __ldcg(reinterpret_cast<const float2*>(src + pp * pstride));
+                            a0 += ov.x * wrow[pp];
+                            a1 += ov.y * wrow[pp];
+                        }
+                        const float inv = s_minv[head];
+                        *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
+                            pack_bf16(a0 * inv, a1 * inv);
+                    }
+                } else {
+                    for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
+                        const int head = idx / (kD / 2), dp = idx % (kD / 2);
+                        float M = -INFINITY;
+                        for (int pp = 0; pp < nparts; ++pp)
+                            M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                        float L = 0.f, a0 = 0.f, a1 = 0.f;
+                        for (int pp = 0; pp < nparts; ++pp) {
+                            const int64_t ph = (part0 + pp) * Hq + head;
+                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
+                            const float wgt = exp2f(ml.x - M);
+                            const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
+                            L += ml.y * wgt;
+                            a0 += ov.x * wgt;
+                            a1 += ov.y * wgt;
+                        }
+                        const float inv = L > 0.f ? 1.f / L : 0.f;
+                        *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
+                            pack_bf16(a0 * inv, a1 * inv);
+                    }
                 }
                 if (threadIdx.x == 0) p.counters[it.b] = 0;
             }
@@ -474,8 +521,8 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set = true;
     }
-    attention_decode_kernel<<<grid, kThreads, smem, stream>>>(tmap_k, tmap_v, p);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(attention_decode_kernel, dim3(grid), dim3(kThreads), smem, stream,
+                                  dim3(1, 1, 1), tmap_k, tmap_v, p));
     return B200_OK;
 }
 

@@ -329,8 +329,8 @@ int launch_attention_prefill(void* out, const void* q, int64_t q_st, int64_t q_s
     B200_CHECK_CUDA(cudaFuncSetAttribute(attention_prefill_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid(div_ceil(max_extend_len, QB), kv_heads, batch);
-    attention_prefill_kernel<<<grid, kThreads, smem, stream>>>(tk, tv, p);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(attention_prefill_kernel, grid, dim3(kThreads), smem, stream,
+                                  dim3(1, 1, 1), tk, tv, p));
     return B200_OK;
 }
 

@@ -45,6 +45,41 @@ void set_last_error(const char* fmt, ...);
 
 #define B200_CHECK_LAUNCH() B200_CHECK_CUDA(cudaGetLastError())
 
+// Whether kernels are launched as programmatic dependent launches (the step runner
+// turns this on for its kernel chain: every kernel there executes griddepcontrol.wait
+// before touching data a predecessor produces).  Per thread; off by default.
+bool pdl_launches_enabled();
+void set_pdl_launches(bool on);
+
+// One launch path for every kernel: cudaLaunchKernelEx, with the programmatic
+// stream serialization attribute when enabled (and an optional cluster shape).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, dim3 cluster, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned n = 0;
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = cluster.x;
+        attrs[n].val.clusterDim.y = cluster.y;
+        attrs[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    if (pdl_launches_enabled()) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int div_ceil(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t div_ceil64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -83,23 +83,19 @@ int launch_act_and_mul(void* out, const void* in, int tokens, int d, bool gelu,
     const int64_t want = div_ceil64(total, 256);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
-    if (gelu)
-        act_and_mul_kernel<true><<<blocks, 256, 0, stream>>>(
-            static_cast<uint4*>(out), static_cast<const uint4*>(in), tokens, vec);
-    else
-        act_and_mul_kernel<false><<<blocks, 256, 0, stream>>>(
-            static_cast<uint4*>(out), static_cast<const uint4*>(in), tokens, vec);
-    B200_CHECK_LAUNCH();
+    auto kernel = gelu ? act_and_mul_kernel<true> : act_and_mul_kernel<false>;
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(blocks), dim3(256), 0, stream, dim3(1, 1, 1),
+                                  static_cast<uint4*>(out), static_cast<const uint4*>(in),
+                                  static_cast<int64_t>(tokens), vec));
     return B200_OK;
 }
 
 int launch_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
                      int vocab, int* status, cudaStream_t stream) {
     if (tokens == 0) return B200_OK;
-    embedding_kernel<<<tokens, 128, 0, stream>>>(static_cast<uint4*>(out),
-                                                 static_cast<const uint4*>(table), ids, hidden / 8,
-                                                 vocab, status);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(embedding_kernel, dim3(tokens), dim3(128), 0, stream, dim3(1, 1, 1),
+                                  static_cast<uint4*>(out), static_cast<const uint4*>(table), ids,
+                                  hidden / 8, vocab, status));
     return B200_OK;
 }
 

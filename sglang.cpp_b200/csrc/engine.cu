@@ -147,6 +147,7 @@ struct b200_engine {
     std::vector<cudaEvent_t> prof_events;   // 2 per layer
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
+    bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
 };
 
 namespace {
@@ -207,15 +208,29 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     const int32_t* meta_table_idx = e->meta_dev;
     const int32_t* meta_qo = e->meta_dev + 2 * Bp;
 
+    // The residual stream starts at zero, so the first fused add+norm leaves residual = embedding
+    // (what the reference's layer 0 does with `residual = x`).
+    B200_CHECK_CUDA(cudaMemsetAsync(e->residual, 0, static_cast<size_t>(T) * hidden * 2, s));
+    // From here on the step is an unbroken chain of kernels.  With programmatic dependent
+    // launches each kernel's prologue (barrier set-up, TMEM allocation, weight-tile TMA loads)
+    // overlaps the tail of its predecessor; every kernel waits (griddepcontrol.wait) before it
+    // reads or writes anything a predecessor touches.
+    struct PdlScope {
+        ~PdlScope() { set_pdl_launches(false); }
+    } pdl_scope;
+    set_pdl_launches(false);  // the first kernel follows a memset / copy: ordinary dependency
     {
         const int n = T > Bp ? T : Bp;
-        prepare_tokens_kernel<<<div_ceil(n, 256), 256, 0, s>>>(
-            e->meta_dev, Bp, T, e->page_table, e->token_pool, e->pt_cols, e->pt_rows, e->pt_cols,
-            e->positions, e->out_loc, e->input_ids, e->seq_lens);
-        B200_CHECK_LAUNCH();
+        B200_CHECK_CUDA(launch_kernel(prepare_tokens_kernel, dim3(div_ceil(n, 256)), dim3(256), 0, s,
+                                      dim3(1, 1, 1), static_cast<const int32_t*>(e->meta_dev), Bp, T,
+                                      static_cast<const int32_t*>(e->page_table),
+                                      static_cast<const int32_t*>(e->token_pool),
+                                      static_cast<int64_t>(e->pt_cols), e->pt_rows, e->pt_cols, e->positions,
+                                      e->out_loc, e->input_ids, e->seq_lens));
     }
+    // (Per-kernel event timing wants each kernel to start after its predecessor ends.)
+    set_pdl_launches(e->use_pdl && !(e->profile_attention && !e->capturing));
     B200_TRY(launch_embedding(e->x, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s));
-    B200_CHECK_CUDA(cudaMemsetAsync(e->residual, 0, static_cast<size_t>(T) * hidden * 2, s));
     const bool round_first = m.fused_residual == 0;
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
 
@@ -271,10 +286,9 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                       round_first, s));
     const __nv_bfloat16* head_in = e->x;
     if (phase == B200_PHASE_PREFILL) {
-        select_last_rows_kernel<<<Bp, 128, 0, s>>>(reinterpret_cast<uint4*>(e->sel),
-                                                   reinterpret_cast<const uint4*>(e->x), meta_qo,
-                                                   hidden / 8);
-        B200_CHECK_LAUNCH();
+        B200_CHECK_CUDA(launch_kernel(select_last_rows_kernel, dim3(Bp), dim3(128), 0, s, dim3(1, 1, 1),
+                                      reinterpret_cast<uint4*>(e->sel), reinterpret_cast<const uint4*>(e->x),
+                                      meta_qo, hidden / 8));
         head_in = e->sel;
     }
     B200_TRY(launch_linear(e->logits, head_in, e->lm_head, nullptr, Bp, m.vocab_size, hidden, hidden,
@@ -283,10 +297,11 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     // Token write-back: token_pool[table_idx[i], write_pos[i]] = next_tokens[i].
     if (B > 0) {
         const int32_t* write_pos = e->meta_dev + 3 * Bp + 1;
-        scatter_int32_kernel<<<div_ceil(B, 256), 256, 0, s>>>(e->token_pool, e->pt_rows, e->pt_cols,
-                                                            e->pt_cols, meta_table_idx, write_pos,
-                                                            e->next_tokens, B);
-        B200_CHECK_LAUNCH();
+        B200_CHECK_CUDA(launch_kernel(scatter_int32_kernel, dim3(div_ceil(B, 256)), dim3(256), 0, s,
+                                      dim3(1, 1, 1), e->token_pool, static_cast<int64_t>(e->pt_rows),
+                                      static_cast<int64_t>(e->pt_cols), static_cast<int64_t>(e->pt_cols),
+                                      meta_table_idx, write_pos, static_cast<const int32_t*>(e->next_tokens),
+                                      static_cast<int64_t>(B)));
     }
     // Kernels launched above: prepare, embedding, per layer 8 (two norms, four GEMMs, the
     // qk-norm/rope/store pass, attention), final norm, lm_head, argmax, token write-back, plus the
@@ -368,6 +383,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     int err = B200_OK;
     e->status = device_status_words(&err);
     if (err != B200_OK) { delete e; return err; }
+    if (const char* v = getenv("B200_PDL")) e->use_pdl = atoi(v) != 0;
 
     auto fail = [&](int code) { b200_engine_destroy(e); return code; };
 #define E_TRY(expr) do { int c__ = (expr); if (c__ != B200_OK) return fail(c__); } while (0)

@@ -31,7 +31,8 @@ constexpr int kTileN = 128;  // output features per CTA (UMMA M)
 constexpr int kBlockK = 64;  // bf16 elements per k-block (one 128-byte swizzle row)
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int kChunkCols = 32;  // token columns exchanged per cluster round
+constexpr int kChunkCols = 32;  // token columns per tcgen05.ld
+constexpr int kRoundCols = 64;  // token columns exchanged per cluster round
 
 // ---- tcgen05 wrappers --------------------------------------------------------
 
@@ -124,6 +125,17 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank
     float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(remote)
+                 : "memory");
     return v;
 }
 
@@ -269,8 +281,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int feat_local = q * 32 + lane;         // feature row inside the tile
     float* xbuf = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
     const uint32_t xbuf_addr = smem_base;
-    const int nchunks = nt / kChunkCols;
-    const int chunk_floats = NUM_A * kChunkCols * kTileN;
+    const int cpr = nt < kRoundCols ? nt : kRoundCols;  // token columns per exchange round
+    const int nrounds = nt / cpr;
+    const int round_floats = NUM_A * cpr * kTileN;
 
     if (is_epi) {
         if (!mbar_wait_bounded(smem_u32(&tmem_full_bar), 0, p.status, 103)) failed = true;
@@ -278,85 +291,95 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
     pdl_launch_dependents();
 
-    for (int c = 0; c < nchunks; ++c) {
-        uint32_t g[32], u[32];
+    for (int r = 0; r < nrounds; ++r) {
+        float* buf = xbuf + (r & 1) * round_floats;
         if (is_epi) {
-            if (my_kb > 0 && !failed) {
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                       static_cast<uint32_t>(c * kChunkCols);
-                tmem_ld_32x32b_x32(taddr, g);
-                if (NUM_A == 2) tmem_ld_32x32b_x32(taddr + nt, u);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    g[j] = 0u;
-                    u[j] = 0u;
-                }
-            }
-        }
-        if (split == 1) {
-            if (is_epi) {
-                const int n = n0 + feat_local;
-                if (n < p.n_out) {
-                    const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+            for (int cc = 0; cc < cpr / kChunkCols; ++cc) {
+                const int c = r * (cpr / kChunkCols) + cc;
+                uint32_t g[32], u[32];
+                if (my_kb > 0 && !failed) {
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                           static_cast<uint32_t>(c * kChunkCols);
+                    tmem_ld_32x32b_x32(taddr, g);
+                    if (NUM_A == 2) tmem_ld_32x32b_x32(taddr + nt, u);
+                    tmem_ld_wait();
+                } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int m = c * kChunkCols + j;
-                        if (m < p.M) {
-                            float r;
-                            if (NUM_A == 2) {
-                                const float gv = round_bf16(__uint_as_float(g[j]));
-                                const float uv = round_bf16(__uint_as_float(u[j]));
-                                r = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
-                            } else {
-                                r = __uint_as_float(g[j]) + bias;
+                        g[j] = 0u;
+                        u[j] = 0u;
+                    }
+                }
+                if (split == 1) {
+                    const int n = n0 + feat_local;
+                    if (n < p.n_out) {
+                        const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int m = c * kChunkCols + j;
+                            if (m < p.M) {
+                                float v;
+                                if (NUM_A == 2) {
+                                    const float gv = round_bf16(__uint_as_float(g[j]));
+                                    const float uv = round_bf16(__uint_as_float(u[j]));
+                                    v = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                                } else {
+                                    v = __uint_as_float(g[j]) + bias;
+                                }
+                                p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(v);
                             }
-                            p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(r);
                         }
                     }
+                } else {
+                    // Publish this CTA's partial sums: [accumulator][column][feature].
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        buf[(cc * kChunkCols + j) * kTileN + feat_local] = __uint_as_float(g[j]);
+                        if (NUM_A == 2)
+                            buf[(cpr + cc * kChunkCols + j) * kTileN + feat_local] = __uint_as_float(u[j]);
+                    }
                 }
             }
-            continue;
         }
+        if (split == 1) continue;
 
-        // Multi-CTA K split: publish this CTA's partial chunk, then reduce the
-        // slice of features this rank owns over all ranks in rank order.
-        float* buf = xbuf + (c & 1) * chunk_floats;
-        if (is_epi) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                buf[j * kTileN + feat_local] = __uint_as_float(g[j]);
-                if (NUM_A == 2) buf[(kChunkCols + j) * kTileN + feat_local] = __uint_as_float(u[j]);
-            }
-        }
         cluster_sync_all();
         if (is_epi) {
-            const int F = kTileN / static_cast<int>(split);  // features owned by this rank
-            const int te = (warp - 2) * 32 + lane;           // 0..127
-            const int f = static_cast<int>(rank) * F + (te % F);
-            const int n = n0 + f;
-            const int cols_per_pass = kTileN / F;
-            const uint32_t cbase = xbuf_addr + static_cast<uint32_t>((c & 1) * chunk_floats) * 4u;
-            const float bias = (p.bias && n < p.n_out) ? __bfloat162float(p.bias[n]) : 0.f;
-            for (int j = te / F; j < kChunkCols; j += cols_per_pass) {
-                float sg = 0.f, su = 0.f;
-                for (uint32_t r = 0; r < split; ++r) {
-                    sg += ld_dsmem_f32(cbase + static_cast<uint32_t>(j * kTileN + f) * 4u, r);
-                    if (NUM_A == 2)
-                        su += ld_dsmem_f32(
-                            cbase + static_cast<uint32_t>((kChunkCols + j) * kTileN + f) * 4u, r);
-                }
-                const int m = c * kChunkCols + j;
-                if (m < p.M && n < p.n_out) {
-                    float r;
+            // This rank owns F features of the tile; four of them per thread and column,
+            // summed over the ranks in rank order with 16-byte distributed-shared loads.
+            const int F = kTileN / static_cast<int>(split);
+            const int f4_per_col = F / 4;
+            const int te = (warp - 2) * 32 + lane;  // 0..127
+            const uint32_t cbase = xbuf_addr + static_cast<uint32_t>((r & 1) * round_floats) * 4u;
+            for (int i = te; i < cpr * f4_per_col; i += 128) {
+                const int col = i / f4_per_col;
+                const int f = static_cast<int>(rank) * F + (i - col * f4_per_col) * 4;
+                float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), su = sg;
+                for (uint32_t rr = 0; rr < split; ++rr) {
+                    const float4 a = ld_dsmem_f32x4(cbase + static_cast<uint32_t>(col * kTileN + f) * 4u, rr);
+                    sg.x += a.x; sg.y += a.y; sg.z += a.z; sg.w += a.w;
                     if (NUM_A == 2) {
-                        const float gv = round_bf16(sg), uv = round_bf16(su);
-                        r = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
-                    } else {
-                        r = sg + bias;
+                        const float4 b2 = ld_dsmem_f32x4(
+                            cbase + static_cast<uint32_t>((cpr + col) * kTileN + f) * 4u, rr);
+                        su.x += b2.x; su.y += b2.y; su.z += b2.z; su.w += b2.w;
                     }
-                    p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(r);
+                }
+                const int m = r * cpr + col;
+                const int n = n0 + f;
+                if (m < p.M && n < p.n_out) {
+                    float v[4] = {sg.x, sg.y, sg.z, sg.w};
+                    const float uu[4] = {su.x, su.y, su.z, su.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (NUM_A == 2) {
+                            const float gv = round_bf16(v[e]), uv = round_bf16(uu[e]);
+                            v[e] = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                        } else if (p.bias) {
+                            v[e] += __bfloat162float(p.bias[n + e]);
+                        }
+                    }
+                    uint2 packed = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+                    *reinterpret_cast<uint2*>(p.y + static_cast<int64_t>(m) * p.n_out + n) = packed;
                 }
             }
         }
@@ -427,7 +450,8 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     const int kbp = div_ceil(kb_total, split);
 
     const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt * kBlockK * 2;
-    const uint32_t exch_bytes = split > 1 ? 2u * num_a * kChunkCols * kTileN * 4u : 0u;
+    const int cpr = nt < kRoundCols ? nt : kRoundCols;
+    const uint32_t exch_bytes = split > 1 ? (nt > cpr ? 2u : 1u) * num_a * cpr * kTileN * 4u : 0u;
     const uint32_t smem_limit = 200 * 1024;
     int stages = kbp < kMaxStages ? kbp : kMaxStages;
     while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
@@ -463,21 +487,8 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_tiles, split, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
-    int nattr = 0;
-    attrs[nattr].id = cudaLaunchAttributeClusterDimension;
-    attrs[nattr].val.clusterDim.x = 1;
-    attrs[nattr].val.clusterDim.y = split;
-    attrs[nattr].val.clusterDim.z = 1;
-    ++nattr;
-    cfg.attrs = attrs;
-    cfg.numAttrs = nattr;
-    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_x, p));
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, split, 1), dim3(kThreads), smem_bytes, stream,
+                                  dim3(1, split, 1), tmap_w, tmap_x, p));
     return B200_OK;
 }
 

@@ -188,10 +188,10 @@ int launch_rmsnorm(void* out, const void* x, const void* weight, int rows, int h
                    cudaStream_t stream) {
     if (rows == 0) return B200_OK;
     const int threads = hidden >= 2048 ? 256 : 128;
-    rmsnorm_kernel<false, false><<<rows, threads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x), nullptr,
-        static_cast<const __nv_bfloat16*>(weight), hidden, eps);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(rmsnorm_kernel<false, false>, dim3(rows), dim3(threads), 0, stream, dim3(1, 1, 1),
+                                  static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x),
+                                  static_cast<__nv_bfloat16*>(nullptr),
+                                  static_cast<const __nv_bfloat16*>(weight), hidden, eps));
     return B200_OK;
 }
 
@@ -200,11 +200,10 @@ int launch_fused_add_rmsnorm(void* x, void* residual, const void* weight, int ro
     if (rows == 0) return B200_OK;
     const int threads = hidden >= 2048 ? 256 : 128;
     auto kernel = round_sum_first ? rmsnorm_kernel<true, true> : rmsnorm_kernel<true, false>;
-    kernel<<<rows, threads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(x),
-        static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(weight), hidden,
-        eps);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(rows), dim3(threads), 0, stream, dim3(1, 1, 1),
+                                  static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(x),
+                                  static_cast<__nv_bfloat16*>(residual),
+                                  static_cast<const __nv_bfloat16*>(weight), hidden, eps));
     return B200_OK;
 }
 

@@ -185,11 +185,12 @@ int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weig
     if (rows == 0) return B200_OK;
     const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
 #define B200_LAUNCH_QRS(D)                                                                       \
-    qknorm_rope_store_kernel<D><<<blocks, 128, 0, stream>>>(                                     \
+    B200_CHECK_CUDA(launch_kernel(                                                               \
+        qknorm_rope_store_kernel<D>, dim3(blocks), dim3(128), 0, stream, dim3(1, 1, 1),          \
         static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_weight),           \
         static_cast<const __nv_bfloat16*>(k_weight), cos_table, sin_table, positions, out_loc,   \
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), tokens,      \
-        q_heads, kv_heads, max_pos, num_slots, eps, write_k_back, status)
+        q_heads, kv_heads, max_pos, num_slots, eps, write_k_back, status))
     switch (head_dim) {
         case 64: B200_LAUNCH_QRS(64); break;
         case 128: B200_LAUNCH_QRS(128); break;

@@ -67,8 +67,8 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   cudaStream_t stream) {
     if (rows == 0) return B200_OK;
-    argmax_bf16_kernel<<<rows, 512, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(logits), vocab, ld);
-    B200_CHECK_LAUNCH();
+    B200_CHECK_CUDA(launch_kernel(argmax_bf16_kernel, dim3(rows), dim3(512), 0, stream, dim3(1, 1, 1), out,
+                                  static_cast<const __nv_bfloat16*>(logits), vocab, ld));
     return B200_OK;
 }
 

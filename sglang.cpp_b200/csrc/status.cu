@@ -18,6 +18,12 @@ int* g_status_words[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
 }  // namespace
 
+namespace {
+thread_local bool g_pdl = false;
+}
+bool pdl_launches_enabled() { return g_pdl; }
+void set_pdl_launches(bool on) { g_pdl = on; }
+
 void set_last_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

@@ -66,9 +66,13 @@ class Pair:
 
 
 def check_logits(got, want, what):
+    """max-abs <= 2e-2; mean-abs <= 1e-3 plus one bf16 step (2^-8 relative) of a typical logit: two
+    bf16 pipelines that sum in different orders (and round the attention probabilities at different
+    points) differ by about one rounding step of the stored logit, whatever its scale."""
     d = (got.float() - want.float()).abs()
+    rms = float(want.float().pow(2).mean().sqrt())
     assert float(d.max()) <= MAX_ABS, f"{what}: max-abs {float(d.max()):.4g}"
-    assert float(d.mean()) <= MEAN_ABS, f"{what}: mean-abs {float(d.mean()):.4g}"
+    assert float(d.mean()) <= MEAN_ABS + rms * 2 ** -8, f"{what}: mean-abs {float(d.mean()):.4g} (logit rms {rms:.3g})"
 
 
 @pytest.mark.parametrize("kind,page_size", [("qwen3", 16), ("qwen3", 1), ("llama", 16), ("qwen2", 4)])
