@@ -207,6 +207,20 @@ B200_API int b200_attention_prefill(void* out, const void* q, int64_t q_stride_t
 B200_API int b200_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                          b200_stream_t stream);
 
+/* Sampler::sample, stochastic branch (src/engine/engine.cc:299-338) with the candidate set of
+ * sample_row (engine.cc:126-158): logits / temperature, keep the top_k largest, then drop sorted
+ * entries whose inclusive cumulative probability exceeds top_p (never the first), renormalise and
+ * draw.  bf16 logits [rows, vocab]; temperatures / top_k / top_p per row as Sampler::prepare
+ * clamps them (top_k, top_p may be NULL = off; a row with temperature <= 1e-6 is greedy).  The
+ * draw uses Philox keyed by seeds[row] (NULL = row index) and step_index, so it is reproducible;
+ * the reference draws from torch's global generator instead.  candidate_mask (NULL or uint8
+ * [rows, vocab]) receives 1 for every token of the final candidate set.  Ties are ordered by
+ * index. */
+B200_API int b200_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
+                         const float* temperatures, const int32_t* top_k, const float* top_p,
+                         const uint64_t* seeds, uint64_t step_index, uint8_t* candidate_mask,
+                         b200_stream_t stream);
+
 /* ---- step runner (include/sglang/engine/engine.h:57-103) -------------------- */
 
 /* The fields of ModelConfig the forward pass reads (include/sglang/models/config.h:15-42). */

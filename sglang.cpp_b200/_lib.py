@@ -62,6 +62,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
+    "b200_sample": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, ctypes.c_uint64, _P, _P]),
     "b200_engine_create": (_I, [_P, _P, POINTER(c_void_p)]),
     "b200_engine_destroy": (_I, [_P]),
     "b200_engine_tensor": (_I, [_P, c_char_p, _I, POINTER(c_void_p), POINTER(c_int64)]),

@@ -148,6 +148,8 @@ struct b200_engine {
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
+    // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
+    static int seed_offset(int Bp) { return (7 * Bp + 1 + 1) & ~1; }
 };
 
 namespace {
@@ -201,7 +203,8 @@ int build_rope_tables(b200_engine* e) {
 }
 
 // The layer stack on `T` tokens of `Bp` requests; everything is enqueued on e->stream.
-int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_extend) {
+int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_extend,
+                    bool sampling = false, uint64_t step_index = 0) {
     const b200_model_config& m = e->m;
     cudaStream_t s = e->stream;
     const int hidden = m.hidden_size, d = m.head_dim;
@@ -293,7 +296,17 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     }
     B200_TRY(launch_linear(e->logits, head_in, e->lm_head, nullptr, Bp, m.vocab_size, hidden, hidden,
                            B200_EPILOGUE_NONE, e->status, s));
-    B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s));
+    if (sampling) {
+        // meta layout after write_pos[Bp]: temperatures | top_k | top_p | seeds (2 ints each)
+        const int32_t* sp = e->meta_dev + 4 * Bp + 1;
+        B200_TRY(launch_sample(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size,
+                               reinterpret_cast<const float*>(sp), sp + Bp,
+                               reinterpret_cast<const float*>(sp + 2 * Bp),
+                               reinterpret_cast<const uint64_t*>(e->meta_dev + e->seed_offset(Bp)), step_index,
+                               nullptr, s));
+    } else {
+        B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s));
+    }
     // Token write-back: token_pool[table_idx[i], write_pos[i]] = next_tokens[i].
     if (B > 0) {
         const int32_t* write_pos = e->meta_dev + 3 * Bp + 1;
@@ -336,6 +349,22 @@ int stage_step(b200_engine* e, const b200_step* st, int* T_out, int* max_ext_out
     }
     mh[3 * Bp] = T;
     for (int i = 0; i < Bp; ++i) mh[3 * Bp + 1 + i] = (i < B && st->write_pos) ? st->write_pos[i] : -1;
+    if (st->temperatures) {
+        float* tf = reinterpret_cast<float*>(mh + 4 * Bp + 1);
+        int32_t* tk = mh + 5 * Bp + 1;
+        float* tp = reinterpret_cast<float*>(mh + 6 * Bp + 1);
+        uint64_t* sd = reinterpret_cast<uint64_t*>(mh + b200_engine::seed_offset(Bp));
+        for (int i = 0; i < Bp; ++i) {
+            // Clamping as Sampler::prepare does (src/engine/engine.cc:264-275).
+            const float t = i < B ? st->temperatures[i] : 0.f;
+            tf[i] = t > 1e-6f ? t : 1e-6f;
+            const int k = (i < B && st->top_k) ? st->top_k[i] : -1;
+            tk[i] = k >= 1 ? k : e->m.vocab_size;
+            const float pp = (i < B && st->top_p) ? st->top_p[i] : 1.f;
+            tp[i] = pp < 1e-6f ? 1e-6f : (pp > 1.f ? 1.f : pp);
+            sd[i] = (i < B && st->seeds) ? st->seeds[i] : static_cast<uint64_t>(i);
+        }
+    }
     *T_out = T;
     *max_ext_out = max_ext;
     return B200_OK;
@@ -456,7 +485,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);
     E_TRY(dev_alloc(e, &e->attn_ws, e->attn_ws_bytes, true));
 
-    e->meta_ints = 4 * e->max_batch + 8;
+    e->meta_ints = 9 * e->max_batch + 16;
     if (cudaMallocHost(&e->meta_host, e->meta_ints * sizeof(int32_t)) != cudaSuccess) {
         set_last_error("engine_create: pinned staging allocation failed");
         return fail(B200_ERR_CUDA);
@@ -608,10 +637,7 @@ int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_h
     B200_CHECK_ARG(B >= 0 && Bp >= B && Bp <= e->max_batch, "engine_step: batch size out of range");
     if (Bp == 0) return B200_OK;
     B200_CHECK_ARG(st->table_idx && st->cached_lens && st->extend_lens, "engine_step: NULL request arrays");
-    if (st->temperatures != nullptr) {
-        set_last_error("engine_step: stochastic sampling is not wired into the step runner yet");
-        return B200_ERR_UNSUPPORTED;
-    }
+    const bool sampling = st->temperatures != nullptr;
     if (e->meta_in_flight) {  // the staging block of the previous step must have been consumed
         B200_CHECK_CUDA(cudaEventSynchronize(e->ev_meta_done));
         e->meta_in_flight = false;
@@ -624,18 +650,19 @@ int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_h
 
     cudaStream_t s = e->stream;
     B200_CHECK_CUDA(cudaEventRecord(e->ev_step_begin, s));
-    B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, (4 * Bp + 1) * sizeof(int32_t),
-                                    cudaMemcpyHostToDevice, s));
+    const size_t meta_bytes = (sampling ? b200_engine::seed_offset(Bp) + 2 * Bp : 4 * Bp + 1) * sizeof(int32_t);
+    B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, meta_bytes, cudaMemcpyHostToDevice, s));
     B200_CHECK_CUDA(cudaEventRecord(e->ev_meta_done, s));
     e->meta_in_flight = true;
     // A captured graph covers all Bp rows; padded rows carry write_pos = -1 so nothing of
     // theirs is written back, and only the first B tokens are copied out.
     auto g = st->phase == B200_PHASE_DECODE ? e->graphs.find(Bp) : e->graphs.end();
-    if (g != e->graphs.end() && !e->profile_attention) {
+    // Sampled steps run the eager sequence: the captured graphs end in the argmax kernel.
+    if (g != e->graphs.end() && !e->profile_attention && !sampling) {
         B200_CHECK_CUDA(cudaGraphLaunch(g->second, s));
         e->launches_last_step = e->graph_launches[Bp];
     } else {
-        B200_TRY(enqueue_forward(e, st->phase, B, Bp, T, max_ext));
+        B200_TRY(enqueue_forward(e, st->phase, B, Bp, T, max_ext, sampling, st->step_index));
     }
     if (next_tokens_host && B > 0)
         B200_CHECK_CUDA(cudaMemcpyAsync(next_tokens_host, e->next_tokens, B * sizeof(int32_t),

@@ -169,15 +169,27 @@ class Engine:
         call("b200_engine_capture_graphs", self._h, bs.ctypes.data, len(bs))
 
     def forward_batch(self, phase: int, table_idx, cached_lens, extend_lens, write_pos=None,
-                      num_reqs: Optional[int] = None) -> ForwardOutput:
+                      num_reqs: Optional[int] = None, temperatures=None, top_k=None, top_p=None,
+                      seeds=None) -> ForwardOutput:
         """Engine::forward_batch (src/engine/engine.cc:495-544).  Arrays are per request over the
-        padded batch; the first ``num_reqs`` are real."""
+        padded batch; the first ``num_reqs`` are real.  ``temperatures`` (per real request) switches
+        the step from greedy argmax to sampling, as BatchSamplingArgs does in the reference."""
         t, c, e = _i32(table_idx), _i32(cached_lens), _i32(extend_lens)
         bp = len(t)
         b = bp if num_reqs is None else num_reqs
         wp = _i32(write_pos) if write_pos is not None else None
+        keep = []
+
+        def opt(a, dtype):
+            if a is None:
+                return None
+            arr = np.ascontiguousarray(np.asarray(a, dtype=dtype))
+            keep.append(arr)
+            return arr.ctypes.data
+
         st = StepStruct(phase, b, bp, t.ctypes.data, c.ctypes.data, e.ctypes.data,
-                        wp.ctypes.data if wp is not None else None, None, None, None, None,
+                        wp.ctypes.data if wp is not None else None, opt(temperatures, np.float32),
+                        opt(top_k, np.int32), opt(top_p, np.float32), opt(seeds, np.uint64),
                         self._step_index)
         self._step_index += 1
         call("b200_engine_step", self._h, ctypes.byref(st), self._next_tokens_cpu.data_ptr())

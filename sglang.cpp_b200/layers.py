@@ -349,6 +349,23 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def sample(logits: torch.Tensor, temperatures: torch.Tensor, top_k: Optional[torch.Tensor] = None,
+           top_p: Optional[torch.Tensor] = None, seeds: Optional[torch.Tensor] = None,
+           step_index: int = 0, return_mask: bool = False):
+    """Sampler::sample, stochastic branch (src/engine/engine.cc:299-338); args as BatchSamplingArgs
+    (include/sglang/engine/engine.h:22-26) holds them: float32 temperatures, int32 top_k, float32
+    top_p, all on the device.  Returns int32 tokens (and the uint8 candidate mask if asked)."""
+    _cuda_bf16(logits, "logits")
+    _check(logits.dim() == 2 and logits.stride(1) == 1, "logits must be rank 2 with contiguous rows")
+    _check(temperatures.dtype == torch.float32 and temperatures.numel() == logits.size(0),
+           "temperatures must be float32 [rows]")
+    out = torch.empty(logits.size(0), dtype=torch.int32, device=logits.device)
+    mask = torch.empty(logits.shape, dtype=torch.uint8, device=logits.device) if return_mask else None
+    call("b200_sample", out.data_ptr(), logits.data_ptr(), logits.size(0), logits.size(1), logits.stride(0),
+         temperatures.data_ptr(), _ptr(top_k), _ptr(top_p), _ptr(seeds), step_index, _ptr(mask), _stream())
+    return (out, mask) if return_mask else out
+
+
 def read_device_status() -> tuple[int, int]:
     import ctypes
     buf = (ctypes.c_int32 * 2)()
