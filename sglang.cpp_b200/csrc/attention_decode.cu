@@ -38,7 +38,7 @@ constexpr uint32_t kStageBytes = 4 * kHalfBytes;     // K lo, K hi, V lo, V hi
 constexpr int kStages = 3;
 constexpr int kMaxBatch = 1024;
 constexpr int kSlotTab = 1024;
-constexpr int kItemsPerCta = 4;
+constexpr int kMinStagesPerCta = 2;   // do not split below two stages (128 KB) per CTA
 constexpr int kMergeTab = 2048;   // (head, partial) softmax weights staged for the merge
 constexpr int kMergeHeads = 128;
 
@@ -63,7 +63,7 @@ struct DecodeParams {
 };
 
 struct ItemInfo {
-    int b, len, s_begin, s_end, nchunks, item;
+    int b, len, s_begin, s_end, nchunks, item, first_slot;
 };
 
 __device__ __forceinline__ void consumer_bar() {
@@ -78,8 +78,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __shared__ __align__(8) uint64_t empty_bar[kStages];
     __shared__ int s_prefix[kMaxBatch + 1];  // exclusive scan of items per request
     __shared__ int s_slot_tab[kSlotTab];
-    __shared__ int s_red[16];
-    __shared__ int s_chunk_stages;
     __shared__ int s_ticket;
     __shared__ float s_mw[kMergeTab];
     __shared__ float s_minv[kMergeHeads];
@@ -103,31 +101,17 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
     pdl_wait_prior();
 
-    // ---- device-side split: stages per request -> items per request -> scan ----
-    int my_stages = 0;
-    for (int b = threadIdx.x; b < B; b += kThreads) my_stages += (max(p.seq_lens[b], 0) + SK - 1) / SK;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) my_stages += __shfl_xor_sync(0xffffffffu, my_stages, o);
-    if (lane == 0) s_red[warp] = my_stages;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int total = 0;
-        for (int w = 0; w < kThreads / 32; ++w) total += s_red[w];
-        const int target = static_cast<int>(gridDim.x) * kItemsPerCta;
-        int cs = (total + target - 1) / target;
-        s_chunk_stages = cs < 2 ? 2 : cs;
-    }
-    __syncthreads();
-    const int chunk_stages = s_chunk_stages;
+    // ---- device-side split ----
+    // All stages of all requests form one global sequence; CTA i takes the contiguous run
+    // [i*per, (i+1)*per) of it, so every CTA streams the same number of bytes (+-1 stage).
+    // A run is cut into items at request boundaries.  s_prefix[b] = first global stage of
+    // request b.  Request b is covered by the CTAs c0 = s_prefix[b]/per .. and its partials
+    // live in the consecutive workspace slots b + c (unique because b and c grow together).
     if (warp == 0) {
         int carry = 0;
         for (int base = 0; base < B; base += 32) {
             const int b = base + lane;
-            int n = 0;
-            if (b < B) {
-                const int st = (max(p.seq_lens[b], 0) + SK - 1) / SK;
-                n = (st + chunk_stages - 1) / chunk_stages;
-            }
+            const int n = b < B ? (max(p.seq_lens[b], 0) + SK - 1) / SK : 0;
             int incl = n;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -140,28 +124,34 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (lane == 0) s_prefix[B] = carry;
     }
     __syncthreads();
-    const int total_items = s_prefix[B];
-    if (total_items > p.max_items) {
-        if (threadIdx.x == 0) atomicExch(&p.status[kStatusBadIndex], total_items + 1);
+    const int total_stages = s_prefix[B];
+    const int per = max((total_stages + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x),
+                        kMinStagesPerCta);
+    const int g_begin = static_cast<int>(blockIdx.x) * per;
+    const int g_end = min(total_stages, g_begin + per);
+    if (static_cast<int>(gridDim.x) + B > p.max_items) {
+        if (threadIdx.x == 0) atomicExch(&p.status[kStatusBadIndex], static_cast<int>(gridDim.x) + B + 1);
         return;
     }
 
-    auto locate = [&](int w) {
+    // The item that starts at global stage gpos (gpos < g_end).
+    auto locate = [&](int gpos) {
         ItemInfo it;
-        int lo = 0, hi = B;  // largest b with s_prefix[b] <= w and items(b) > 0
+        int lo = 0, hi = B;  // largest b with s_prefix[b] <= gpos (requests without stages are skipped)
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if (s_prefix[mid] <= w) lo = mid; else hi = mid;
+            if (s_prefix[mid] <= gpos) lo = mid; else hi = mid;
         }
         it.b = lo;
-        it.item = w;
         it.len = p.seq_lens[lo];
-        const int st = (it.len + SK - 1) / SK;
-        it.nchunks = (st + chunk_stages - 1) / chunk_stages;
-        const int per = (st + it.nchunks - 1) / it.nchunks;
-        const int c = w - s_prefix[lo];
-        it.s_begin = c * per;
-        it.s_end = min(it.s_begin + per, st);
+        const int first = s_prefix[lo];
+        const int st = s_prefix[lo + 1] - first;
+        it.s_begin = gpos - first;
+        it.s_end = min(st, it.s_begin + (g_end - gpos));
+        const int c0 = first / per;
+        it.nchunks = (first + st - 1) / per - c0 + 1;   // CTAs that share this request
+        it.first_slot = lo + c0;
+        it.item = lo + static_cast<int>(blockIdx.x);
         return it;
     };
 
@@ -173,8 +163,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if (warp == kConsumerWarps) {
         // ================= producer warp =================
         const uint32_t copy_bytes = static_cast<uint32_t>(p.kpc) * Hkv * 128u;  // one half-tile box
-        for (int w = blockIdx.x; w < total_items && !failed; w += gridDim.x) {
-            const ItemInfo it = locate(w);
+        for (int gpos = g_begin; gpos < g_end && !failed;) {
+            const ItemInfo it = locate(gpos);
+            gpos += it.s_end - it.s_begin;
             const int32_t* pt_row = p.page_table + static_cast<int64_t>(p.table_idx[it.b]) * p.pt_stride;
             const int first_key = it.s_begin * SK;
             const int item_keys = min(it.len, it.s_end * SK) - first_key;
@@ -223,8 +214,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int g = lane >> 2, t = lane & 3;
     const int mi = lane >> 3, r8 = lane & 7;
 
-    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
-        const ItemInfo it = locate(w);
+    for (int gpos = g_begin; gpos < g_end;) {
+        const ItemInfo it = locate(gpos);
+        gpos += it.s_end - it.s_begin;
 
         // Query fragments: rows of the A operand are the G heads of this KV group.
         uint32_t qa[8][4];
@@ -396,7 +388,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (ticket == it.nchunks - 1) {
                 // This CTA finished the request's last item: merge all partials (read through
                 // L2 with ld.cg; the other CTAs' stores are visible after the ticket).
-                const int64_t part0 = static_cast<int64_t>(s_prefix[it.b]) * KG;
+                const int64_t part0 = static_cast<int64_t>(it.first_slot) * KG;
                 if (Hq * nparts <= kMergeTab && Hq <= kMergeHeads) {
                     // Phase 1: one warp per head computes the softmax weight of every partial.
                     for (int head = warp; head < Hq; head += kConsumerWarps) {
@@ -465,7 +457,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads) {
     const int kg = kConsumerWarps / kv_heads;
-    const int64_t items = static_cast<int64_t>(sm_count()) * kItemsPerCta + max_batch;
+    const int64_t items = static_cast<int64_t>(sm_count()) + max_batch;
     const int64_t parts = items * kg;
     return kMaxBatch * 4 + parts * q_heads * (kD + 2) * 4 + 256;
 }
@@ -482,7 +474,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
     const int64_t avail = workspace_bytes - kMaxBatch * 4 - 256;
     const int64_t per_item = static_cast<int64_t>(kg) * q_heads * (kD + 2) * 4;
     const int64_t max_items = avail / per_item;
-    if (max_items < static_cast<int64_t>(grid) * kItemsPerCta + batch) {
+    if (max_items < static_cast<int64_t>(grid) + batch) {
         set_last_error("attention_decode: workspace of %lld bytes is too small (need %lld)",
                        static_cast<long long>(workspace_bytes),
                        static_cast<long long>(decode_workspace_bytes(batch, q_heads, kv_heads)));

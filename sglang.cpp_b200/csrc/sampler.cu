@@ -288,6 +288,8 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
     }
     const float scale = 1.4426950408889634f / T;
     auto weight = [&](uint32_t key) { return exp2f((key_to_float(key) - lmax) * scale); };
+    // Mass of n tied entries (n may be 0, and then the key may be one no entry has).
+    auto tie_mass = [&](int n, uint32_t key) { return n > 0 ? static_cast<float>(n) * weight(key) : 0.f; };
     auto mass_ge = [&](uint32_t c) {
         float s = 0.f;
         for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
@@ -318,7 +320,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
     // ---- top-p over the top-k set ----
     float P = top_p ? top_p[row] : 1.0f;
     if (P < 1.0f) {
-        const float Z = mass_ge(thr + 1) + static_cast<float>(n_eq) * weight(thr);
+        const float Z = mass_ge(thr + 1) + tie_mass(n_eq, thr);
         const float budget = P * Z;
         uint32_t t = 0;  // largest key whose "this key and above" mass exceeds the budget
         for (int bit = 15; bit >= 0; --bit) {
@@ -330,13 +332,13 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
         if (t < thr) t = thr;
         const float m_full = t + 1 > kmax ? 0.f : mass_ge(t + 1);
         const int c_t = t == thr ? n_eq : count_eq(t);
-        int j = static_cast<int>(floorf((budget - m_full) / weight(t)));
+        int j = c_t > 0 ? static_cast<int>(floorf((budget - m_full) / weight(t))) : 0;
         j = max(0, min(j, c_t));
         if (m_full == 0.f && j == 0) j = 1;  // the first sorted entry is never dropped
         thr = t;
         n_eq = j;
     }
-    const float Zf = mass_ge(thr + 1) + static_cast<float>(n_eq) * weight(thr);
+    const float Zf = mass_ge(thr + 1) + tie_mass(n_eq, thr);
 
     // ---- draw ----
     const uint64_t seed = seeds ? seeds[row] : static_cast<uint64_t>(row);
