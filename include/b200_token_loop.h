@@ -185,6 +185,26 @@ B200_API int b200_attention_decode(void* out, const void* q, int64_t q_stride_to
                                    int head_dim, int page_size, float sm_scale, void* workspace,
                                    int64_t workspace_bytes, b200_stream_t stream);
 
+/* No counterpart in the reference.  The same computation as b200_attention_decode for callers
+ * that cannot allocate device memory when they need it (a process whose device-memory budget is
+ * already owned by one pool, or a step loop that must not run into cudaMalloc's device-wide
+ * synchronisation): there is no workspace argument, the split-KV scratch is an 8 MiB array built
+ * into the library image (every GPU that loads the library carries it until exit).  The call makes
+ * no cudaMalloc / cudaFree and no other allocating call.  Shapes whose partial results need more
+ * than that array (see b200_attention_decode_workspace_bytes; 64 requests x 16 query heads need
+ * under 2 MiB) are refused with B200_ERR_UNSUPPORTED.  The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress) with that device current; make that first call
+ * before any stream capture begins.  All calls share the one array and it keeps the previous
+ * call's contents (the call clears the words that must start at zero): two calls whose kernels
+ * overlap on the GPU race. */
+B200_API int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_token,
+                                           int64_t q_stride_head, const void* k_cache,
+                                           const void* v_cache, int64_t num_slots,
+                                           const int32_t* page_table, int64_t page_table_stride,
+                                           const int32_t* table_idx, const int32_t* seq_lens,
+                                           int batch, int q_heads, int kv_heads, int head_dim,
+                                           int page_size, float sm_scale, b200_stream_t stream);
+
 /* FlashInferBackend::forward for a prefill (extend) batch
  * (src/attention/flashinfer_backend.cu:596-678): causal attention of ragged
  * query rows against paged keys.  Request b owns query rows

@@ -60,6 +60,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_linear": (_I, [_P, _P, _P, _P, _I, _I, _I, _L, _I, _P]),
     "b200_attention_decode_workspace_bytes": (_L, [_I, _I, _I, _I]),
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
+    "b200_attention_decode_noalloc": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
     "b200_sample": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, ctypes.c_uint64, _P, _P]),

@@ -21,6 +21,8 @@
 //     across item boundaries, so there is no pipeline bubble between items.
 //   * every warp writes an (m, l, O) partial; the CTA that finishes a request's
 //     last item merges the partials (threadfence + atomic ticket) and writes bf16.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tensormap.cuh"
@@ -589,6 +591,102 @@ int b200_attention_decode(void* out, const void* q, int64_t q_stride_token, int6
                                          page_table, page_table_stride, table_idx, seq_lens, batch,
                                          q_heads, kv_heads, page_size, sm_scale, workspace,
                                          workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ============================================================================
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need
+// attention: a serving process whose whole device-memory budget has already been
+// handed to one pool (the reference sizes its KV pool from cudaMemGetInfo and lets
+// LibTorch's caching allocator own the rest), or a step loop that must not meet
+// cudaMalloc's device-wide synchronisation.  For them the split-KV scratch of the
+// decode kernel lives in the library image itself: a file-scope __device__ array of
+// kNoAllocScratchBytes that every GPU which loads the library carries until exit.
+// ============================================================================
+namespace b200 {
+namespace {
+
+constexpr int64_t kNoAllocScratchBytes = 8ll << 20;  // the stated maximum: 8 MiB per GPU
+constexpr int64_t kNoAllocStatusBytes = 256;         // tail of the array: the kernel's status words
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {};  // device address of the array, per device
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_token,
+                                  int64_t q_stride_head, const void* k_cache, const void* v_cache,
+                                  int64_t num_slots, const int32_t* page_table,
+                                  int64_t page_table_stride, const int32_t* table_idx,
+                                  const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
+                                  int head_dim, int page_size, float sm_scale, b200_stream_t stream) {
+    using namespace b200;
+    B200_CHECK_ARG(batch == 0 || (out && q && k_cache && v_cache && page_table && table_idx && seq_lens),
+                   "attention_decode_noalloc: NULL tensor");
+    B200_CHECK_ARG(head_dim == kD, "attention_decode_noalloc: head_dim must be 128");
+    B200_CHECK_ARG(batch >= 0 && batch <= kMaxBatch, "attention_decode_noalloc: batch must be in [0, 1024]");
+    B200_CHECK_ARG(kv_heads >= 1 && kv_heads <= 8 && (8 % kv_heads) == 0,
+                   "attention_decode_noalloc: kv_heads (per rank) must be 1, 2, 4 or 8");
+    B200_CHECK_ARG(q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
+                   "attention_decode_noalloc: q_heads must be a multiple of kv_heads with group size <= 16");
+    B200_CHECK_ARG(page_size >= 1 && (page_size & (page_size - 1)) == 0,
+                   "attention_decode_noalloc: page_size must be a power of two");
+    B200_CHECK_ARG(q_stride_token % 2 == 0 && q_stride_head % 2 == 0,
+                   "attention_decode_noalloc: q strides must be even");
+    B200_CHECK_ARG(num_slots > 0, "attention_decode_noalloc: num_slots must be positive");
+    if (batch == 0) return B200_OK;
+
+    // The built-in scratch has a fixed size: refuse shapes whose partials do not fit.
+    const int64_t usable = kNoAllocScratchBytes - kNoAllocStatusBytes;
+    const int64_t need = decode_workspace_bytes(batch, q_heads, kv_heads);
+    if (need > usable) {
+        set_last_error("attention_decode_noalloc: batch %d with %d q heads / %d kv heads needs %lld bytes of "
+                       "scratch, the built-in array holds %lld; use b200_attention_decode with a caller "
+                       "workspace instead",
+                       batch, q_heads, kv_heads, static_cast<long long>(need), static_cast<long long>(usable));
+        return B200_ERR_UNSUPPORTED;
+    }
+
+    // Set-up, once per device, with that device current: the array's name is only a host-side
+    // handle, so ask the runtime for its device address and hand THAT to the kernel.
+    int dev = 0;
+    B200_CHECK_CUDA(cudaGetDevice(&dev));
+    B200_CHECK_ARG(dev >= 0 && dev < kNoAllocMaxDevices, "attention_decode_noalloc: device index out of range");
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {
+            void* ptr = nullptr;
+            B200_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+            g_noalloc_ptr[dev] = ptr;
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    int* status = reinterpret_cast<int*>(base + usable);
+    // The array keeps whatever the previous call left.  The per-request tickets must start at
+    // zero (a call that ended normally leaves them so, one that was cut short may not) and so must
+    // the status words; partial sums are always written before they are read.
+    B200_CHECK_CUDA(cudaMemsetAsync(base, 0, kMaxBatch * sizeof(int), s));
+    B200_CHECK_CUDA(cudaMemsetAsync(status, 0, kNoAllocStatusBytes, s));
+
+    CUtensorMap tk, tv;
+    int err = make_kv_tmap(&tk, k_cache, num_slots, kv_heads, page_size);
+    if (err != B200_OK) return err;
+    err = make_kv_tmap(&tv, v_cache, num_slots, kv_heads, page_size);
+    if (err != B200_OK) return err;
+    return launch_attention_decode(out, q, q_stride_token, q_stride_head, tk, tv, num_slots, page_table,
+                                   page_table_stride, table_idx, seq_lens, batch, q_heads, kv_heads,
+                                   page_size, sm_scale, base, usable, status, s);
 }
 
 }  // extern "C"
