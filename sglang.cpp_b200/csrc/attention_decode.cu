@@ -101,6 +101,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
         tma_prefetch_desc(&tmap_v);
     }
 
+    pdl_launch_dependents();
     pdl_wait_prior();
 
     // ---- device-side split ----

@@ -69,6 +69,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
             z[i] = make_uint4(0, 0, 0, 0);
         fence_proxy_async_smem();
     }
+    pdl_launch_dependents();
     pdl_wait_prior();
     __syncthreads();
 

@@ -16,6 +16,7 @@ template <bool GELU>
 __global__ void __launch_bounds__(256)
 act_and_mul_kernel(uint4* __restrict__ out, const uint4* __restrict__ in, int64_t tokens,
                    int vec_per_row) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int64_t total = tokens * vec_per_row;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -41,6 +42,7 @@ act_and_mul_kernel(uint4* __restrict__ out, const uint4* __restrict__ in, int64_
 __global__ void __launch_bounds__(128)
 embedding_kernel(uint4* __restrict__ out, const uint4* __restrict__ table,
                  const int32_t* __restrict__ ids, int vec_per_row, int vocab, int* status) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int64_t t = blockIdx.x;
     const int id = ids[t];

@@ -34,6 +34,7 @@ __global__ void prepare_tokens_kernel(const int32_t* __restrict__ meta, int Bp, 
                                       int pt_rows, int pt_cols, int32_t* __restrict__ positions,
                                       int32_t* __restrict__ out_loc, int32_t* __restrict__ input_ids,
                                       int32_t* __restrict__ seq_lens) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int32_t* table_idx = meta;
     const int32_t* cached = meta + Bp;
@@ -57,6 +58,7 @@ __global__ void prepare_tokens_kernel(const int32_t* __restrict__ meta, int Bp, 
 // dst[b, :] = src[qo_indptr[b + 1] - 1, :]   (select_lm_head_input, src/models/utils.cc:8-19)
 __global__ void select_last_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                         const int32_t* __restrict__ qo, int vec_per_row) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int b = blockIdx.x;
     const int64_t row = qo[b + 1] - 1;
@@ -68,6 +70,7 @@ __global__ void scatter_int32_kernel(int32_t* __restrict__ table, int64_t rows, 
                                      int64_t cols, const int32_t* __restrict__ r,
                                      const int32_t* __restrict__ p, const int32_t* __restrict__ v,
                                      int64_t count) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= count) return;

@@ -167,6 +167,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __shared__ __align__(8) uint64_t tmem_full_bar;
     __shared__ uint32_t tmem_base_slot;
 
+    // Let the next kernel in the stream become resident right away: its set-up and weight loads
+    // then overlap this kernel (it still waits for this grid to finish before touching its input).
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int nt = p.nt;
@@ -289,7 +292,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (!mbar_wait_bounded(smem_u32(&tmem_full_bar), 0, p.status, 103)) failed = true;
         tc_fence_after();
     }
-    pdl_launch_dependents();
 
     for (int r = 0; r < nrounds; ++r) {
         float* buf = xbuf + (r & 1) * round_floats;

@@ -38,6 +38,7 @@ rmsnorm_kernel(__nv_bfloat16* out, const __nv_bfloat16* x_in,
     uint4* ov = reinterpret_cast<uint4*>(out + row * hidden);
     const uint4* wv = reinterpret_cast<const uint4*>(weight);
 
+    pdl_launch_dependents();
     pdl_wait_prior();
 
     float vals[kNormVecPerThread][8];
@@ -105,8 +106,6 @@ rmsnorm_kernel(__nv_bfloat16* out, const __nv_bfloat16* x_in,
 
     ss = block_sum(ss, red);
     const float scale = rsqrtf(ss / static_cast<float>(hidden) + eps);
-
-    pdl_launch_dependents();
 
 #pragma unroll
     for (int i = 0; i < kNormVecPerThread; ++i) {

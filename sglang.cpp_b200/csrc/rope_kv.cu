@@ -92,6 +92,7 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
     const int rows_per_token = q_heads + 2 * kv_heads;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
 
+    pdl_launch_dependents();
     pdl_wait_prior();
     if (row >= static_cast<int64_t>(tokens) * rows_per_token) return;
     const int64_t t = row / rows_per_token;

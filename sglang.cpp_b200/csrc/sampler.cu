@@ -23,6 +23,7 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
                    int64_t ld) {
     __shared__ float s_v[16];
     __shared__ int s_i[16];
+    pdl_launch_dependents();
     pdl_wait_prior();
     const __nv_bfloat16* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
     MaxIdx best{-INFINITY, 0x7fffffff};
@@ -228,6 +229,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
               uint64_t step_index, uint8_t* __restrict__ mask) {
     __shared__ SampleSmem sm;
     __shared__ int s_chosen;
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int row = blockIdx.x;
     const uint4* rv = reinterpret_cast<const uint4*>(logits + static_cast<int64_t>(row) * ld);
