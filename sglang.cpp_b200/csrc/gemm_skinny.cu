@@ -128,6 +128,9 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank
     return v;
 }
 
+__device__ __forceinline__ void st_dsmem_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float4 v;
@@ -144,7 +147,20 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
 }
 
+// Optional timeline capture for tuning (compiled out unless B200_GEMM_TRACE is defined): the
+// first thread of each role records %globaltimer at fixed points into p.trace[cta][point].
+#ifdef B200_GEMM_TRACE
+#define B200_TRACE(i)                                                                         \
+    do {                                                                                      \
+        if (p.trace && (threadIdx.x & 31) == 0)                                               \
+            p.trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = global_timer_ns();     \
+    } while (0)
+#else
+#define B200_TRACE(i) do { } while (0)
+#endif
+
 struct SkinnyParams {
+    unsigned long long* trace;  // NULL unless tracing
     __nv_bfloat16* y;          // [M, n_out]
     const __nv_bfloat16* bias; // [n_out] or NULL (plain epilogue only)
     int M;                     // rows of x / y
@@ -169,6 +185,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
     // Let the next kernel in the stream become resident right away: its set-up and weight loads
     // then overlap this kernel (it still waits for this grid to finish before touching its input).
+    B200_TRACE(0);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -208,6 +225,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    B200_TRACE(1);
 
     bool failed = false;
 
@@ -255,6 +273,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     break;
                 }
                 tc_fence_after();
+                if (i == 0) B200_TRACE(2);
                 const uint32_t a0 = smem_base + s * stage_bytes;
                 const uint32_t b0 = a0 + NUM_A * a_bytes;
 #pragma unroll
@@ -279,22 +298,36 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __syncwarp();
 
     // ---- epilogue: every warp walks the same sequence of cluster barriers ----
+    // Split-K exchange is PUSH based: rank r owns F = 128/split features of the tile.  Every CTA
+    // stores its partial sums for those features straight into rank r's exchange buffer (remote
+    // shared-memory stores do not stall the sender), one cluster barrier makes them visible, and
+    // the owner reduces from its own shared memory in rank order.  Nobody reads or writes a
+    // peer's memory after the last barrier, so CTAs leave independently.  The exchange buffer is
+    // a region of its own behind the operand stages: a peer may push while this CTA's MMAs still
+    // read the stages.
     const bool is_epi = warp >= 2;
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
     const int feat_local = q * 32 + lane;         // feature row inside the tile
-    float* xbuf = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
-    const uint32_t xbuf_addr = smem_base;
     const int cpr = nt < kRoundCols ? nt : kRoundCols;  // token columns per exchange round
     const int nrounds = nt / cpr;
-    const int round_floats = NUM_A * cpr * kTileN;
+    const int F = kTileN / static_cast<int>(split);     // features owned by one rank
+    const uint32_t round_bytes = static_cast<uint32_t>(NUM_A) * cpr * kTileN * 4u;
+    const uint32_t xbuf_addr = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+    const float* xbuf = reinterpret_cast<const float*>(smem_raw + (xbuf_addr - smem_u32(smem_raw)));
+    // Where this thread's feature lives: owner rank and the base of that rank's buffer.
+    const uint32_t owner = static_cast<uint32_t>(feat_local / F);
+    const uint32_t fl = static_cast<uint32_t>(feat_local % F);
+    uint32_t remote_base = 0;
+    if (split > 1) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_base) : "r"(xbuf_addr), "r"(owner));
 
     if (is_epi) {
         if (!mbar_wait_bounded(smem_u32(&tmem_full_bar), 0, p.status, 103)) failed = true;
         tc_fence_after();
+        B200_TRACE(3);
     }
 
     for (int r = 0; r < nrounds; ++r) {
-        float* buf = xbuf + (r & 1) * round_floats;
+        const uint32_t buf_off = static_cast<uint32_t>(r & 1) * round_bytes;
         if (is_epi) {
             for (int cc = 0; cc < cpr / kChunkCols; ++cc) {
                 const int c = r * (cpr / kChunkCols) + cc;
@@ -305,6 +338,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     tmem_ld_32x32b_x32(taddr, g);
                     if (NUM_A == 2) tmem_ld_32x32b_x32(taddr + nt, u);
                     tmem_ld_wait();
+                    B200_TRACE(4);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -333,12 +367,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                         }
                     }
                 } else {
-                    // Publish this CTA's partial sums: [accumulator][column][feature].
+                    // owner layout: [source rank][accumulator][column][owned feature]
+                    const uint32_t dst0 = remote_base + buf_off +
+                                          ((rank * NUM_A * cpr + cc * kChunkCols) * F + fl) * 4u;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        buf[(cc * kChunkCols + j) * kTileN + feat_local] = __uint_as_float(g[j]);
+                        st_dsmem_f32(dst0 + static_cast<uint32_t>(j * F) * 4u, __uint_as_float(g[j]));
                         if (NUM_A == 2)
-                            buf[(cpr + cc * kChunkCols + j) * kTileN + feat_local] = __uint_as_float(u[j]);
+                            st_dsmem_f32(dst0 + static_cast<uint32_t>((cpr + j) * F) * 4u, __uint_as_float(u[j]));
                     }
                 }
             }
@@ -346,28 +382,25 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (split == 1) continue;
 
         cluster_sync_all();
+        B200_TRACE(5);
         if (is_epi) {
-            // This rank owns F features of the tile; four of them per thread and column,
-            // summed over the ranks in rank order with 16-byte distributed-shared loads.
-            const int F = kTileN / static_cast<int>(split);
             const int f4_per_col = F / 4;
             const int te = (warp - 2) * 32 + lane;  // 0..127
-            const uint32_t cbase = xbuf_addr + static_cast<uint32_t>((r & 1) * round_floats) * 4u;
+            const float* rb = xbuf + buf_off / 4u;
             for (int i = te; i < cpr * f4_per_col; i += 128) {
                 const int col = i / f4_per_col;
-                const int f = static_cast<int>(rank) * F + (i - col * f4_per_col) * 4;
+                const int f = (i - col * f4_per_col) * 4;   // owned-feature index
                 float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), su = sg;
                 for (uint32_t rr = 0; rr < split; ++rr) {
-                    const float4 a = ld_dsmem_f32x4(cbase + static_cast<uint32_t>(col * kTileN + f) * 4u, rr);
+                    const float4 a = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + col) * F + f));
                     sg.x += a.x; sg.y += a.y; sg.z += a.z; sg.w += a.w;
                     if (NUM_A == 2) {
-                        const float4 b2 = ld_dsmem_f32x4(
-                            cbase + static_cast<uint32_t>((cpr + col) * kTileN + f) * 4u, rr);
+                        const float4 b2 = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + cpr + col) * F + f));
                         su.x += b2.x; su.y += b2.y; su.z += b2.z; su.w += b2.w;
                     }
                 }
                 const int m = r * cpr + col;
-                const int n = n0 + f;
+                const int n = n0 + static_cast<int>(rank) * F + f;
                 if (m < p.M && n < p.n_out) {
                     float v[4] = {sg.x, sg.y, sg.z, sg.w};
                     const float uu[4] = {su.x, su.y, su.z, su.w};
@@ -386,11 +419,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
         }
     }
-    if (split > 1) cluster_sync_all();  // nobody leaves while a peer may still read its chunk
+    B200_TRACE(6);
+    B200_TRACE(6);
 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+    B200_TRACE(7);
 }
 
 struct TmapCacheEntry {
@@ -440,13 +475,15 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     const int n_tiles = div_ceil(n_out, kTileN);
     const int num_a = gated ? 2 : 1;
 
-    // K split: about 1.5 CTAs per SM in total, at most 8 ranks (portable cluster size).
+    // K split: up to one CTA per SM in total, at most 8 ranks (portable cluster size).
     int split = 1;
     const int forced = env_int("B200_GEMM_SPLIT", 0);
     if (forced > 0) {
         split = forced;
     } else {
-        const int budget = sm_count() * 3 / 2;
+        // One CTA per SM at most: a CTA holds its whole K slice plus the exchange buffer, so two
+        // rarely fit on an SM, and a second wave would double the kernel's time.
+        const int budget = sm_count();
         while (split < 8 && n_tiles * split * 2 <= budget && split * 2 <= kb_total) split *= 2;
     }
     const int kbp = div_ceil(kb_total, split);
@@ -457,10 +494,10 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     const uint32_t smem_limit = 200 * 1024;
     int stages = kbp < kMaxStages ? kbp : kMaxStages;
     while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
-    uint32_t smem_bytes = stages * stage_bytes;
-    if (smem_bytes < exch_bytes) smem_bytes = exch_bytes;
+    while (stages > 1 && stages * stage_bytes + exch_bytes > smem_limit) --stages;
+    uint32_t smem_bytes = stages * stage_bytes + exch_bytes;
     smem_bytes += 1024;  // alignment slack
-    if (stage_bytes > smem_limit) {
+    if (stage_bytes + exch_bytes > smem_limit) {
         set_last_error("linear: one pipeline stage (%u bytes) does not fit in shared memory",
                        stage_bytes);
         return B200_ERR_UNSUPPORTED;
@@ -475,6 +512,10 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     if (err != B200_OK) return err;
 
     SkinnyParams p;
+    p.trace = nullptr;
+#ifdef B200_GEMM_TRACE
+    p.trace = reinterpret_cast<unsigned long long*>(getenv("B200_GEMM_TRACE_PTR") ? strtoull(getenv("B200_GEMM_TRACE_PTR"), nullptr, 0) : 0ull);
+#endif
     p.y = static_cast<__nv_bfloat16*>(y);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.M = M;
