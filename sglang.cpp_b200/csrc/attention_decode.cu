@@ -79,8 +79,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __shared__ __align__(8) uint64_t full_bar[kStages];
     __shared__ __align__(8) uint64_t empty_bar[kStages];
     __shared__ int s_prefix[kMaxBatch + 1];  // exclusive scan of items per request
+    __shared__ int s_len[kMaxBatch];         // seq_lens, read once
     __shared__ int s_slot_tab[kSlotTab];
-    __shared__ int s_ticket;
+    __shared__ int s_pend[2][4];             // cross-CTA items of this CTA: b, ticket, nchunks, first_slot
     __shared__ float s_mw[kMergeTab];
     __shared__ float s_minv[kMergeHeads];
 
@@ -121,7 +122,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 const int t = __shfl_up_sync(0xffffffffu, incl, o);
                 if (lane >= o) incl += t;
             }
-            if (b < B) s_prefix[b] = carry + incl - n;
+            if (b < B) {
+                s_prefix[b] = carry + incl - n;
+                s_len[b] = p.seq_lens[b];
+            }
             carry += __shfl_sync(0xffffffffu, incl, 31);
         }
         if (lane == 0) s_prefix[B] = carry;
@@ -146,7 +150,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (s_prefix[mid] <= gpos) lo = mid; else hi = mid;
         }
         it.b = lo;
-        it.len = p.seq_lens[lo];
+        it.len = s_len[lo];
         const int first = s_prefix[lo];
         const int st = s_prefix[lo + 1] - first;
         it.s_begin = gpos - first;
@@ -217,25 +221,96 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int g = lane >> 2, t = lane & 3;
     const int mi = lane >> 3, r8 = lane & 7;
 
-    for (int gpos = g_begin; gpos < g_end;) {
-        const ItemInfo it = locate(gpos);
-        gpos += it.s_end - it.s_begin;
-
-        // Query fragments: rows of the A operand are the G heads of this KV group.
-        uint32_t qa[8][4];
-        {
-            const __nv_bfloat16* q0 = p.q + it.b * p.q_st + static_cast<int64_t>(h * G + g) * p.q_sh;
-            const __nv_bfloat16* q1 = q0 + 8 * p.q_sh;
-            const bool r0 = g < G, r1 = (g + 8) < G;
+    // Query fragments: rows of the A operand are the G heads of this KV group.
+    uint32_t qa[8][4];
+    auto load_q = [&](int b) {
+        const __nv_bfloat16* q0 = p.q + b * p.q_st + static_cast<int64_t>(h * G + g) * p.q_sh;
+        const __nv_bfloat16* q1 = q0 + 8 * p.q_sh;
+        const bool r0 = g < G, r1 = (g + 8) < G;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const int d0 = ks * 16 + 2 * t;
-                qa[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0) : 0u;
-                qa[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0 + 8) : 0u;
-                qa[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0) : 0u;
-                qa[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0 + 8) : 0u;
+        for (int ks = 0; ks < 8; ++ks) {
+            const int d0 = ks * 16 + 2 * t;
+            qa[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0) : 0u;
+            qa[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + d0 + 8) : 0u;
+            qa[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0) : 0u;
+            qa[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + d0 + 8) : 0u;
+        }
+    };
+    const int Hq = p.q_heads;
+
+    // Merge of all partials of request b (every consumer thread takes part).
+    auto merge_request = [&](int b, int nparts, int first_slot) {
+        const int64_t part0 = static_cast<int64_t>(first_slot) * KG;
+        consumer_bar();  // the staging arrays may still be read by a previous merge
+        if (Hq * nparts <= kMergeTab && Hq <= kMergeHeads) {
+            // Phase 1: one warp per head computes the softmax weight of every partial.
+            for (int head = warp; head < Hq; head += kConsumerWarps) {
+                float mloc = -INFINITY;
+                for (int pp = lane; pp < nparts; pp += 32)
+                    mloc = fmaxf(mloc, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                const float M = warp_max(mloc);
+                float lsum = 0.f;
+                for (int pp = lane; pp < nparts; pp += 32) {
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(
+                        p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                    const float wgt = exp2f(ml.x - M);
+                    s_mw[head * nparts + pp] = wgt;
+                    lsum += ml.y * wgt;
+                }
+                const float Lt = warp_sum(lsum);
+                if (lane == 0) s_minv[head] = Lt > 0.f ? 1.f / Lt : 0.f;
+            }
+            consumer_bar();
+            // Phase 2: independent, unrolled loads of the partial outputs.
+            for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
+                const int head = idx / (kD / 2), dp = idx % (kD / 2);
+                const float* wrow = s_mw + head * nparts;
+                const float* src = p.ws_o + (part0 * Hq + head) * kD + dp * 2;
+                const int64_t pstride = static_cast<int64_t>(Hq) * kD;
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+                for (int pp = 0; pp < nparts; ++pp) {
+                    const float2 ov = __ldcg(reinterpret_cast<const float2*>(src + pp * pstride));
+                    a0 += ov.x * wrow[pp];
+                    a1 += ov.y * wrow[pp];
+                }
+                const float inv = s_minv[head];
+                *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(b) * Hq + head) * kD + dp * 2) =
+                    pack_bf16(a0 * inv, a1 * inv);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
+                const int head = idx / (kD / 2), dp = idx % (kD / 2);
+                float M = -INFINITY;
+                for (int pp = 0; pp < nparts; ++pp)
+                    M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
+                float L = 0.f, a0 = 0.f, a1 = 0.f;
+                for (int pp = 0; pp < nparts; ++pp) {
+                    const int64_t ph = (part0 + pp) * Hq + head;
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
+                    const float wgt = exp2f(ml.x - M);
+                    const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
+                    L += ml.y * wgt;
+                    a0 += ov.x * wgt;
+                    a1 += ov.y * wgt;
+                }
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+                *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(b) * Hq + head) * kD + dp * 2) =
+                    pack_bf16(a0 * inv, a1 * inv);
             }
         }
+    };
+
+    int npend = 0;  // cross-CTA items whose merge is decided after this CTA's last stage
+    int gpos = g_begin;
+    bool have = gpos < g_end;
+    ItemInfo it = {};
+    if (have) {
+        it = locate(gpos);
+        load_q(it.b);
+    }
+    while (have) {
+        gpos += it.s_end - it.s_begin;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
         float o[16][4];
 #pragma unroll
@@ -339,13 +414,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[slot]));
         }
 
+        // The next item's queries are requested now, so their latency hides behind this
+        // item's epilogue (the fragments of the finished item are no longer needed).
+        const bool has_next = gpos < g_end;
+        ItemInfo nx = it;
+        if (has_next) {
+            nx = locate(gpos);
+            load_q(nx.b);
+        }
+
         // ---- item epilogue ----
         l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
         const int nparts = it.nchunks * KG;
-        const int Hq = p.q_heads;
         if (nparts == 1) {
             // Single partial: normalise and store bf16 directly.
 #pragma unroll
@@ -378,80 +461,41 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                             make_float2(rr ? m1 : m0, rr ? l1 : l0);
                 }
             }
-            // Release: the barrier orders every thread's partial stores before thread 0's
-            // fence, and the fence orders them before the ticket (fences are cumulative).
-            consumer_bar();
-            if (threadIdx.x == 0) {
+            if (it.nchunks == 1) {
+                // All partials of the request are this CTA's own (several key groups per stage).
                 __threadfence();
-                s_ticket = atomicAdd(&p.counters[it.b], 1);
-                __threadfence();
-            }
-            consumer_bar();
-            const int ticket = s_ticket;
-            if (ticket == it.nchunks - 1) {
-                // This CTA finished the request's last item: merge all partials (read through
-                // L2 with ld.cg; the other CTAs' stores are visible after the ticket).
-                const int64_t part0 = static_cast<int64_t>(it.first_slot) * KG;
-                if (Hq * nparts <= kMergeTab && Hq <= kMergeHeads) {
-                    // Phase 1: one warp per head computes the softmax weight of every partial.
-                    for (int head = warp; head < Hq; head += kConsumerWarps) {
-                        float mloc = -INFINITY;
-                        for (int pp = lane; pp < nparts; pp += 32)
-                            mloc = fmaxf(mloc, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                        const float M = warp_max(mloc);
-                        float lsum = 0.f;
-                        for (int pp = lane; pp < nparts; pp += 32) {
-                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(
-                                p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                            const float wgt = exp2f(ml.x - M);
-                            s_mw[head * nparts + pp] = wgt;
-                            lsum += ml.y * wgt;
-                        }
-                        const float Lt = warp_sum(lsum);
-                        if (lane == 0) s_minv[head] = Lt > 0.f ? 1.f / Lt : 0.f;
-                    }
-                    consumer_bar();
-                    // Phase 2: independent, unrolled loads of the partial outputs.
-                    for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
-                        const int head = idx / (kD / 2), dp = idx % (kD / 2);
-                        const float* wrow = s_mw + head * nparts;
-                        const float* src = p.ws_o + (part0 * Hq + head) * kD + dp * 2;
-                        const int64_t pstride = static_cast<int64_t>(Hq) * kD;
-                        float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-                        for (int pp = 0; pp < nparts; ++pp) {
-                            const float2 ov = __ldcg(reinterpret_cast<const float2*>(src + pp * pstride));
-                            a0 += ov.x * wrow[pp];
-                            a1 += ov.y * wrow[pp];
-                        }
-                        const float inv = s_minv[head];
-                        *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
-                            pack_bf16(a0 * inv, a1 * inv);
-                    }
-                } else {
-                    for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
-                        const int head = idx / (kD / 2), dp = idx % (kD / 2);
-                        float M = -INFINITY;
-                        for (int pp = 0; pp < nparts; ++pp)
-                            M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                        float L = 0.f, a0 = 0.f, a1 = 0.f;
-                        for (int pp = 0; pp < nparts; ++pp) {
-                            const int64_t ph = (part0 + pp) * Hq + head;
-                            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
-                            const float wgt = exp2f(ml.x - M);
-                            const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
-                            L += ml.y * wgt;
-                            a0 += ov.x * wgt;
-                            a1 += ov.y * wgt;
-                        }
-                        const float inv = L > 0.f ? 1.f / L : 0.f;
-                        *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(it.b) * Hq + head) * kD + dp * 2) =
-                            pack_bf16(a0 * inv, a1 * inv);
-                    }
+                merge_request(it.b, nparts, it.first_slot);
+            } else {
+                // The request is shared with other CTAs.  Release: the barrier orders every
+                // thread's partial stores before thread 0's fence, the fence orders them before
+                // the ticket (fences are cumulative).  Nobody waits for the ticket here: whether
+                // this CTA has to merge is looked at after its last stage, so the stage pipeline
+                // keeps running.  At most two items of a contiguous run cross CTAs.
+                consumer_bar();
+                if (threadIdx.x == 0 && npend < 2) {
+                    __threadfence();
+                    s_pend[npend][0] = it.b;
+                    s_pend[npend][1] = atomicAdd(&p.counters[it.b], 1);
+                    s_pend[npend][2] = it.nchunks;
+                    s_pend[npend][3] = it.first_slot;
                 }
-                if (threadIdx.x == 0) p.counters[it.b] = 0;
+                ++npend;
             }
-            consumer_bar();  // s_ticket is reused by the next item
+        }
+        have = has_next;
+        it = nx;
+    }
+
+    // ---- deferred merges: requests for which this CTA delivered the last partial ----
+    if (npend > 0) {
+        consumer_bar();
+        for (int k = 0; k < min(npend, 2); ++k) {
+            const int b = s_pend[k][0], ticket = s_pend[k][1], nchunks = s_pend[k][2];
+            if (ticket == nchunks - 1) {
+                __threadfence();  // the other CTAs' partials are visible once the last ticket is
+                merge_request(b, nchunks * KG, s_pend[k][3]);
+                if (threadIdx.x == 0) p.counters[b] = 0;
+            }
         }
     }
 }

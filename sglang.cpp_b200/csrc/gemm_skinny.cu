@@ -493,6 +493,10 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     const uint32_t exch_bytes = split > 1 ? (nt > cpr ? 2u : 1u) * num_a * cpr * kTileN * 4u : 0u;
     const uint32_t smem_limit = 200 * 1024;
     int stages = kbp < kMaxStages ? kbp : kMaxStages;
+    // More tiles than SMs (lm_head): keep the ring small enough for two CTAs per SM, so one CTA's
+    // start-up and epilogue overlap the other's streaming.
+    if (n_tiles * split > sm_count())
+        while (stages > 2 && stages * stage_bytes + exch_bytes > 100 * 1024) --stages;
     while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
     while (stages > 1 && stages * stage_bytes + exch_bytes > smem_limit) --stages;
     uint32_t smem_bytes = stages * stage_bytes + exch_bytes;
