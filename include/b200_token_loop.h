@@ -149,7 +149,8 @@ enum {
     /* y[m, j] = silu(bf16(acc[m, j])) * bf16(acc[m, N/2 + j]), j < N/2: the
      * gate_up projection followed by silu_and_mul (src/models/utils.cc:41-57). */
     B200_EPILOGUE_SWIGLU = 1,
-    B200_EPILOGUE_GEGLU = 2
+    B200_EPILOGUE_GEGLU = 2,     /* tanh-approximated GELU, as gelu_and_mul (src/layers/activation.cu:11-13) */
+    B200_EPILOGUE_GEGLU_ERF = 3  /* exact GELU, as torch::gelu in MoELayer::forward (src/moe/moe.cc:80) */
 };
 
 /* LinearBase::forward (src/layers/linear.cc:24-26): y = x W^T (+ bias), bf16 in,
@@ -158,6 +159,32 @@ enum {
  * N/2 with a gated epilogue).  K must be a multiple of 64, N of 16. */
 B200_API int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, int N,
                          int K, int64_t ldx, int epilogue, b200_stream_t stream);
+
+/* ---- mixture of experts (include/sglang/moe/moe.h:9-35) -------------------- */
+
+/* Bytes of scratch b200_moe_forward needs (routing tables and the permuted activations). */
+B200_API int64_t b200_moe_workspace_bytes(int tokens, int num_experts, int top_k, int hidden_size,
+                                          int intermediate_size);
+
+/* The routing half of MoELayer::forward (src/moe/moe.cc:47-55): fp32 softmax of bf16 router
+ * logits [tokens, num_experts], top_k largest per token (lower expert index on ties), optional
+ * renormalisation w / (sum w + 1e-8), weights rounded to bf16 as the reference casts them.
+ * topk_ids int32 [tokens, top_k], topk_weights float [tokens, top_k], expert_counts int32
+ * [num_experts + 1] (histogram; cleared by the call). */
+B200_API int b200_moe_route(int32_t* topk_ids, float* topk_weights, int32_t* expert_counts,
+                            const void* router_logits, int tokens, int num_experts, int top_k,
+                            int renormalize, b200_stream_t stream);
+
+/* MoELayer::forward (src/moe/moe.cc:36-96) for tp_size 1 (the caller all-reduces under TP):
+ * out[t] = sum over the token's top_k experts e, in k order with bf16 accumulation, of
+ * w[t,k] * down_e(act(gate_e x_t) * up_e x_t).  hidden_states / out bf16 [tokens, hidden_size];
+ * gate_up_proj bf16 [E, 2*I, hidden]; down_proj bf16 [E, hidden, I]; activation 0 = silu,
+ * 1 = gelu (exact, as torch::gelu).  No host synchronisation: six launches. */
+B200_API int b200_moe_forward(void* out, const void* hidden_states, const void* router_logits,
+                              const void* gate_up_proj, const void* down_proj, int tokens,
+                              int num_experts, int top_k, int hidden_size, int intermediate_size,
+                              int renormalize, int activation, void* workspace,
+                              int64_t workspace_bytes, b200_stream_t stream);
 
 /* ---- attention (include/sglang/attention/backend.h:24-41) ------------------ */
 

@@ -58,6 +58,9 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_gather_int32_2d": (_I, [_P, _P, _L, _L, _L, _P, _P, _L, _P]),
     "b200_write_token_pool": (_I, [_P, _L, _L, _L, _P, _P, _P, _L, _P]),
     "b200_linear": (_I, [_P, _P, _P, _P, _I, _I, _I, _L, _I, _P]),
+    "b200_moe_workspace_bytes": (_L, [_I, _I, _I, _I, _I]),
+    "b200_moe_route": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "b200_moe_forward": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P]),
     "b200_attention_decode_workspace_bytes": (_L, [_I, _I, _I, _I]),
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
     "b200_attention_decode_noalloc": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P]),

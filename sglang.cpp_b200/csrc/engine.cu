@@ -127,6 +127,8 @@ struct b200_engine {
             *next_tokens = nullptr;
     void* attn_ws = nullptr;
     int64_t attn_ws_bytes = 0;
+    __nv_bfloat16* router_logits = nullptr;
+    void* moe_ws = nullptr;
 
     // per-step metadata: pinned staging + device mirror
     int32_t* meta_host = nullptr;
@@ -280,8 +282,14 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, L.post_norm, T, hidden, m.rms_norm_eps,
                                           round_first, s));
         if (m.num_experts > 0) {
-            set_last_error("engine: MoE layers are not wired into the step runner yet");
-            return B200_ERR_UNSUPPORTED;
+            // MoEMLP::forward (src/models/utils.cc:82-91): router logits, then the expert layer.
+            B200_TRY(launch_linear(e->router_logits, e->x, L.router, nullptr, T, m.num_experts, hidden, hidden,
+                                   B200_EPILOGUE_NONE, e->status, s));
+            B200_TRY(launch_moe_forward(e->x, e->x, e->router_logits, L.experts_gate_up, L.experts_down, T,
+                                        m.num_experts, m.num_experts_per_tok, hidden,
+                                        m.moe_intermediate_size / e->c.tp_size, m.norm_topk_prob,
+                                        m.hidden_act == 1 ? 1 : 0, e->moe_ws, e->status, s));
+            continue;
         }
         B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
                                e->status, s));
@@ -485,6 +493,13 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     E_TRY(named_alloc(e, &e->input_ids, "input_ids", Tm));
     E_TRY(named_alloc(e, &e->seq_lens, "seq_lens", e->max_batch));
     E_TRY(named_alloc(e, &e->next_tokens, "next_tokens", e->max_batch, true));
+    if (m.num_experts > 0) {
+        E_TRY(named_alloc(e, &e->router_logits, "router_logits", Tm * m.num_experts));
+        E_TRY(dev_alloc(e, &e->moe_ws,
+                        moe_workspace_bytes(static_cast<int>(Tm), m.num_experts, m.num_experts_per_tok, m.hidden_size,
+                                            m.moe_intermediate_size / c.tp_size),
+                        false));
+    }
     e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);
     E_TRY(dev_alloc(e, &e->attn_ws, e->attn_ws_bytes, true));
 

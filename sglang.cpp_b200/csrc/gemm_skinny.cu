@@ -143,6 +143,12 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gated_act(int epilogue, float g) {
+    if (epilogue == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
+    if (epilogue == B200_EPILOGUE_GEGLU_ERF) return gelu_erf_f(g);
+    return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+}
 __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
 }
@@ -171,12 +177,21 @@ struct SkinnyParams {
     int stages;                // shared-memory stages in the ring
     int epilogue;              // B200_EPILOGUE_*
     int* status;
+    // Grouped mode (expert GEMMs): blockIdx.z = group, blockIdx.y = 256-row slab of the group.
+    // Group g multiplies rows [offsets[g], offsets[g] + counts[g]) of x by rows
+    // [g * w_rows_per_group, ...) of w; counts / offsets live in device memory.
+    const int32_t* group_counts;
+    const int32_t* group_offsets;
+    int w_rows_per_group;
 };
 
 template <int NUM_A>
 __global__ void __launch_bounds__(kThreads, 1)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                   const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
+                   const __grid_constant__ CUtensorMap tmap_x,
+                   const __grid_constant__ CUtensorMap tmap_x64,
+                   const __grid_constant__ CUtensorMap tmap_x128,
+                   const __grid_constant__ CUtensorMap tmap_x256, const SkinnyParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -189,7 +204,25 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int nt = p.nt;
+    int nt = p.nt;          // accumulator columns = rows of the x box
+    int rows = p.M;         // valid rows of x / y handled by this CTA
+    int x_row0 = 0;         // first row of x and of y
+    int w_row0 = 0;         // first row of this group's weights
+    const CUtensorMap* tx = &tmap_x;
+    if (p.group_counts != nullptr) {
+        pdl_wait_prior();   // the group table comes from the kernel before this one
+        const int grp = blockIdx.z;
+        const int cnt = p.group_counts[grp];
+        const int m0 = static_cast<int>(blockIdx.y) * 256;
+        if (m0 >= cnt) return;  // whole CTA, before any barrier or TMEM use
+        rows = min(256, cnt - m0);
+        if (rows <= 32) { nt = 32; tx = &tmap_x; }
+        else if (rows <= 64) { nt = 64; tx = &tmap_x64; }
+        else if (rows <= 128) { nt = 128; tx = &tmap_x128; }
+        else { nt = 256; tx = &tmap_x256; }
+        x_row0 = p.group_offsets[grp] + m0;
+        w_row0 = grp * p.w_rows_per_group;
+    }
     const uint32_t a_bytes = kTileN * kBlockK * 2;            // 16 KB per weight tile
     const uint32_t b_bytes = static_cast<uint32_t>(nt) * kBlockK * 2;
     const uint32_t stage_bytes = NUM_A * a_bytes + b_bytes;
@@ -215,7 +248,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmap_w);
-        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(tx);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
@@ -238,8 +271,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const uint32_t dst = smem_base + i * stage_bytes;
                 const int kc = (kb_begin + i) * kBlockK;
                 mbar_arrive_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &tmap_w, kc, n0, bar);
-                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, p.up_row_offset + n0, bar);
+                tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
+                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
             }
             pdl_wait_prior();
             for (int i = 0; i < my_kb && !failed; ++i) {
@@ -254,11 +287,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                         break;
                     }
                     mbar_arrive_expect_tx(bar, stage_bytes);
-                    tma_load_2d(dst, &tmap_w, kc, n0, bar);
+                    tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
                     if (NUM_A == 2)
-                        tma_load_2d(dst + a_bytes, &tmap_w, kc, p.up_row_offset + n0, bar);
+                        tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
                 }
-                tma_load_2d(dst + NUM_A * a_bytes, &tmap_x, kc, 0, bar);
+                tma_load_2d(dst + NUM_A * a_bytes, tx, kc, x_row0, bar);
             }
         }
     } else if (warp == 1) {
@@ -353,16 +386,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int m = c * kChunkCols + j;
-                            if (m < p.M) {
+                            if (m < rows) {
                                 float v;
                                 if (NUM_A == 2) {
                                     const float gv = round_bf16(__uint_as_float(g[j]));
                                     const float uv = round_bf16(__uint_as_float(u[j]));
-                                    v = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                                    v = gated_act(p.epilogue, gv) * uv;
                                 } else {
                                     v = __uint_as_float(g[j]) + bias;
                                 }
-                                p.y[static_cast<int64_t>(m) * p.n_out + n] = __float2bfloat16_rn(v);
+                                p.y[static_cast<int64_t>(x_row0 + m) * p.n_out + n] = __float2bfloat16_rn(v);
                             }
                         }
                     }
@@ -401,20 +434,20 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 }
                 const int m = r * cpr + col;
                 const int n = n0 + static_cast<int>(rank) * F + f;
-                if (m < p.M && n < p.n_out) {
+                if (m < rows && n < p.n_out) {
                     float v[4] = {sg.x, sg.y, sg.z, sg.w};
                     const float uu[4] = {su.x, su.y, su.z, su.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         if (NUM_A == 2) {
                             const float gv = round_bf16(v[e]), uv = round_bf16(uu[e]);
-                            v[e] = (p.epilogue == B200_EPILOGUE_GEGLU ? gelu_tanh_f(gv) : silu_f(gv)) * uv;
+                            v[e] = gated_act(p.epilogue, gv) * uv;
                         } else if (p.bias) {
                             v[e] += __bfloat162float(p.bias[n + e]);
                         }
                     }
                     uint2 packed = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
-                    *reinterpret_cast<uint2*>(p.y + static_cast<int64_t>(m) * p.n_out + n) = packed;
+                    *reinterpret_cast<uint2*>(p.y + static_cast<int64_t>(x_row0 + m) * p.n_out + n) = packed;
                 }
             }
         }
@@ -530,12 +563,70 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.stages = stages;
     p.epilogue = epilogue;
     p.status = status;
+    p.group_counts = nullptr;
+    p.group_offsets = nullptr;
+    p.w_rows_per_group = 0;
 
     auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, split, 1), dim3(kThreads), smem_bytes, stream,
-                                  dim3(1, split, 1), tmap_w, tmap_x, p));
+                                  dim3(1, split, 1), tmap_w, tmap_x, tmap_x, tmap_x, tmap_x, p));
+    return B200_OK;
+}
+
+// Grouped GEMM for expert layers: group g multiplies rows [offsets[g], offsets[g] + counts[g]) of
+// x [total_rows, K] by w[g] ([N, K], groups stacked) into the same rows of y.  counts / offsets
+// are device arrays (no host synchronisation); max_rows_per_group bounds any count.
+int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* counts,
+                        const int32_t* offsets, int num_groups, int max_rows_per_group,
+                        int64_t total_rows, int N, int K, int epilogue, int* status,
+                        cudaStream_t stream) {
+    const bool gated = epilogue != B200_EPILOGUE_NONE;
+    const int n_out = gated ? N / 2 : N;
+    const int num_a = gated ? 2 : 1;
+    const int kb_total = K / kBlockK;
+    const int n_tiles = div_ceil(n_out, kTileN);
+    const int slabs = div_ceil(max_rows_per_group, 256);
+    if (num_groups == 0 || slabs == 0 || total_rows == 0) return B200_OK;
+    int nt_max = 32;
+    while (nt_max < 256 && nt_max < max_rows_per_group) nt_max *= 2;
+    const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt_max * kBlockK * 2;
+    const uint32_t smem_limit = 200 * 1024;
+    int stages = kb_total < kMaxStages ? kb_total : kMaxStages;
+    while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
+    const uint32_t smem_bytes = stages * stage_bytes + 1024;
+
+    CUtensorMap tmap_w, tx[4];
+    int err = cached_tmap(&tmap_w, w, static_cast<uint64_t>(K), static_cast<uint64_t>(num_groups) * N,
+                          static_cast<uint64_t>(K) * 2, kBlockK, kTileN);
+    if (err != B200_OK) return err;
+    const uint32_t boxes[4] = {32, 64, 128, 256};
+    for (int i = 0; i < 4; ++i) {
+        err = cached_tmap(&tx[i], x, static_cast<uint64_t>(K), static_cast<uint64_t>(total_rows),
+                          static_cast<uint64_t>(K) * 2, kBlockK, boxes[i]);
+        if (err != B200_OK) return err;
+    }
+    SkinnyParams p;
+    p.trace = nullptr;
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.bias = nullptr;
+    p.M = 0;
+    p.n_out = n_out;
+    p.up_row_offset = N / 2;
+    p.kb_total = kb_total;
+    p.nt = nt_max;
+    p.stages = stages;
+    p.epilogue = epilogue;
+    p.status = status;
+    p.group_counts = counts;
+    p.group_offsets = offsets;
+    p.w_rows_per_group = N;
+    auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem_bytes)));
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, slabs, num_groups), dim3(kThreads), smem_bytes, stream,
+                                  dim3(1, 1, 1), tmap_w, tx[0], tx[1], tx[2], tx[3], p));
     return B200_OK;
 }
 
@@ -564,7 +655,7 @@ int b200_linear(void* y, const void* x, const void* w, const void* bias, int M, 
     B200_CHECK_ARG(M == 0 || (y && x && w), "linear: NULL tensor");
     B200_CHECK_ARG(K % 64 == 0, "linear: K must be a multiple of 64");
     B200_CHECK_ARG(ldx >= K && ldx % 8 == 0, "linear: ldx must be >= K and a multiple of 8");
-    B200_CHECK_ARG(epilogue >= B200_EPILOGUE_NONE && epilogue <= B200_EPILOGUE_GEGLU,
+    B200_CHECK_ARG(epilogue >= B200_EPILOGUE_NONE && epilogue <= B200_EPILOGUE_GEGLU_ERF,
                    "linear: unknown epilogue");
     const bool gated = epilogue != B200_EPILOGUE_NONE;
     B200_CHECK_ARG(!gated || (N % 2 == 0), "linear: a gated epilogue needs an even N");

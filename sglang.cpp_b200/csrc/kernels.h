@@ -33,6 +33,16 @@ int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                   int64_t ldx, int epilogue, int* status, cudaStream_t stream);
 
+int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* counts,
+                        const int32_t* offsets, int num_groups, int max_rows_per_group,
+                        int64_t total_rows, int N, int K, int epilogue, int* status,
+                        cudaStream_t stream);
+
+int64_t moe_workspace_bytes(int tokens, int E, int top_k, int H, int I);
+int launch_moe_forward(void* out, const void* hidden, const void* router_logits, const void* gate_up,
+                       const void* down, int tokens, int E, int top_k, int H, int I, int renorm,
+                       int activation, void* workspace, int* status, cudaStream_t stream);
+
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);
 int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,

@@ -338,6 +338,60 @@ def qknorm_rope_store(qkv: torch.Tensor, q_norm: Optional[RMSNorm], k_norm: Opti
          1 if write_k_back else 0, _stream())
 
 
+# --------------------------------------------------------------------------- MoE
+class MoELayer:
+    """include/sglang/moe/moe.h:9-35, src/moe/moe.cc:7-96 (tp_size 1)."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 renormalize: bool = False, activation: str = "silu", device="cuda"):
+        _check(num_experts > 0, "MoELayer requires num_experts > 0")
+        _check(top_k > 0, "MoELayer requires top_k > 0")
+        _check(top_k <= num_experts, "MoELayer top_k must be <= num_experts")
+        _check(hidden_size > 0, "MoELayer requires hidden_size > 0")
+        _check(intermediate_size > 0, "MoELayer requires intermediate_size > 0")
+        _check(activation in ("silu", "gelu"), f"Unsupported MoE activation function: {activation}")
+        self.num_experts_, self.top_k_ = num_experts, top_k
+        self.hidden_size_, self.intermediate_size_ = hidden_size, intermediate_size
+        self.renormalize_, self.activation_ = renormalize, activation
+        self.gate_up_proj = torch.empty(num_experts, 2 * intermediate_size, hidden_size, dtype=bf16, device=device)
+        self.down_proj = torch.empty(num_experts, hidden_size, intermediate_size, dtype=bf16, device=device)
+        self.w1, self.w2 = self.gate_up_proj, self.down_proj
+        self._ws = None
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        _check(hidden_states.dim() == 2, "MoELayer hidden_states must be [num_tokens, hidden_size]")
+        _check(router_logits.dim() == 2, "MoELayer router_logits must be [num_tokens, num_experts]")
+        _check(hidden_states.size(0) == router_logits.size(0), "MoELayer token count mismatch")
+        _check(hidden_states.size(1) == self.hidden_size_, "MoELayer hidden size mismatch")
+        _check(router_logits.size(1) == self.num_experts_, "MoELayer expert count mismatch")
+        _cuda_bf16(hidden_states, "hidden_states")
+        _cuda_bf16(router_logits, "router_logits")
+        T = hidden_states.size(0)
+        need = _lib.load().b200_moe_workspace_bytes(T, self.num_experts_, self.top_k_, self.hidden_size_,
+                                                    self.intermediate_size_)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=hidden_states.device)
+        out = torch.empty_like(hidden_states)
+        call("b200_moe_forward", out.data_ptr(), hidden_states.contiguous().data_ptr(),
+             router_logits.contiguous().data_ptr(), self.gate_up_proj.data_ptr(), self.down_proj.data_ptr(), T,
+             self.num_experts_, self.top_k_, self.hidden_size_, self.intermediate_size_,
+             1 if self.renormalize_ else 0, 1 if self.activation_ == "gelu" else 0, self._ws.data_ptr(),
+             self._ws.numel(), _stream())
+        return out
+
+
+def moe_route(router_logits: torch.Tensor, top_k: int, renormalize: bool):
+    """Routing of MoELayer::forward (src/moe/moe.cc:47-55): (ids int32, weights float32, counts int32)."""
+    _cuda_bf16(router_logits, "router_logits")
+    T, E = router_logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
+    counts = torch.empty(E + 1, dtype=torch.int32, device=router_logits.device)
+    call("b200_moe_route", ids.data_ptr(), w.data_ptr(), counts.data_ptr(), router_logits.contiguous().data_ptr(),
+         T, E, top_k, 1 if renormalize else 0, _stream())
+    return ids, w, counts[:E]
+
+
 # --------------------------------------------------------------------------- sampler
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """Sampler::sample, greedy branch (src/engine/engine.cc:294-298); returns int32."""

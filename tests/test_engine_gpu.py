@@ -24,6 +24,9 @@ def small_cfg(kind: str) -> O.ModelConfig:
     if kind == "qwen2":
         return O.ModelConfig(2, 256, 8, 8, 128, 512, 1024, 1e-6, 1e6, 512, True, False, False,
                              attention_bias=True)
+    if kind == "qwen3moe":
+        return O.ModelConfig(2, 256, 4, 2, 128, 512, 1024, 1e-6, 1e6, 512, False, True, True, "silu",
+                             8, 2, 128, True)
     raise ValueError(kind)
 
 
@@ -75,7 +78,7 @@ def check_logits(got, want, what):
     assert float(d.mean()) <= MEAN_ABS + rms * 2 ** -8, f"{what}: mean-abs {float(d.mean()):.4g} (logit rms {rms:.3g})"
 
 
-@pytest.mark.parametrize("kind,page_size", [("qwen3", 16), ("qwen3", 1), ("llama", 16), ("qwen2", 4)])
+@pytest.mark.parametrize("kind,page_size", [("qwen3", 16), ("qwen3", 1), ("llama", 16), ("qwen2", 4), ("qwen3moe", 16)])
 def test_prefill_then_decode_matches_oracle(pkg, kind, page_size):
     cfg = small_cfg(kind)
     pr = Pair(pkg, cfg, page_size)

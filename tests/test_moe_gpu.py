@@ -1,0 +1,64 @@
+"""The MoE kernels against the oracle (which is pinned to the reference's own MoELayer, see
+tests/golden/moe_ref_fp32.json) and routing against torch.topk.
+
+Tolerance: the oracle here reproduces the reference's bf16 rounding points (store_bf16); the CUDA
+path rounds at the same points, so results differ by summation order inside the GEMMs only: one
+bf16 step per stage, a few steps after the k-fold accumulation.
+"""
+import pytest
+import torch
+
+from oracle import token_loop_oracle as O
+from tests.parity_cases import assert_close_bf16, randn_bf16
+
+pytestmark = pytest.mark.gpu
+bf16 = torch.bfloat16
+
+
+@pytest.mark.parametrize("T,E,k,renorm", [(6, 3, 2, True), (256, 128, 8, True), (33, 16, 1, False), (64, 64, 4, True)])
+def test_route_matches_torch_topk(L, T, E, k, renorm):
+    gen = torch.Generator().manual_seed(T + E)
+    logits = randn_bf16(gen, T, E)
+    ids, w, counts = L.moe_route(logits.cuda(), k, renorm)
+    probs = torch.softmax(logits.float(), -1)
+    tw, ti = probs.topk(k, -1)
+    if renorm:
+        tw = tw / (tw.sum(-1, keepdim=True) + 1e-8)
+    # bit-exact expert sets (as sets: equal probabilities may be ordered either way by topk)
+    assert torch.equal(ids.cpu().long().sort(-1).values, ti.sort(-1).values)
+    same_order = (ids.cpu().long() == ti)
+    assert_close_bf16(w.cpu()[same_order], tw.to(bf16).float()[same_order], 1e-6, 2 ** -7, "routing weights")
+    assert torch.equal(counts.cpu().long(), torch.bincount(ti.flatten(), minlength=E))
+
+
+@pytest.mark.parametrize("T,E,k,H,I,renorm,act", [
+    (6, 3, 2, 64, 64, True, "silu"),            # the reference test's routing shape
+    (64, 16, 4, 256, 128, True, "silu"),
+    (256, 128, 8, 2048, 768, True, "silu"),     # Qwen3-30B-A3B decode step at batch 256
+    (40, 8, 2, 128, 192, False, "gelu"),
+    (300, 4, 2, 128, 64, True, "silu"),         # more than 256 rows for one expert
+    (1, 8, 8, 64, 64, True, "silu"),
+])
+def test_moe_forward_matches_oracle(L, T, E, k, H, I, renorm, act):
+    gen = torch.Generator().manual_seed(T * 7 + E)
+    hidden = randn_bf16(gen, T, H)
+    logits = randn_bf16(gen, T, E)
+    moe = L.MoELayer(E, k, H, I, renorm, act)
+    gu = randn_bf16(gen, E, 2 * I, H, std=H ** -0.5)
+    dn = randn_bf16(gen, E, H, I, std=I ** -0.5)
+    moe.gate_up_proj.copy_(gu.cuda())
+    moe.down_proj.copy_(dn.cuda())
+    got = moe.forward(hidden.cuda(), logits.cuda())
+    want = O.moe_forward(hidden, logits, gu, dn, k, renorm, act, O.store_bf16)
+    assert_close_bf16(got, want, 2e-2, 4 * 2 ** -7, f"moe forward {T}x{E} top{k}")
+    assert L.read_device_status() == (0, 0)
+
+
+def test_moe_rejects_bad_arguments(L, pkg):
+    with pytest.raises(pkg.B200Error):
+        L.MoELayer(4, 5, 64, 64)            # top_k > num_experts
+    moe = L.MoELayer(4, 2, 64, 64)
+    with pytest.raises(pkg.B200Error):
+        moe.forward(torch.zeros(3, 32, dtype=bf16, device="cuda"), torch.zeros(3, 4, dtype=bf16, device="cuda"))
+    with pytest.raises(pkg.B200Error):
+        moe.forward(torch.zeros(3, 64, dtype=bf16, device="cuda"), torch.zeros(2, 4, dtype=bf16, device="cuda"))
