@@ -15,19 +15,25 @@ pytestmark = pytest.mark.gpu
 bf16 = torch.bfloat16
 
 
+def distinct_router_logits(gen, T, E):
+    """Rows without ties (each a permutation of E distinct bf16-exact values in [-4, 4)): with equal
+    probabilities at the k-th place torch.topk and any other top-k may pick different experts."""
+    grid = (torch.arange(E, dtype=torch.float32) - E / 2) * (8.0 / E if E >= 8 else 1.0)
+    assert torch.equal(grid.to(bf16).float(), grid) and grid.unique().numel() == E
+    return torch.stack([grid[torch.randperm(E, generator=gen)] for _ in range(T)]).to(bf16)
+
+
 @pytest.mark.parametrize("T,E,k,renorm", [(6, 3, 2, True), (256, 128, 8, True), (33, 16, 1, False), (64, 64, 4, True)])
 def test_route_matches_torch_topk(L, T, E, k, renorm):
     gen = torch.Generator().manual_seed(T + E)
-    logits = randn_bf16(gen, T, E)
+    logits = distinct_router_logits(gen, T, E)
     ids, w, counts = L.moe_route(logits.cuda(), k, renorm)
     probs = torch.softmax(logits.float(), -1)
     tw, ti = probs.topk(k, -1)
     if renorm:
         tw = tw / (tw.sum(-1, keepdim=True) + 1e-8)
-    # bit-exact expert sets (as sets: equal probabilities may be ordered either way by topk)
-    assert torch.equal(ids.cpu().long().sort(-1).values, ti.sort(-1).values)
-    same_order = (ids.cpu().long() == ti)
-    assert_close_bf16(w.cpu()[same_order], tw.to(bf16).float()[same_order], 1e-6, 2 ** -7, "routing weights")
+    assert torch.equal(ids.cpu().long(), ti)          # bit-exact experts, in the same order
+    assert_close_bf16(w.cpu(), tw.to(bf16).float(), 1e-6, 2 ** -7, "routing weights")
     assert torch.equal(counts.cpu().long(), torch.bincount(ti.flatten(), minlength=E))
 
 
@@ -42,7 +48,7 @@ def test_route_matches_torch_topk(L, T, E, k, renorm):
 def test_moe_forward_matches_oracle(L, T, E, k, H, I, renorm, act):
     gen = torch.Generator().manual_seed(T * 7 + E)
     hidden = randn_bf16(gen, T, H)
-    logits = randn_bf16(gen, T, E)
+    logits = distinct_router_logits(gen, T, E)
     moe = L.MoELayer(E, k, H, I, renorm, act)
     gu = randn_bf16(gen, E, 2 * I, H, std=H ** -0.5)
     dn = randn_bf16(gen, E, H, I, std=I ** -0.5)
