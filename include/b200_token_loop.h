@@ -268,6 +268,38 @@ B200_API int b200_sample(int32_t* out, const void* logits, int rows, int vocab, 
                          const uint64_t* seeds, uint64_t step_index, uint8_t* candidate_mask,
                          b200_stream_t stream);
 
+/* ---- tensor-parallel all-reduce (include/sglang/distributed/distributed.h:24) --- */
+
+/* One process per GPU.  A communicator owns this rank's two exchange buffers (call parity 0 / 1)
+ * of buffer_bytes each and a flag table, in device memory that the peers map through CUDA IPC.
+ * Set-up (the part the reference does with an NCCL unique id, src/distributed/distributed.cc:
+ * 142-173): every rank creates, exports its 64-byte handle, the host code gathers all handles
+ * in rank order (torch.distributed / MPI / a file), every rank connects. */
+typedef struct b200_comm b200_comm;
+B200_API int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out);
+B200_API int b200_comm_handle_bytes(void);
+B200_API int b200_comm_export(b200_comm* comm, void* handle_out);
+B200_API int b200_comm_connect(b200_comm* comm, const void* all_handles);
+/* Device address of this rank's exchange buffer for the given parity: the producer of the
+ * partial sum (the row-parallel GEMM) writes there. */
+B200_API void* b200_comm_buffer(b200_comm* comm, int parity);
+B200_API int b200_comm_destroy(b200_comm* comm);
+
+/* tensor_model_parallel_all_reduce (src/distributed/distributed.cc:205-226): out[rows, hidden]
+ * = bf16(sum over ranks, in rank order, fp32) of the partials in the exchange buffers of
+ * `parity`.  One-shot: every rank reads every peer's partial over NVLink with plain loads.
+ * Successive calls must alternate parity.  The wait for the peers is bounded; a time-out is
+ * reported through the device status words. */
+B200_API int b200_allreduce(b200_comm* comm, int parity, void* out, int rows, int hidden,
+                            b200_stream_t stream);
+/* The all-reduce above fused with the RMSNorm::fused_add_forward_inplace that the models run on
+ * its result (src/models/qwen3.cc:24,31; src/layers/linear.cc:52-55,73-76):
+ * residual <- bf16(all-reduce) + residual; x_out <- rmsnorm(sum) * weight. */
+B200_API int b200_allreduce_fused_add_rmsnorm(b200_comm* comm, int parity, void* x_out,
+                                              void* residual, const void* weight, int rows,
+                                              int hidden, float eps, int round_sum_first,
+                                              b200_stream_t stream);
+
 /* ---- step runner (include/sglang/engine/engine.h:57-103) -------------------- */
 
 /* The fields of ModelConfig the forward pass reads (include/sglang/models/config.h:15-42). */
@@ -363,6 +395,11 @@ B200_API int b200_engine_synchronize(b200_engine* engine);
 
 /* Copies the bf16 logits [rows, vocab] of the last step to host memory (synchronous). */
 B200_API int b200_engine_read_logits(b200_engine* engine, void* host, int rows);
+
+/* Tensor parallelism (engine created with tp_size > 1): export this rank's IPC handle
+ * (b200_comm_handle_bytes bytes) and connect to all ranks' handles before the first step. */
+B200_API int b200_engine_comm_export(b200_engine* engine, void* handle_out);
+B200_API int b200_engine_comm_connect(b200_engine* engine, const void* all_handles);
 
 /* The stream the engine enqueues on (Engine::stream_), as a cudaStream_t. */
 B200_API b200_stream_t b200_engine_stream(b200_engine* engine);

@@ -340,7 +340,11 @@ class OracleModel:
     (src/models/qwen3.cc:21-35,55-66,84-87; llama.cc:15-29,49-55,74-77; qwen3_moe.cc:14-28;
     src/models/utils.cc:8-19,41-57,82-91,138-142; src/layers/attention_layer.cc:17-51)."""
 
-    def __init__(self, cfg: ModelConfig, weights: dict, store: Store = store_bf16):
+    def __init__(self, cfg: ModelConfig, weights: dict, store: Store = store_bf16, all_reduce=None):
+        """all_reduce: under tensor parallelism, a callable that sums a tensor over the ranks
+        (tensor_model_parallel_all_reduce, src/distributed/distributed.cc:205-226); cfg then holds
+        the per-rank head counts and intermediate size and weights the rank's shard."""
+        self.all_reduce = all_reduce
         self.cfg = cfg
         # Up-cast the (bf16-rounded) weights to fp32 once; tied tensors stay tied.
         cache: dict[int, torch.Tensor] = {}
@@ -375,17 +379,21 @@ class OracleModel:
         kv.v[li][loc] = v
         o = paged_attention(q, kv.k[li], kv.v[li], page_table, batch.table_idx, batch.seq_lens,
                             batch.qo_indptr, self.sm_scale, st)
-        return linear(o.reshape(T, qd), L["o"], None, st)
+        return self._reduce(linear(o.reshape(T, qd), L["o"], None, st))
+
+    def _reduce(self, y):
+        """LinearRowParallel / LinearOProj::forward (src/layers/linear.cc:52-55,73-76)."""
+        return y if self.all_reduce is None else self.store(self.all_reduce(y))
 
     def _mlp(self, L, x):
         cfg, st = self.cfg, self.store
         if cfg.num_experts > 0:
             logits = linear(x, L["router"], None, st)
-            return moe_forward(x, logits, L["experts_gate_up"], L["experts_down"],
-                               cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.hidden_act, st)
+            return self._reduce(moe_forward(x, logits, L["experts_gate_up"], L["experts_down"],
+                                            cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.hidden_act, st))
         gu = linear(x, L["gate_up"], None, st)
         y = silu_and_mul(gu, st) if cfg.hidden_act == "silu" else gelu_and_mul(gu, st)
-        return linear(y, L["down"], None, st)
+        return self._reduce(linear(y, L["down"], None, st))
 
     def hidden_states(self, batch: StepBatch, kv: KVState, page_table: np.ndarray) -> torch.Tensor:
         cfg, st = self.cfg, self.store

@@ -67,6 +67,16 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
     "b200_sample": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, ctypes.c_uint64, _P, _P]),
+    "b200_comm_create": (_I, [_I, _I, _L, POINTER(c_void_p)]),
+    "b200_comm_handle_bytes": (_I, []),
+    "b200_comm_export": (_I, [_P, _P]),
+    "b200_comm_connect": (_I, [_P, _P]),
+    "b200_comm_buffer": (c_void_p, [_P, _I]),
+    "b200_comm_destroy": (_I, [_P]),
+    "b200_allreduce": (_I, [_P, _I, _P, _I, _I, _P]),
+    "b200_allreduce_fused_add_rmsnorm": (_I, [_P, _I, _P, _P, _P, _I, _I, _F, _I, _P]),
+    "b200_engine_comm_export": (_I, [_P, _P]),
+    "b200_engine_comm_connect": (_I, [_P, _P]),
     "b200_engine_create": (_I, [_P, _P, POINTER(c_void_p)]),
     "b200_engine_destroy": (_I, [_P]),
     "b200_engine_tensor": (_I, [_P, c_char_p, _I, POINTER(c_void_p), POINTER(c_int64)]),

@@ -1,0 +1,306 @@
+// One-shot all-reduce over NVLink peer memory, alone or fused with the residual add + RMSNorm
+// that follows every row-parallel projection under tensor parallelism.
+//
+// Stands where tensor_model_parallel_all_reduce does (src/distributed/distributed.cc:205-226,
+// called from LinearRowParallel / LinearOProj::forward, src/layers/linear.cc:52-55,73-76), and
+// folds in the RMSNorm::fused_add_forward_inplace the models run next.  One process per GPU.
+//
+//   * every rank owns two exchange buffers (call parity) and a flag table in ordinary device
+//     memory; peers map them through CUDA IPC handles exchanged on the host;
+//   * the producer GEMM writes its partial result straight into the local exchange buffer;
+//   * the kernel announces "call c ready" to every peer (system-scope release store into the
+//     peer's flag table, one slot per CTA so CTAs never coordinate), waits — bounded — for the
+//     same announcement from every peer, then reads the peers' partials with plain 16-byte
+//     loads (no TMA, no multicast), sums in fp32 in rank order, rounds to bf16 (the value the
+//     reference's all-reduce returns) and continues with the add + norm on the row;
+//   * call parity makes the buffers safe to reuse with this single barrier: a rank can only
+//     start writing parity p again after a call in which every peer reported having finished
+//     its previous read of parity p.
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxCommBlocks = 1024;  // CTAs per launch that take part in the handshake
+
+struct CommDevice {
+    const __nv_bfloat16* peer_buf[2][kMaxRanks];  // [parity][rank] -> that rank's exchange buffer
+    uint32_t* peer_flags[kMaxRanks];              // [rank] -> that rank's flag table [blocks][ranks]
+    uint32_t* self_counter;                       // [blocks] calls this CTA slot has completed
+    int rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Handshake of one CTA slot with the same slot on every peer.  Returns false on time-out.
+__device__ __forceinline__ bool comm_barrier(const CommDevice& c, int* status) {
+    __shared__ int s_ok;
+    const int slot = blockIdx.x % kMaxCommBlocks;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < c.world) {
+        const uint32_t call = c.self_counter[slot] + 1;
+        const int peer = threadIdx.x;
+        // This rank's partial was written by the kernel before this one; make it visible to
+        // the other GPUs before the flag that announces it.
+        __threadfence_system();
+        st_release_sys(c.peer_flags[peer] + slot * kMaxRanks + c.rank, call);
+        const uint32_t* mine = c.peer_flags[c.rank] + slot * kMaxRanks + peer;
+        const uint64_t t0 = global_timer_ns();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(mine) - call) < 0) {
+            if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicExch(&status[kStatusTimeout], 401);
+                s_ok = 0;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) c.self_counter[slot] += 1;
+    return s_ok != 0;
+}
+
+constexpr int kArVecPerThread = 4;  // 16-byte vectors a thread keeps in registers (hidden <= 8192)
+
+// One CTA per row (grid-stride over rows).
+// MODE 0: out = bf16(sum of partials)                       (tensor_model_parallel_all_reduce)
+// MODE 1: residual <- bf16(sum) + residual; out <- rmsnorm  (+ RMSNorm::fused_add_forward_inplace)
+template <int MODE, bool ROUND_FIRST>
+__global__ void __launch_bounds__(256)
+allreduce_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat16* residual,
+                 const __nv_bfloat16* __restrict__ weight, int rows, int hidden, float eps, int* status) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    comm_barrier(c, status);
+    const int nvec = hidden >> 3;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t base = static_cast<int64_t>(row) * nvec;
+        float vals[kArVecPerThread][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < kArVecPerThread; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            if (v >= nvec) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < c.world; ++r) {  // rank order: every rank gets the same bits
+                const uint4 a = __ldcv(reinterpret_cast<const uint4*>(c.peer_buf[parity][r]) + base + v);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += bf16_lo(aw[j]);
+                    acc[2 * j + 1] += bf16_hi(aw[j]);
+                }
+            }
+            uint32_t y[4];  // what the reference's all-reduce returns: the sum in bf16
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] = pack_bf16(acc[2 * j], acc[2 * j + 1]);
+            if (MODE == 0) {
+                reinterpret_cast<uint4*>(out)[base + v] = make_uint4(y[0], y[1], y[2], y[3]);
+            } else {
+                const uint4 rr = reinterpret_cast<const uint4*>(residual)[base + v];
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = bf16_lo(y[j]) + bf16_lo(rw[j]);
+                    const float hi = bf16_hi(y[j]) + bf16_hi(rw[j]);
+                    packed[j] = pack_bf16(lo, hi);
+                    vals[i][2 * j] = ROUND_FIRST ? bf16_lo(packed[j]) : lo;
+                    vals[i][2 * j + 1] = ROUND_FIRST ? bf16_hi(packed[j]) : hi;
+                }
+                reinterpret_cast<uint4*>(residual)[base + v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+            }
+        }
+        if (MODE == 0) continue;
+        ss = warp_sum(ss);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+        tot = warp_sum(tot);
+        const float scale = rsqrtf(tot / static_cast<float>(hidden) + eps);
+#pragma unroll
+        for (int i = 0; i < kArVecPerThread; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            if (v >= nvec) continue;
+            const uint4 w4 = reinterpret_cast<const uint4*>(weight)[v];
+            const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                o[j] = pack_bf16(vals[i][2 * j] * scale * bf16_lo(ww[j]), vals[i][2 * j + 1] * scale * bf16_hi(ww[j]));
+            reinterpret_cast<uint4*>(out)[base + v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+// Host object: this rank's exchange buffers and flag table, and the peers' mappings.
+struct b200_comm {
+    int rank = 0, world = 1, device = 0;
+    int64_t buffer_bytes = 0;
+    void* local_base = nullptr;       // [flags | counters | buffer 0 | buffer 1]
+    void* peer_base[kMaxRanks] = {};  // mapped bases (own entry = local_base)
+    bool connected = false;
+    CommDevice dev = {};
+    int64_t flags_bytes = 0, counters_bytes = 0;
+};
+
+namespace {
+int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+}  // namespace
+
+extern "C" {
+
+int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out) {
+    B200_CHECK_ARG(out, "comm_create: out is NULL");
+    B200_CHECK_ARG(world >= 1 && world <= kMaxRanks, "comm_create: world size must be in [1, 8]");
+    B200_CHECK_ARG(rank >= 0 && rank < world, "comm_create: rank out of range");
+    B200_CHECK_ARG(buffer_bytes > 0, "comm_create: buffer_bytes must be positive");
+    b200_comm* c = new b200_comm();
+    c->rank = rank;
+    c->world = world;
+    B200_CHECK_CUDA(cudaGetDevice(&c->device));
+    c->buffer_bytes = align_up(buffer_bytes, 256);
+    c->flags_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * kMaxRanks * 4, 256);
+    c->counters_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
+    const int64_t total = c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
+    if (cudaMalloc(&c->local_base, static_cast<size_t>(total)) != cudaSuccess ||
+        cudaMemset(c->local_base, 0, static_cast<size_t>(total)) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
+        set_last_error("comm_create: allocating %lld bytes failed: %s", static_cast<long long>(total),
+                       cudaGetErrorString(cudaGetLastError()));
+        delete c;
+        return B200_ERR_CUDA;
+    }
+    c->peer_base[rank] = c->local_base;
+    *out = c;
+    return B200_OK;
+}
+
+int b200_comm_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+
+int b200_comm_export(b200_comm* c, void* handle_out) {
+    B200_CHECK_ARG(c && handle_out, "comm_export: NULL argument");
+    cudaIpcMemHandle_t h;
+    B200_CHECK_CUDA(cudaIpcGetMemHandle(&h, c->local_base));
+    memcpy(handle_out, &h, sizeof(h));
+    return B200_OK;
+}
+
+int b200_comm_connect(b200_comm* c, const void* all_handles) {
+    B200_CHECK_ARG(c && all_handles, "comm_connect: NULL argument");
+    B200_CHECK_ARG(!c->connected, "comm_connect: already connected");
+    const char* hs = static_cast<const char*>(all_handles);
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, hs + static_cast<size_t>(r) * sizeof(h), sizeof(h));
+        B200_CHECK_CUDA(cudaIpcOpenMemHandle(&c->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    for (int r = 0; r < c->world; ++r) {
+        char* base = static_cast<char*>(c->peer_base[r]);
+        c->dev.peer_flags[r] = reinterpret_cast<uint32_t*>(base);
+        for (int p = 0; p < 2; ++p)
+            c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
+                                                                          p * c->buffer_bytes);
+    }
+    c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
+    c->dev.rank = c->rank;
+    c->dev.world = c->world;
+    c->connected = true;
+    return B200_OK;
+}
+
+void* b200_comm_buffer(b200_comm* c, int parity) {
+    if (!c || parity < 0 || parity > 1) return nullptr;
+    return static_cast<char*>(c->local_base) + c->flags_bytes + c->counters_bytes + parity * c->buffer_bytes;
+}
+
+int b200_comm_destroy(b200_comm* c) {
+    if (!c) return B200_OK;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank && c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+    if (c->local_base) cudaFree(c->local_base);
+    delete c;
+    return B200_OK;
+}
+
+}  // extern "C"
+
+namespace b200 {
+
+int launch_allreduce(b200_comm* c, int parity, int mode, void* out, void* residual, const void* weight,
+                     int rows, int hidden, float eps, bool round_first, int* status, cudaStream_t stream) {
+    if (!c || !c->connected) {
+        set_last_error("all-reduce: the communicator is not connected");
+        return B200_ERR_STATE;
+    }
+    if (hidden % 8 != 0 || hidden > 256 * 8 * kArVecPerThread) {
+        set_last_error("all-reduce: row width %d must be a multiple of 8 and at most 8192", hidden);
+        return B200_ERR_UNSUPPORTED;
+    }
+    if (static_cast<int64_t>(rows) * hidden * 2 > c->buffer_bytes) {
+        set_last_error("all-reduce: %d x %d exceeds the exchange buffer", rows, hidden);
+        return B200_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0) return B200_OK;
+    // Every rank must launch the same number of CTAs: the handshake pairs CTA slots.
+    const int grid = rows < kMaxCommBlocks ? rows : kMaxCommBlocks;
+    auto kernel = mode == 0 ? allreduce_kernel<0, false>
+                            : (round_first ? allreduce_kernel<1, true> : allreduce_kernel<1, false>);
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(256), 0, stream, dim3(1, 1, 1), c->dev, parity,
+                                  static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(residual),
+                                  static_cast<const __nv_bfloat16*>(weight), rows, hidden, eps, status));
+    return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_allreduce(b200_comm* comm, int parity, void* out, int rows, int hidden, b200_stream_t stream) {
+    B200_CHECK_ARG(comm && (rows == 0 || out), "allreduce: NULL argument");
+    B200_CHECK_ARG(parity == 0 || parity == 1, "allreduce: parity must be 0 or 1");
+    int err = B200_OK;
+    int* status = device_status_words(&err);
+    if (err != B200_OK) return err;
+    return launch_allreduce(comm, parity, 0, out, nullptr, nullptr, rows, hidden, 0.f, false, status,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b200_allreduce_fused_add_rmsnorm(b200_comm* comm, int parity, void* x_out, void* residual,
+                                     const void* weight, int rows, int hidden, float eps,
+                                     int round_sum_first, b200_stream_t stream) {
+    B200_CHECK_ARG(comm && (rows == 0 || (x_out && residual && weight)), "allreduce_fused_add_rmsnorm: NULL argument");
+    B200_CHECK_ARG(parity == 0 || parity == 1, "allreduce_fused_add_rmsnorm: parity must be 0 or 1");
+    int err = B200_OK;
+    int* status = device_status_words(&err);
+    if (err != B200_OK) return err;
+    return launch_allreduce(comm, parity, 1, x_out, residual, weight, rows, hidden, eps, round_sum_first != 0,
+                            status, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

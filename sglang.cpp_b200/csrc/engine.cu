@@ -101,6 +101,19 @@ struct Tensor {
 
 using namespace b200;
 
+struct b200_comm;
+extern "C" {
+int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out);
+int b200_comm_export(b200_comm* c, void* handle_out);
+int b200_comm_connect(b200_comm* c, const void* all_handles);
+void* b200_comm_buffer(b200_comm* c, int parity);
+int b200_comm_destroy(b200_comm* c);
+}
+namespace b200 {
+int launch_allreduce(b200_comm* c, int parity, int mode, void* out, void* residual, const void* weight,
+                     int rows, int hidden, float eps, bool round_first, int* status, cudaStream_t stream);
+}
+
 struct b200_engine {
     b200_model_config m;
     b200_engine_config c;
@@ -152,6 +165,7 @@ struct b200_engine {
     std::vector<cudaEvent_t> prof_events;   // 2 per layer
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
+    b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
     // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
     static int seed_offset(int Bp) { return (7 * Bp + 1 + 1) & ~1; }
@@ -240,12 +254,32 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     set_pdl_launches(e->use_pdl && !(e->profile_attention && !e->capturing));
     B200_TRY(launch_embedding(e->x, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s));
     const bool round_first = m.fused_residual == 0;
+    // Under tensor parallelism the row-parallel projections (o_proj, down_proj, the MoE output)
+    // leave a partial sum: they write it into this rank's exchange buffer, and the add + norm
+    // that follows becomes the fused all-reduce kernel.  Two calls per layer alternate the
+    // buffers, so the parity of a call is fixed across steps (and inside a captured graph).
+    const bool tp = e->c.tp_size > 1;
+    int ar_calls = 0;
+    bool x_is_partial = false;  // does the running `x` sit in an exchange buffer awaiting reduction?
+    auto proj_out = [&]() -> __nv_bfloat16* {
+        if (!tp) return e->x;
+        x_is_partial = true;
+        return static_cast<__nv_bfloat16*>(b200_comm_buffer(e->comm, ar_calls & 1));
+    };
+    auto add_norm = [&](const __nv_bfloat16* w) -> int {
+        if (tp && x_is_partial) {
+            x_is_partial = false;
+            const int parity = ar_calls++ & 1;
+            return launch_allreduce(e->comm, parity, 1, e->x, e->residual, w, T, hidden, m.rms_norm_eps,
+                                    round_first, e->status, s);
+        }
+        return launch_fused_add_rmsnorm(e->x, e->residual, w, T, hidden, m.rms_norm_eps, round_first, s);
+    };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
 
     for (int l = 0; l < m.num_layers; ++l) {
         LayerWeights& L = e->layers[l];
-        B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, L.input_norm, T, hidden, m.rms_norm_eps,
-                                          round_first, s));
+        B200_TRY(add_norm(L.input_norm));
         B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
                                B200_EPILOGUE_NONE, e->status, s));
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
@@ -277,15 +311,14 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
             e->prof_pairs_recorded = l + 1;
         }
-        B200_TRY(launch_linear(e->x, e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
+        B200_TRY(launch_linear(proj_out(), e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
                                B200_EPILOGUE_NONE, e->status, s));
-        B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, L.post_norm, T, hidden, m.rms_norm_eps,
-                                          round_first, s));
+        B200_TRY(add_norm(L.post_norm));
         if (m.num_experts > 0) {
             // MoEMLP::forward (src/models/utils.cc:82-91): router logits, then the expert layer.
             B200_TRY(launch_linear(e->router_logits, e->x, L.router, nullptr, T, m.num_experts, hidden, hidden,
                                    B200_EPILOGUE_NONE, e->status, s));
-            B200_TRY(launch_moe_forward(e->x, e->x, e->router_logits, L.experts_gate_up, L.experts_down, T,
+            B200_TRY(launch_moe_forward(proj_out(), e->x, e->router_logits, L.experts_gate_up, L.experts_down, T,
                                         m.num_experts, m.num_experts_per_tok, hidden,
                                         m.moe_intermediate_size / e->c.tp_size, m.norm_topk_prob,
                                         m.hidden_act == 1 ? 1 : 0, e->moe_ws, e->status, s));
@@ -293,11 +326,10 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         }
         B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
                                e->status, s));
-        B200_TRY(launch_linear(e->x, e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
+        B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
                                B200_EPILOGUE_NONE, e->status, s));
     }
-    B200_TRY(launch_fused_add_rmsnorm(e->x, e->residual, e->final_norm, T, hidden, m.rms_norm_eps,
-                                      round_first, s));
+    B200_TRY(add_norm(e->final_norm));
     const __nv_bfloat16* head_in = e->x;
     if (phase == B200_PHASE_PREFILL) {
         B200_CHECK_CUDA(launch_kernel(select_last_rows_kernel, dim3(Bp), dim3(128), 0, s, dim3(1, 1, 1),
@@ -493,6 +525,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     E_TRY(named_alloc(e, &e->input_ids, "input_ids", Tm));
     E_TRY(named_alloc(e, &e->seq_lens, "seq_lens", e->max_batch));
     E_TRY(named_alloc(e, &e->next_tokens, "next_tokens", e->max_batch, true));
+    if (c.tp_size > 1) E_TRY(b200_comm_create(c.tp_rank, c.tp_size, Tm * H * 2, &e->comm));
     if (m.num_experts > 0) {
         E_TRY(named_alloc(e, &e->router_logits, "router_logits", Tm * m.num_experts));
         E_TRY(dev_alloc(e, &e->moe_ws,
@@ -530,6 +563,7 @@ int b200_engine_destroy(b200_engine* e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
+    if (e->comm) b200_comm_destroy(e->comm);
     for (void* p : e->allocs) cudaFree(p);
     if (e->meta_host) cudaFreeHost(e->meta_host);
     if (e->scatter_host) cudaFreeHost(e->scatter_host);
@@ -717,6 +751,16 @@ int b200_engine_read_logits(b200_engine* e, void* host, int rows) {
 }
 
 b200_stream_t b200_engine_stream(b200_engine* e) { return e ? e->stream : nullptr; }
+
+int b200_engine_comm_export(b200_engine* e, void* handle_out) {
+    B200_CHECK_ARG(e && e->comm, "engine_comm_export: the engine was not created with tp_size > 1");
+    return b200_comm_export(e->comm, handle_out);
+}
+
+int b200_engine_comm_connect(b200_engine* e, const void* all_handles) {
+    B200_CHECK_ARG(e && e->comm, "engine_comm_connect: the engine was not created with tp_size > 1");
+    return b200_comm_connect(e->comm, all_handles);
+}
 
 int b200_engine_set_profiling(b200_engine* e, int on) {
     B200_CHECK_ARG(e, "engine_set_profiling: NULL engine");

@@ -98,45 +98,30 @@ class Engine:
 
     def load_weights(self, w: dict, tp_rank: int = 0, tp_size: int = 1) -> None:
         """Upload weights given in the reference's packed layouts (full, unsharded tensors as
-        oracle.init_weights makes them), applying the reference's TP shard rules
-        (src/models/weight_loader.cc:284-353) for this rank."""
+        oracle.init_weights makes them), cut with the reference's TP shard rules for this rank
+        (sglang_cpp_b200.tp.shard_layer)."""
+        from .tp import shard_layer
+
         cfg = self.model_config
-        d = cfg.head_dim
-        hq, hkv = cfg.num_qo_heads // tp_size, cfg.num_kv_heads // tp_size
         self.load("embed", 0, w["embed"])
         if not cfg.tie_word_embeddings:
             self.load("lm_head", 0, w["lm_head"])
         self.load("final_norm", 0, w["final_norm"])
         for l, L in enumerate(w["layers"]):
-            qd, kd = cfg.num_qo_heads * d, cfg.num_kv_heads * d
-            q, k, v = L["qkv"][:qd], L["qkv"][qd:qd + kd], L["qkv"][qd + kd:]
-            shard = lambda t, n: t[tp_rank * n:(tp_rank + 1) * n]
-            self.load("qkv", l, torch.cat([shard(q, hq * d), shard(k, hkv * d), shard(v, hkv * d)], 0))
-            if cfg.attention_bias:
-                b = L["qkv_bias"]
-                self.load("qkv_bias", l, torch.cat([shard(b[:qd], hq * d), shard(b[qd:qd + kd], hkv * d),
-                                                     shard(b[qd + kd:], hkv * d)], 0))
-            self.load("o", l, L["o"][:, tp_rank * hq * d:(tp_rank + 1) * hq * d])
-            self.load("input_norm", l, L["input_norm"])
-            self.load("post_norm", l, L["post_norm"])
-            if cfg.qk_norm:
-                self.load("q_norm", l, L["q_norm"])
-                self.load("k_norm", l, L["k_norm"])
-            if cfg.num_experts > 0:
-                ie = cfg.moe_intermediate_size
-                il = ie // tp_size
-                gu = L["experts_gate_up"]
-                self.load("router", l, L["router"])
-                self.load("experts_gate_up", l, torch.cat([gu[:, tp_rank * il:(tp_rank + 1) * il],
-                                                            gu[:, ie + tp_rank * il:ie + (tp_rank + 1) * il]], 1))
-                self.load("experts_down", l, L["experts_down"][:, :, tp_rank * il:(tp_rank + 1) * il])
-            else:
-                I = cfg.intermediate_size
-                il = I // tp_size
-                gu = L["gate_up"]
-                self.load("gate_up", l, torch.cat([gu[tp_rank * il:(tp_rank + 1) * il],
-                                                   gu[I + tp_rank * il:I + (tp_rank + 1) * il]], 0))
-                self.load("down", l, L["down"][:, tp_rank * il:(tp_rank + 1) * il])
+            for name, t in shard_layer(cfg, L, tp_rank, tp_size).items():
+                self.load(name, l, t)
+
+    def connect_tp(self, group=None) -> None:
+        """Exchange the CUDA IPC handles of the all-reduce buffers over torch.distributed and map
+        the peers (what the reference's NCCL unique-id rendezvous does,
+        src/distributed/distributed.cc:142-173)."""
+        from .tp import exchange_handles
+
+        n = _lib.load().b200_comm_handle_bytes()
+        buf = ctypes.create_string_buffer(n)
+        call("b200_engine_comm_export", self._h, buf)
+        allh = exchange_handles(buf.raw, self.config.tp_rank, self.config.tp_size, group)
+        call("b200_engine_comm_connect", self._h, allh)
 
     def load_rope_tables(self, cos: torch.Tensor, sin: torch.Tensor) -> None:
         """Overwrite the RoPE tables with ones built elsewhere (e.g. bit-identical to torch's)."""

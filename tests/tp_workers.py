@@ -1,0 +1,131 @@
+"""Worker functions for the two-rank tensor-parallel tests (spawned with torch.multiprocessing)."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def _cfg():
+    from oracle import token_loop_oracle as O
+
+    # Llama wiring (the TP benchmark architecture), 2 layers, 4 q / 2 kv heads so that 2 ranks divide them
+    return O.ModelConfig(2, 256, 4, 2, 128, 512, 1024, 1e-5, 5e5, 256, False, False, False)
+
+
+def _batch(cfg, prompts):
+    from oracle import token_loop_oracle as O
+
+    ids, pos, loc, qo, cur = [], [], [], [0], 0
+    pt = np.zeros((len(prompts), 64), dtype=np.int32)
+    for b, p in enumerate(prompts):
+        for i, t in enumerate(p):
+            ids.append(t)
+            pos.append(i)
+            loc.append(cur)
+            pt[b, i] = cur
+            cur += 1
+        qo.append(len(ids))
+    return O.StepBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(loc, np.int32),
+                       np.arange(len(prompts), dtype=np.int32), np.array([len(p) for p in prompts], np.int32),
+                       np.array(qo, np.int32), True), pt, cur
+
+
+def cpu_oracle_worker(rank, world, port, out_path):
+    """Each gloo rank runs the oracle on its weight shard with dist.all_reduce where the reference
+    all-reduces; rank 0 saves the logits for comparison with the unsharded oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+
+    entry.load_package()
+    from sglang_cpp_b200 import tp
+
+    cfg = _cfg()
+    w = O.init_weights(cfg, seed=0, std=0.05)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (7, 19)]
+    batch, pt, slots = _batch(cfg, prompts)
+
+    def all_reduce(t):
+        t = t.clone()
+        dist.all_reduce(t)
+        return t
+
+    local = O.OracleModel(tp.local_config(cfg, world), tp.shard_weights(cfg, w, rank, world), O.store_fp32, all_reduce)
+    kv = O.KVState.create(tp.local_config(cfg, world), slots + 1)
+    logits = local.forward(batch, kv, pt)
+    if rank == 0:
+        full = O.OracleModel(cfg, w, O.store_fp32)
+        want = full.forward(batch, O.KVState.create(cfg, slots + 1), pt)
+        torch.save({"got": logits, "want": want}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gpu_engine_worker(rank, world, port, out_path):
+    """Two processes, one GPU each: the engine with tp_size = 2 (fused all-reduce over peer memory)
+    against the unsharded oracle, prefill then decode."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+
+    pkg = entry.load_package()
+    pkg.load_library()
+    from sglang_cpp_b200.engine import Engine, EngineConfig
+    from sglang_cpp_b200.host_batch import HostBatcher
+
+    cfg = _cfg()
+    w = O.init_weights(cfg, seed=0, std=0.02)
+    eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world))
+    eng.load_weights(w, rank, world)
+    cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
+    eng.load_rope_tables(cos, sin)
+    eng.connect_tp()
+    hb = HostBatcher(eng, 32, 16, 4, enable_prefix_cache=False)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.int32) for n in (7, 19)]
+    reqs = [hb.add_request(p, 8) for p in prompts]
+    hb.prefill(reqs).synchronize()
+    res = {"prefill": eng.logits(2).clone()}
+    toks = []
+    for _ in range(3):
+        out = hb.decode(reqs)
+        out.synchronize()
+        toks.append(out.next_tokens_cpu.clone())
+    res["decode_logits"] = eng.logits(2).clone()
+    res["tokens"] = torch.stack(toks)
+    # both ranks must agree bit for bit (same sums in the same rank order)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (res["decode_logits"], res["tokens"]))
+    if rank == 0:
+        res["ranks_agree"] = all(torch.equal(g[0], gathered[0][0]) and torch.equal(g[1], gathered[0][1]) for g in gathered)
+        # the oracle, unsharded, on the same requests
+        model = O.OracleModel(cfg, w, O.store_bf16)
+        kv = O.KVState.create(cfg, 33 * 16)
+        pt = np.zeros((5, 256), dtype=np.int32)
+        for r in reqs:
+            s = hb.slots_of(r)
+            pt[r.table_idx, :len(s)] = s
+        ids, pos, loc, qo = [], [], [], [0]
+        for r, p in zip(reqs, prompts):
+            for i, t in enumerate(p):
+                ids.append(int(t)); pos.append(i); loc.append(hb.slots_of(r)[i])
+            qo.append(len(ids))
+        b = O.StepBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(loc, np.int32),
+                        np.array([r.table_idx for r in reqs], np.int32), np.array([len(p) for p in prompts], np.int32),
+                        np.array(qo, np.int32), True)
+        res["want_prefill"] = model.forward(b, kv, pt)
+        torch.save(res, out_path)
+    dist.barrier()
+    eng.close()
+    dist.destroy_process_group()
