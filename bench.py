@@ -309,6 +309,117 @@ def run_gpu(args):
         print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------- TP workload
+def run_gpu_tp(args):
+    """Workload "c4": Llama-3-8B architecture, bf16, random-init weights drawn on the device,
+    tensor parallel over all ranks (heads and MLP columns split, the post-projection all-reduce
+    fused with add + norm over NVLink peer memory), batch 128, prompts of 1024 uniform-random
+    tokens, greedy decode, page size 16.  Strong scaling: the same job on N GPUs."""
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg = entry.load_package()
+    pkg.load_library()
+    from sglang_cpp_b200.engine import Engine, EngineConfig
+    from sglang_cpp_b200.host_batch import HostBatcher
+
+    cfg = O.llama3_8b()
+    B, PROMPT = 128, 1024
+    K, W = args.steps, args.warmup
+    total_new = (K + W) + 24
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab_size, size=PROMPT).astype(np.int32) for _ in range(B)]
+    num_pages = B * math.ceil((PROMPT + total_new + 1) / PAGE_SIZE) + 8
+    engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, B, PROMPT + total_new + 1, MAX_EXTEND_TOKENS, rank, world))
+    engine.fill_random(seed=0)
+    if world > 1:
+        engine.connect_tp()
+    hb = HostBatcher(engine, num_pages, PAGE_SIZE, B, enable_prefix_cache=False)
+    reqs, batch = [], []
+    t0 = time.perf_counter()
+    for p in prompts:
+        r = hb.add_request(p, total_new)
+        reqs.append(r)
+        batch.append(r)
+        if len(batch) * PROMPT >= MAX_EXTEND_TOKENS:
+            hb.prefill(batch).synchronize()
+            batch = []
+    if batch:
+        hb.prefill(batch).synchronize()
+    prefill_s = time.perf_counter() - t0
+    engine.capture_graphs([B])
+    stream = torch.cuda.ExternalStream(pkg.load_library().b200_engine_stream(engine._h))
+
+    def barrier():
+        engine.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        hb.decode(reqs)
+    barrier()
+    ctx0 = reqs[0].device_len
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    toks = None
+    for _ in range(K):
+        toks = hb.decode(reqs)
+    ev1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    dev_ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([dev_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = float(t[0])
+        # lock-step check: every rank sampled the same tokens
+        mine = toks.next_tokens_cpu.clone().cuda()
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        same = torch.tensor([int(torch.equal(mine, ref))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        lockstep = bool(same.item())
+    else:
+        lockstep = True
+    peak, peak_kind = measured_peaks()
+    d, L = cfg.head_dim, cfg.num_layers
+    per_layer = ((cfg.num_qo_heads + 2 * cfg.num_kv_heads) * d * cfg.hidden_size + cfg.hidden_size * cfg.num_qo_heads * d
+                 + 3 * cfg.intermediate_size * cfg.hidden_size)
+    mean_ctx = ctx0 + (K - 1) / 2
+    kv_tok = 2 * cfg.num_kv_heads * d * L * 2
+    # per GPU: sharded layers and KV, replicated lm_head
+    bytes_gpu = 2 * L * per_layer / world + 2 * cfg.vocab_size * cfg.hidden_size + B * mean_ctx * kv_tok / world
+    line = {
+        "metric": "decode tokens/s at bs=128 (Llama-3-8B, TP over all GPUs)", "value": round(B * K / (dev_ms * 1e-3), 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy",
+                   "parallelism": f"tp{world}", "mean_context": mean_ctx, "ranks_in_lockstep": lockstep},
+        "step_roofline": {"algorithmic_bytes_per_step_per_gpu": int(bytes_gpu),
+                          "frac_of_measured_hbm": round(bytes_gpu / (dev_ms / K * 1e-3) / 1e9 / peak, 4)},
+        "prefill": {"tokens": B * PROMPT, "seconds": round(prefill_s, 3)},
+        "clocks": clocks,
+    }
+    engine.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
 # ------------------------------------------------------------------------------- CPU side
 CPU_SAMPLE_REQS = 8
 
@@ -393,6 +504,9 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4"],
+                    help="c2 (default, the headline metric): Qwen3-0.6B decode, replicas when N > 1; "
+                         "c4: Llama-3-8B decode, tensor parallel over the N ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-region", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
@@ -401,6 +515,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c4":
+        run_gpu_tp(args)
     else:
         run_gpu(args)
 

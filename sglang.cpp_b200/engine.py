@@ -123,6 +123,40 @@ class Engine:
         allh = exchange_handles(buf.raw, self.config.tp_rank, self.config.tp_size, group)
         call("b200_engine_comm_connect", self._h, allh)
 
+    def fill_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random-init weights generated on the device (benchmarks of models too large to draw on
+        the host): N(0, std) for matrices, 1 for norm weights.  Replicated tensors (embedding,
+        lm_head, norms, router) get the same values on every rank; sharded ones differ by rank."""
+        cfg, rank = self.model_config, self.config.tp_rank
+        dev = torch.device("cuda", torch.cuda.current_device())
+
+        def fill(name, layer, gen_seed, ones=False):
+            try:
+                ptr, n = self.tensor_info(name, layer)
+            except B200Error:
+                return
+            view = _as_cuda_tensor(ptr, n).view(torch.bfloat16)
+            if ones:
+                view.fill_(1.0)
+                return
+            g = torch.Generator(device=dev).manual_seed(gen_seed)
+            chunk = 1 << 26
+            for off in range(0, view.numel(), chunk):
+                m = min(chunk, view.numel() - off)
+                view[off:off + m] = (torch.randn(m, generator=g, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
+
+        fill("embed", 0, seed * 1000 + 1)
+        if not cfg.tie_word_embeddings:
+            fill("lm_head", 0, seed * 1000 + 2)
+        fill("final_norm", 0, 0, ones=True)
+        for l in range(cfg.num_layers):
+            for i, name in enumerate(("qkv", "qkv_bias", "o", "gate_up", "down", "experts_gate_up", "experts_down")):
+                fill(name, l, seed * 1000 + 100 + l * 16 + i + 7919 * (rank + 1))
+            fill("router", l, seed * 1000 + 100 + l * 16 + 15)
+            for name in ("input_norm", "post_norm", "q_norm", "k_norm"):
+                fill(name, l, 0, ones=True)
+        torch.cuda.synchronize()
+
     def load_rope_tables(self, cos: torch.Tensor, sin: torch.Tensor) -> None:
         """Overwrite the RoPE tables with ones built elsewhere (e.g. bit-identical to torch's)."""
         self.load("rope_cos", 0, cos.float())
