@@ -393,6 +393,19 @@ def run_gpu_tp(args):
         lockstep = bool(same.item())
     else:
         lockstep = True
+    # per-kernel timing of attention and all-reduce launches: eager steps, one event pair per launch
+    engine.set_profiling(True)
+    hb.decode(reqs).synchronize()
+    attn_ms = ar_ms = 0.0
+    attn_n = ar_n = 0
+    for _ in range(4):
+        hb.decode(reqs).synchronize()
+        ms, n, _k = engine.read_profile()
+        attn_ms, attn_n = attn_ms + ms, attn_n + n
+        if world > 1:
+            ms, n = engine.read_profile_allreduce()
+            ar_ms, ar_n = ar_ms + ms, ar_n + n
+    engine.set_profiling(False)
     peak, peak_kind = measured_peaks()
     d, L = cfg.head_dim, cfg.num_layers
     per_layer = ((cfg.num_qo_heads + 2 * cfg.num_kv_heads) * d * cfg.hidden_size + cfg.hidden_size * cfg.num_qo_heads * d
@@ -410,6 +423,9 @@ def run_gpu_tp(args):
         "step_roofline": {"algorithmic_bytes_per_step_per_gpu": int(bytes_gpu),
                           "frac_of_measured_hbm": round(bytes_gpu / (dev_ms / K * 1e-3) / 1e9 / peak, 4)},
         "prefill": {"tokens": B * PROMPT, "seconds": round(prefill_s, 3)},
+        "kernels": {"attention_us_per_launch": round(attn_ms * 1e3 / max(attn_n, 1), 2),
+                    "allreduce_us_per_launch": round(ar_ms * 1e3 / max(ar_n, 1), 2) if ar_n else None,
+                    "allreduce_launches_per_step": ar_n // 4},
         "clocks": clocks,
     }
     engine.close()

@@ -412,6 +412,9 @@ B200_API b200_stream_t b200_engine_stream(b200_engine* engine);
 B200_API int b200_engine_set_profiling(b200_engine* engine, int on);
 B200_API int b200_engine_read_profile(b200_engine* engine, float* attention_ms,
                                       int32_t* attention_launches, int32_t* kernel_launches);
+/* The same for the fused all-reduce launches of the last profiled step (tensor parallelism). */
+B200_API int b200_engine_read_profile_allreduce(b200_engine* engine, float* allreduce_ms,
+                                                int32_t* launches);
 
 /* Device time of the last step in milliseconds (CUDA events around it); synchronises. */
 B200_API int b200_engine_last_step_ms(b200_engine* engine, float* ms);

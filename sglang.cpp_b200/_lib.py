@@ -89,6 +89,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_engine_stream": (c_void_p, [_P]),
     "b200_engine_last_step_ms": (_I, [_P, POINTER(c_float)]),
     "b200_engine_set_profiling": (_I, [_P, _I]),
+    "b200_engine_read_profile_allreduce": (_I, [_P, POINTER(c_float), POINTER(c_int32)]),
     "b200_engine_read_profile": (_I, [_P, POINTER(c_float), POINTER(c_int32), POINTER(c_int32)]),
 }
 

@@ -163,6 +163,8 @@ struct b200_engine {
     bool profile_attention = false;
     bool capturing = false;
     std::vector<cudaEvent_t> prof_events;   // 2 per layer
+    std::vector<cudaEvent_t> prof_events_ar;  // 2 per all-reduce call
+    int prof_ar_recorded = 0;
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
@@ -269,9 +271,23 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     auto add_norm = [&](const __nv_bfloat16* w) -> int {
         if (tp && x_is_partial) {
             x_is_partial = false;
-            const int parity = ar_calls++ & 1;
-            return launch_allreduce(e->comm, parity, 1, e->x, e->residual, w, T, hidden, m.rms_norm_eps,
-                                    round_first, e->status, s);
+            const int call = ar_calls++;
+            const bool timed_ar = e->profile_attention && !e->capturing;
+            if (timed_ar) {
+                while (static_cast<int>(e->prof_events_ar.size()) < 2 * (call + 1)) {
+                    cudaEvent_t ev = nullptr;
+                    B200_CHECK_CUDA(cudaEventCreate(&ev));
+                    e->prof_events_ar.push_back(ev);
+                }
+                B200_CHECK_CUDA(cudaEventRecord(e->prof_events_ar[2 * call], s));
+            }
+            int rc = launch_allreduce(e->comm, call & 1, 1, e->x, e->residual, w, T, hidden, m.rms_norm_eps,
+                                      round_first, e->status, s);
+            if (timed_ar) {
+                B200_CHECK_CUDA(cudaEventRecord(e->prof_events_ar[2 * call + 1], s));
+                e->prof_ar_recorded = call + 1;
+            }
+            return rc;
         }
         return launch_fused_add_rmsnorm(e->x, e->residual, w, T, hidden, m.rms_norm_eps, round_first, s);
     };
@@ -563,6 +579,7 @@ int b200_engine_destroy(b200_engine* e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : e->prof_events_ar) cudaEventDestroy(ev);
     if (e->comm) b200_comm_destroy(e->comm);
     for (void* p : e->allocs) cudaFree(p);
     if (e->meta_host) cudaFreeHost(e->meta_host);
@@ -766,6 +783,20 @@ int b200_engine_set_profiling(b200_engine* e, int on) {
     B200_CHECK_ARG(e, "engine_set_profiling: NULL engine");
     e->profile_attention = on != 0;
     e->prof_pairs_recorded = 0;
+    return B200_OK;
+}
+
+int b200_engine_read_profile_allreduce(b200_engine* e, float* allreduce_ms, int32_t* launches) {
+    B200_CHECK_ARG(e, "engine_read_profile_allreduce: NULL engine");
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    float total = 0.f;
+    for (int i = 0; i < e->prof_ar_recorded; ++i) {
+        float ms = 0.f;
+        B200_CHECK_CUDA(cudaEventElapsedTime(&ms, e->prof_events_ar[2 * i], e->prof_events_ar[2 * i + 1]));
+        total += ms;
+    }
+    if (allreduce_ms) *allreduce_ms = total;
+    if (launches) *launches = e->prof_ar_recorded;
     return B200_OK;
 }
 

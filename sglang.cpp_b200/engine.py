@@ -231,6 +231,11 @@ class Engine:
         call("b200_engine_read_profile", self._h, ctypes.byref(ms), ctypes.byref(n), ctypes.byref(k))
         return float(ms.value), int(n.value), int(k.value)
 
+    def read_profile_allreduce(self) -> tuple[float, int]:
+        ms, n = ctypes.c_float(), ctypes.c_int32()
+        call("b200_engine_read_profile_allreduce", self._h, ctypes.byref(ms), ctypes.byref(n))
+        return float(ms.value), int(n.value)
+
     def last_step_ms(self) -> float:
         ms = ctypes.c_float()
         call("b200_engine_last_step_ms", self._h, ctypes.byref(ms))
