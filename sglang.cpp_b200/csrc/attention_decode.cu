@@ -4,9 +4,10 @@
 // Design, in the order the bytes move:
 //   * KV pool layout (one layer): [slots, kv_heads, 128] bf16, so all heads of a
 //     slot are contiguous and a page of P consecutive slots is one dense block.
-//     A TMA tensor map views it as rows of 128 elements; the producer warp copies
-//     boxes of (keys-per-copy x kv_heads) rows x 64 elements with the 128-byte
-//     swizzle into a 3-stage ring of 64 KB stages (K lo/hi halves, V lo/hi halves).
+//     A 3-D TMA tensor map [head][slot][128] views it head-major; the producer warp copies
+//     boxes of (all kv heads x keys-per-copy x 64 elements) with the 128-byte swizzle into a
+//     3-stage ring of 64 KB stages (K lo/hi halves, V lo/hi halves), so the keys of one head
+//     are adjacent 128-byte rows (conflict-free ldmatrix).
 //   * a stage always holds 128 (key, head) rows: 128/kv_heads keys x kv_heads.
 //     Eight consumer warps each own one (head, 16-key group) tile of a stage, so a
 //     warp keeps the same KV head for the whole kernel.
@@ -15,12 +16,12 @@
 //     exp2 domain, O += P V.  Tensor throughput is irrelevant here; mma + ldmatrix
 //     is used because it needs ~10x fewer issue slots than CUDA-core dot products,
 //     which keeps the SM free to run the copy pipeline.
-//   * work items are (request, run of stages); the split is computed on the
-//     device from seq_lens alone (no host plan, graph-replay safe) so that there
-//     are ~8 items per CTA; CTAs take items round-robin and the stage ring runs
-//     across item boundaries, so there is no pipeline bubble between items.
-//   * every warp writes an (m, l, O) partial; the CTA that finishes a request's
-//     last item merges the partials (threadfence + atomic ticket) and writes bf16.
+//   * all stages of all requests form one global sequence that is cut into equal contiguous
+//     runs, one per CTA (computed on the device from seq_lens alone: no host plan, graph-replay
+//     safe), so every CTA streams the same number of bytes; a run is split into items at
+//     request boundaries and the stage ring runs across item boundaries.
+//   * every warp writes an (m, l, O) partial; the CTA that delivers a request's last partial
+//     (threadfence + atomic ticket, looked at after the CTA's last stage) merges and writes bf16.
 #include <mutex>
 
 #include "common.cuh"
