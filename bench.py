@@ -50,11 +50,13 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-def make_prompts(vocab: int):
-    """Seed 2: lengths uniform in [512, 2048], ids uniform over the vocabulary, groups of 4 requests
-    share their first 256 ids."""
+def make_prompts(vocab: int, fixed_len: int = 0):
+    """Seed 2: lengths uniform in [512, 2048] (or all ``fixed_len``), ids uniform over the
+    vocabulary, groups of 4 requests share their first 256 ids."""
     rng = np.random.default_rng(2)
     lens = rng.integers(PROMPT_LO, PROMPT_HI + 1, size=BATCH)
+    if fixed_len:
+        lens[:] = fixed_len
     prompts = []
     for b in range(BATCH):
         if b % 4 == 0:
@@ -151,10 +153,12 @@ def run_gpu(args):
     from sglang_cpp_b200.engine import Engine, EngineConfig
     from sglang_cpp_b200.host_batch import HostBatcher
 
+    if args.eager:
+        os.environ["B200_PDL"] = "0"  # read by the engine at creation
     cfg = O.qwen3_0_6b()
     K, W = args.steps, args.warmup
     total_new = 2 * (K + W) + 24
-    prompts = make_prompts(cfg.vocab_size)
+    prompts = make_prompts(cfg.vocab_size, args.context)
     max_len = max(len(p) for p in prompts) + total_new + 1
     num_pages = sum(math.ceil((len(p) + total_new + 1) / PAGE_SIZE) for p in prompts) + 8
     engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, BATCH, max_len, MAX_EXTEND_TOKENS))
@@ -187,7 +191,8 @@ def run_gpu(args):
         tokens += r.extend_len()
     flush()
     prefill_s = time.perf_counter() - t_prefill0
-    engine.capture_graphs([BATCH])
+    if not args.eager:
+        engine.capture_graphs([BATCH])
     state0 = [(r.cached_len, r.device_len) for r in reqs]
 
     def reset():
@@ -274,8 +279,9 @@ def run_gpu(args):
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts U[512,2048] seed 2, "
-                               "256-token shared prefix per 4 requests, page size 16, greedy",
+        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts %s seed 2, "
+                               "256-token shared prefix per 4 requests, page size 16, greedy"
+                               % ("of %d tokens" % args.context if args.context else "U[512,2048]"),
                    "l2": "inputs larger than L2: each step streams ~%.1f GB of KV and 1.19 GB of weights"
                          % (sum(mean_ctx) * 114688 / 1e9),
                    "parallelism": "replicas" if world > 1 else "single GPU",
@@ -523,7 +529,12 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"],
                     help="c2 (default, the headline metric): Qwen3-0.6B decode, replicas when N > 1; "
                          "c4: Llama-3-8B decode, tensor parallel over the N ranks")
+    ap.add_argument("--context", type=int, default=0,
+                    help="c2 only: give every prompt this length instead of U[512,2048]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true",
+                    help="c2 only: plain launches, no graph replay and no programmatic dependent launches "
+                         "(the form a profiler can list kernel by kernel); not a bench value")
     ap.add_argument("--profile-region", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()

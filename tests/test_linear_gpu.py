@@ -24,6 +24,7 @@ RTOL = 2 ** -7
     (256, 128, 2048),     # Qwen3-MoE router
     (33, 1000, 192),      # N not a multiple of the 128-feature tile
     (300, 512, 256),      # more rows than one slab
+    (64, 151936, 1024),   # Qwen3-0.6B lm_head (tied embedding): 311 MB of weights
     (0, 512, 256),
 ])
 def test_linear_matches_oracle(L, M, N, K):
