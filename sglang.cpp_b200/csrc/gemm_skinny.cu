@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tensormap.cuh"
+#include "tcgen05.cuh"
 
 namespace b200 {
 namespace {
@@ -33,76 +34,6 @@ constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr int kChunkCols = 32;  // token columns per tcgen05.ld
 constexpr int kRoundCols = 64;  // token columns exchanged per cluster round
-
-// ---- tcgen05 wrappers --------------------------------------------------------
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-                 "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 128
-// bytes (64 elements) under the 128-byte swizzle: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);  // start address / 16
-    d |= static_cast<uint64_t>(1) << 16;                     // leading byte offset (unused here)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset / 16
-    d |= static_cast<uint64_t>(1) << 46;                     // descriptor version for sm_100
-    d |= static_cast<uint64_t>(2) << 61;                     // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M=128.
-__device__ __forceinline__ uint32_t idesc_bf16_m128(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(128 >> 4) << 24);
-}
 
 // ---- cluster helpers ----------------------------------------------------------
 
@@ -461,6 +392,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     B200_TRACE(7);
 }
 
+}  // namespace
+
 struct TmapCacheEntry {
     const void* base;
     uint64_t inner, outer, pitch;
@@ -491,12 +424,10 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t out
     return B200_OK;
 }
 
-int env_int(const char* name, int dflt) {
+static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return (v && *v) ? atoi(v) : dflt;
 }
-
-}  // namespace
 
 // One slab of at most 256 rows.
 int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, int M, int N,
@@ -632,6 +563,9 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
 
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                   int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
+    // Few rows: stream the weights once (swap-AB, split-K).  Many rows: tensor-bound tiles.
+    if (M >= env_int("B200_GEMM_TILE_MIN_M", 257))
+        return launch_tile_gemm(y, x, w, bias, M, N, K, ldx, epilogue, status, stream);
     const int n_out = epilogue != B200_EPILOGUE_NONE ? N / 2 : N;
     const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
     __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);

@@ -29,6 +29,15 @@ int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   cudaStream_t stream);
 
+// Tensor map of a 2-D bf16 tensor [outer, inner] copied in [box_outer, box_inner] boxes with the
+// 128-byte swizzle, from a small per-thread cache (the same buffers come back every layer).
+int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                uint32_t box_inner, uint32_t box_outer);
+
+// Large-M GEMM (prefill batches): persistent 128 x 256 output tiles on the tcgen05 tensor cores.
+int launch_tile_gemm(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
+                     int64_t ldx, int epilogue, int* status, cudaStream_t stream);
+
 // y[M, n_out] = x[M, K] w[N, K]^T (+bias / gated epilogue); any M (slabs of 256 rows).
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                   int64_t ldx, int epilogue, int* status, cudaStream_t stream);

@@ -66,6 +66,51 @@ def test_gate_up_swiglu_epilogue(L, pkg, M, I, K):
     assert_close_bf16(y, out, 4e-3, 3 * RTOL, "fused vs unfused SwiGLU")
 
 
+@pytest.mark.parametrize("M,N,K", [
+    (257, 256, 64),       # smallest prefill-path case: 3 token blocks, one k-block
+    (1000, 1000, 192),    # ragged in M and N
+    (2048, 4096, 1024),   # one full band, Qwen3-0.6B qkv
+    (4500, 1024, 3072),   # more than two bands, down_proj
+    (8192, 512, 128),     # more tiles per CTA than accumulators
+])
+def test_linear_prefill_tiles_match_oracle(L, M, N, K):
+    """Batches of more than 256 rows take the persistent 128 x 256 tile kernel."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    x = randn_bf16(gen, M, K)
+    w = randn_bf16(gen, N, K, std=0.05)
+    b = randn_bf16(gen, N)
+    y = L.linear(x.cuda(), w.cuda(), b.cuda())
+    assert y.shape == (M, N)
+    assert_close_bf16(y, O.linear(x, w, b), 2e-3 * (K / 1024) ** 0.5 + 1e-3, RTOL, f"tile linear {M}x{N}x{K}")
+    assert L.read_device_status() == (0, 0)
+
+
+def test_linear_prefill_tiles_equal_slab_path(L, monkeypatch):
+    """The tile kernel and the 256-row slab path agree (fp32 accumulation in k order on both)."""
+    gen = torch.Generator().manual_seed(21)
+    buf = randn_bf16(gen, 700, 1536)
+    w = randn_bf16(gen, 1000, 1024, std=0.05)
+    xs = buf.cuda()[:, 256:1280]                      # row stride 1536, K = 1024
+    y_tile = L.linear(xs, w.cuda())
+    monkeypatch.setenv("B200_GEMM_TILE_MIN_M", "1000000")
+    monkeypatch.setenv("B200_GEMM_SPLIT", "1")
+    y_slab = L.linear(xs, w.cuda())
+    monkeypatch.delenv("B200_GEMM_TILE_MIN_M")
+    monkeypatch.delenv("B200_GEMM_SPLIT")
+    assert torch.equal(y_tile, y_slab)
+
+
+@pytest.mark.parametrize("M,I,K", [(300, 768, 2048), (2048, 3072, 1024), (513, 200, 64)])
+def test_gate_up_swiglu_prefill_tiles(L, pkg, M, I, K):
+    gen = torch.Generator().manual_seed(M + I)
+    x = randn_bf16(gen, M, K)
+    w = randn_bf16(gen, 2 * I, K, std=0.05)
+    y = L.linear(x.cuda(), w.cuda(), epilogue=pkg.EPILOGUE_SWIGLU)
+    assert y.shape == (M, I)
+    assert_close_bf16(y, O.silu_and_mul(O.linear(x, w)), 4e-3, 3 * RTOL, "tile gate_up + SwiGLU")
+    assert L.read_device_status() == (0, 0)
+
+
 def test_linear_split_k_variants_agree(L, monkeypatch):
     """Every cluster size gives the same result up to fp32 summation order."""
     import os
