@@ -130,17 +130,34 @@ class HostBatcher:
         return self._mirror[req.table_idx]
 
     # ---- steps --------------------------------------------------------------
-    def prefill(self, reqs):
-        """One prefill step over `reqs` (each runs positions [cached_len, device_len))."""
+    def prefill(self, reqs, chunk_tokens: Optional[int] = None, sampling: Optional[dict] = None):
+        """One prefill step over `reqs` (each runs positions [cached_len, device_len)).
+
+        With ``chunk_tokens`` a request whose remaining prompt is longer runs only that many tokens
+        this step (the chunked request of src/scheduler/prefill.cc:301-330,382-400): its sampled token is dropped
+        (write position -1) and the next call continues where this one stopped.  ``sampling`` holds
+        per-request ``temperatures / top_k / top_p / seeds`` (BatchSamplingArgs)."""
+        partial = []
+        for r in reqs:
+            full = len(r.input_ids)
+            if r.device_len < full:          # continuing a chunked request
+                r.device_len = full
+            cut = chunk_tokens is not None and r.extend_len() > chunk_tokens
+            if cut:
+                r.device_len = r.cached_len + chunk_tokens
+            partial.append(cut)
         self.allocate(reqs)
         out = self.engine.forward_batch(
             0, [r.table_idx for r in reqs], [r.cached_len for r in reqs], [r.extend_len() for r in reqs],
-            write_pos=[r.write_pos() for r in reqs])
-        for r in reqs:
-            r.complete_one()
+            write_pos=[-1 if cut else r.write_pos() for r, cut in zip(reqs, partial)], **(sampling or {}))
+        for r, cut in zip(reqs, partial):
+            if cut:
+                r.cached_len = r.device_len
+            else:
+                r.complete_one()
         return out
 
-    def decode(self, reqs, padded_size: Optional[int] = None):
+    def decode(self, reqs, padded_size: Optional[int] = None, sampling: Optional[dict] = None):
         """One decode step; pads with the dummy request up to `padded_size`."""
         self.allocate(reqs)
         n = len(reqs)
@@ -149,7 +166,7 @@ class HostBatcher:
         out = self.engine.forward_batch(
             1, [r.table_idx for r in reqs] + [dummy] * (bp - n),
             [r.cached_len for r in reqs] + [0] * (bp - n), [1] * bp,
-            write_pos=[r.write_pos() for r in reqs], num_reqs=n)
+            write_pos=[r.write_pos() for r in reqs], num_reqs=n, **(sampling or {}))
         for r in reqs:
             r.complete_one()
         return out
