@@ -186,6 +186,20 @@ B200_API int b200_moe_forward(void* out, const void* hidden_states, const void* 
                               int renormalize, int activation, void* workspace,
                               int64_t workspace_bytes, b200_stream_t stream);
 
+/* One rank's share of MoELayer::forward under expert parallelism.  No counterpart in the
+ * reference, whose MoELayer gives every rank a slice of every expert's intermediate dimension
+ * (src/moe/moe.cc:12-30); here the rank holds whole experts [expert_begin, expert_begin +
+ * num_local_experts) of the router's num_experts: gate_up_proj bf16 [num_local_experts, 2*I,
+ * hidden], down_proj bf16 [num_local_experts, hidden, I].  Routing runs over all experts; only
+ * the local experts' terms are summed into out (rows with none are zero); the all-reduce the
+ * caller runs next (tensor_model_parallel_all_reduce, src/moe/moe.cc:92-94) adds the ranks. */
+B200_API int b200_moe_forward_local(void* out, const void* hidden_states, const void* router_logits,
+                                    const void* gate_up_proj, const void* down_proj, int tokens,
+                                    int num_experts, int top_k, int hidden_size,
+                                    int intermediate_size, int renormalize, int activation,
+                                    int expert_begin, int num_local_experts, void* workspace,
+                                    int64_t workspace_bytes, b200_stream_t stream);
+
 /* ---- attention (include/sglang/attention/backend.h:24-41) ------------------ */
 
 /* Bytes of scratch b200_attention_decode needs for up to max_batch requests
@@ -334,6 +348,9 @@ typedef struct b200_engine_config {
     int32_t max_extend_tokens; /* most tokens one prefill step may carry */
     int32_t tp_rank;
     int32_t tp_size;
+    int32_t expert_parallel;   /* MoE models under tp_size > 1: 0 = every rank holds a slice of every
+                                  expert's intermediate dimension (the reference's layout), 1 = rank r
+                                  holds whole experts [r*E/tp, (r+1)*E/tp) */
 } b200_engine_config;
 
 enum { B200_PHASE_PREFILL = 0, B200_PHASE_DECODE = 1 };

@@ -165,10 +165,15 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 def moe_forward(hidden: torch.Tensor, router_logits: torch.Tensor, gate_up: torch.Tensor,
                 down: torch.Tensor, top_k: int, renormalize: bool, activation: str = "silu",
-                store: Store = store_bf16) -> torch.Tensor:
+                store: Store = store_bf16, expert_begin: int = 0) -> torch.Tensor:
     """MoELayer::forward (src/moe/moe.cc:36-96), loop order and rounding points included:
     fp32 softmax -> top-k -> optional renormalisation -> weights cast to the activation dtype ->
-    for k, for expert: linear, act*up, linear, scale, index_add_."""
+    for k, for expert: linear, act*up, linear, scale, index_add_.
+
+    ``expert_begin`` (no counterpart in the reference, which shards every expert's intermediate
+    dimension instead): gate_up / down hold only experts [expert_begin, expert_begin + len) of the
+    router's range and only their contributions are summed — one rank's share under expert
+    parallelism, to be summed over ranks by the all-reduce that follows."""
     h = hidden.to(f32)
     probs = torch.softmax(router_logits.to(f32), -1)
     tw, ti = probs.topk(top_k, -1)
@@ -177,7 +182,7 @@ def moe_forward(hidden: torch.Tensor, router_logits: torch.Tensor, gate_up: torc
     out = torch.zeros_like(h)
     E = gate_up.shape[0]
     for k in range(top_k):
-        ids = ti[:, k]
+        ids = ti[:, k] - expert_begin
         w = store(tw[:, k])
         for e in range(E):
             idx = torch.nonzero(ids == e).squeeze(1)
@@ -340,11 +345,14 @@ class OracleModel:
     (src/models/qwen3.cc:21-35,55-66,84-87; llama.cc:15-29,49-55,74-77; qwen3_moe.cc:14-28;
     src/models/utils.cc:8-19,41-57,82-91,138-142; src/layers/attention_layer.cc:17-51)."""
 
-    def __init__(self, cfg: ModelConfig, weights: dict, store: Store = store_bf16, all_reduce=None):
+    def __init__(self, cfg: ModelConfig, weights: dict, store: Store = store_bf16, all_reduce=None,
+                 expert_begin: int = 0):
         """all_reduce: under tensor parallelism, a callable that sums a tensor over the ranks
         (tensor_model_parallel_all_reduce, src/distributed/distributed.cc:205-226); cfg then holds
-        the per-rank head counts and intermediate size and weights the rank's shard."""
+        the per-rank head counts and intermediate size and weights the rank's shard.
+        expert_begin: under expert parallelism, the first expert this rank holds."""
         self.all_reduce = all_reduce
+        self.expert_begin = expert_begin
         self.cfg = cfg
         # Up-cast the (bf16-rounded) weights to fp32 once; tied tensors stay tied.
         cache: dict[int, torch.Tensor] = {}
@@ -390,7 +398,8 @@ class OracleModel:
         if cfg.num_experts > 0:
             logits = linear(x, L["router"], None, st)
             return self._reduce(moe_forward(x, logits, L["experts_gate_up"], L["experts_down"],
-                                            cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.hidden_act, st))
+                                            cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.hidden_act, st,
+                                            self.expert_begin))
         gu = linear(x, L["gate_up"], None, st)
         y = silu_and_mul(gu, st) if cfg.hidden_act == "silu" else gelu_and_mul(gu, st)
         return self._reduce(linear(y, L["down"], None, st))

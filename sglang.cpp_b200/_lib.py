@@ -61,6 +61,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_moe_workspace_bytes": (_L, [_I, _I, _I, _I, _I]),
     "b200_moe_route": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "b200_moe_forward": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P]),
+    "b200_moe_forward_local": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P]),
     "b200_attention_decode_workspace_bytes": (_L, [_I, _I, _I, _I]),
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
     "b200_attention_decode_noalloc": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
@@ -112,7 +113,7 @@ class EngineConfigStruct(ctypes.Structure):
     _fields_ = [
         ("page_size", c_int32), ("num_pages", c_int32), ("max_running_req", c_int32),
         ("max_seq_len", c_int32), ("max_extend_tokens", c_int32), ("tp_rank", c_int32),
-        ("tp_size", c_int32),
+        ("tp_size", c_int32), ("expert_parallel", c_int32),
     ]
 
 

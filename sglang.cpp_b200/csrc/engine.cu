@@ -119,6 +119,7 @@ struct b200_engine {
     b200_engine_config c;
     int device = 0;
     int hq = 0, hkv = 0, inter = 0, qkv_dim = 0;  // per-rank sizes
+    int moe_inter = 0, experts_local = 0, expert_begin = 0;  // per-rank expert layout
     int64_t num_slots = 0;
     int pt_rows = 0, pt_cols = 0;
     int max_tokens = 0, max_batch = 0;
@@ -335,9 +336,9 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             B200_TRY(launch_linear(e->router_logits, e->x, L.router, nullptr, T, m.num_experts, hidden, hidden,
                                    B200_EPILOGUE_NONE, e->status, s));
             B200_TRY(launch_moe_forward(proj_out(), e->x, e->router_logits, L.experts_gate_up, L.experts_down, T,
-                                        m.num_experts, m.num_experts_per_tok, hidden,
-                                        m.moe_intermediate_size / e->c.tp_size, m.norm_topk_prob,
-                                        m.hidden_act == 1 ? 1 : 0, e->moe_ws, e->status, s));
+                                        m.num_experts, m.num_experts_per_tok, hidden, e->moe_inter,
+                                        m.norm_topk_prob, m.hidden_act == 1 ? 1 : 0, e->expert_begin,
+                                        e->experts_local, e->moe_ws, e->status, s));
             continue;
         }
         B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
@@ -444,14 +445,23 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
                    "engine_create: hidden and intermediate sizes must be multiples of 64");
     B200_CHECK_ARG(c.tp_size >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "engine_create: bad TP rank/size");
     B200_CHECK_ARG(m.num_qo_heads % c.tp_size == 0, "num_qo_heads must be divisible by tp_size");
-    B200_CHECK_ARG(m.num_kv_heads % c.tp_size == 0, "num_kv_heads must be divisible by tp_size");
+    // Fewer KV heads than ranks: each KV head is replicated on tp_size / num_kv_heads ranks.
+    B200_CHECK_ARG(m.num_kv_heads % c.tp_size == 0 || c.tp_size % m.num_kv_heads == 0,
+                   "num_kv_heads must divide, or be divisible by, tp_size");
+    if (m.num_experts > 0 && c.expert_parallel) {
+        B200_CHECK_ARG(m.num_experts % c.tp_size == 0, "num_experts must be divisible by tp_size");
+        B200_CHECK_ARG(m.moe_intermediate_size % 64 == 0, "MoELayer intermediate size must be a multiple of 64");
+    } else if (m.num_experts > 0) {
+        B200_CHECK_ARG(m.moe_intermediate_size % (64 * c.tp_size) == 0,
+                       "MoELayer intermediate size / tp_size must be a multiple of 64");
+    }
     B200_CHECK_ARG(m.intermediate_size % (64 * c.tp_size) == 0 || m.num_experts > 0,
                    "intermediate_size / tp_size must be a multiple of 64");
     B200_CHECK_ARG(c.page_size >= 1 && (c.page_size & (c.page_size - 1)) == 0,
                    "engine_create: page_size must be a power of two");
     B200_CHECK_ARG(c.num_pages >= 1 && c.max_running_req >= 1 && c.max_seq_len >= 1 && c.max_extend_tokens >= 1,
                    "engine_create: bad engine sizes");
-    const int hkv = m.num_kv_heads / c.tp_size;
+    const int hkv = m.num_kv_heads >= c.tp_size ? m.num_kv_heads / c.tp_size : 1;
     B200_CHECK_ARG(hkv <= 8 && 8 % hkv == 0, "engine_create: kv heads per rank must be 1, 2, 4 or 8");
 
     b200_engine* e = new b200_engine();
@@ -460,6 +470,12 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     B200_CHECK_CUDA(cudaGetDevice(&e->device));
     e->hq = m.num_qo_heads / c.tp_size;
     e->hkv = hkv;
+    if (m.num_experts > 0) {
+        const bool ep = c.expert_parallel != 0;
+        e->moe_inter = ep ? m.moe_intermediate_size : m.moe_intermediate_size / c.tp_size;
+        e->experts_local = ep ? m.num_experts / c.tp_size : m.num_experts;
+        e->expert_begin = ep ? c.tp_rank * e->experts_local : 0;
+    }
     e->inter = m.intermediate_size / c.tp_size;
     e->qkv_dim = (e->hq + 2 * e->hkv) * m.head_dim;
     e->num_slots = static_cast<int64_t>(c.num_pages + 1) * c.page_size;
@@ -514,10 +530,10 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
             E_TRY(named_alloc(e, &L.k_norm, "k_norm" + sfx, D));
         }
         if (m.num_experts > 0) {
-            const int64_t ie = m.moe_intermediate_size / c.tp_size;
+            const int64_t ie = e->moe_inter, el = e->experts_local;
             E_TRY(named_alloc(e, &L.router, "router" + sfx, static_cast<int64_t>(m.num_experts) * H));
-            E_TRY(named_alloc(e, &L.experts_gate_up, "experts_gate_up" + sfx, static_cast<int64_t>(m.num_experts) * 2 * ie * H));
-            E_TRY(named_alloc(e, &L.experts_down, "experts_down" + sfx, static_cast<int64_t>(m.num_experts) * H * ie));
+            E_TRY(named_alloc(e, &L.experts_gate_up, "experts_gate_up" + sfx, el * 2 * ie * H));
+            E_TRY(named_alloc(e, &L.experts_down, "experts_down" + sfx, el * H * ie));
         } else {
             E_TRY(named_alloc(e, &L.gate_up, "gate_up" + sfx, 2 * static_cast<int64_t>(e->inter) * H));
             E_TRY(named_alloc(e, &L.down, "down" + sfx, H * e->inter));
@@ -546,7 +562,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
         E_TRY(named_alloc(e, &e->router_logits, "router_logits", Tm * m.num_experts));
         E_TRY(dev_alloc(e, &e->moe_ws,
                         moe_workspace_bytes(static_cast<int>(Tm), m.num_experts, m.num_experts_per_tok, m.hidden_size,
-                                            m.moe_intermediate_size / c.tp_size),
+                                            e->moe_inter),
                         false));
     }
     e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);

@@ -50,7 +50,8 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
 int64_t moe_workspace_bytes(int tokens, int E, int top_k, int H, int I);
 int launch_moe_forward(void* out, const void* hidden, const void* router_logits, const void* gate_up,
                        const void* down, int tokens, int E, int top_k, int H, int I, int renorm,
-                       int activation, void* workspace, int* status, cudaStream_t stream);
+                       int activation, int expert_begin, int num_local_experts, void* workspace,
+                       int* status, cudaStream_t stream);
 
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);

@@ -80,14 +80,17 @@ moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int tokens, int E, in
     }
 }
 
+// Row ranges of the experts [e_begin, e_begin + e_count) this call computes (all of them unless
+// the experts are partitioned over ranks); every other expert gets offset -1 = "not here".
 __global__ void __launch_bounds__(256)
 moe_scan_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
-                int32_t* __restrict__ cursor, int E) {
+                int32_t* __restrict__ cursor, int E, int e_begin, int e_count) {
     pdl_launch_dependents();
     pdl_wait_prior();
     __shared__ int s[256];
     const int e = threadIdx.x;
-    s[e] = e < E ? counts[e] : 0;
+    const bool local = e >= e_begin && e < e_begin + e_count;
+    s[e] = (e < E && local) ? counts[e] : 0;
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -100,7 +103,7 @@ moe_scan_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ offset
     }
     __syncthreads();
     if (e < E) {
-        offsets[e] = s[e];
+        offsets[e] = local ? s[e] : -1;
         cursor[e] = 0;
     }
 }
@@ -116,10 +119,12 @@ moe_scatter_kernel(const uint4* __restrict__ hidden, uint4* __restrict__ xp,
     const int pair = blockIdx.x;
     if (threadIdx.x == 0) {
         const int e = ids[pair];
-        s_row = offsets[e] + atomicAdd(&cursor[e], 1);
+        const int base = offsets[e];
+        s_row = base < 0 ? -1 : base + atomicAdd(&cursor[e], 1);
         pos[pair] = s_row;
     }
     __syncthreads();
+    if (s_row < 0) return;  // another rank's expert
     const uint4* src = hidden + static_cast<int64_t>(pair / top_k) * vec_per_row;
     uint4* dst = xp + static_cast<int64_t>(s_row) * vec_per_row;
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
@@ -136,7 +141,9 @@ moe_combine_kernel(uint4* __restrict__ out, const uint4* __restrict__ y, const i
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < top_k; ++k) {
             const float w = weights[t * top_k + k];
-            const uint4 a = y[static_cast<int64_t>(pos[t * top_k + k]) * vec_per_row + v];
+            const int row = pos[t * top_k + k];
+            if (row < 0) continue;  // another rank's expert: its term arrives through the all-reduce
+            const uint4 a = y[static_cast<int64_t>(row) * vec_per_row + v];
             const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -200,7 +207,8 @@ int launch_moe_route(int32_t* ids, float* weights, int32_t* counts, const void* 
 
 int launch_moe_forward(void* out, const void* hidden, const void* router_logits, const void* gate_up,
                        const void* down, int tokens, int E, int top_k, int H, int I, int renorm,
-                       int activation, void* workspace, int* status, cudaStream_t stream) {
+                       int activation, int expert_begin, int num_local_experts, void* workspace,
+                       int* status, cudaStream_t stream) {
     if (tokens == 0) return B200_OK;
     MoeWorkspace w;
     carve(&w, static_cast<uint8_t*>(workspace), tokens, E, top_k, H, I);
@@ -208,17 +216,21 @@ int launch_moe_forward(void* out, const void* hidden, const void* router_logits,
     int err = launch_moe_route(w.ids, w.weights, w.counts, router_logits, tokens, E, top_k, renorm, stream);
     if (err != B200_OK) return err;
     B200_CHECK_CUDA(launch_kernel(moe_scan_kernel, dim3(1), dim3(256), 0, stream, dim3(1, 1, 1),
-                                  static_cast<const int32_t*>(w.counts), w.offsets, w.cursor, E));
+                                  static_cast<const int32_t*>(w.counts), w.offsets, w.cursor, E, expert_begin,
+                                  num_local_experts));
     B200_CHECK_CUDA(launch_kernel(moe_scatter_kernel, dim3(pairs), dim3(128), 0, stream, dim3(1, 1, 1),
                                   static_cast<const uint4*>(hidden), reinterpret_cast<uint4*>(w.xp),
                                   static_cast<const int32_t*>(w.ids), static_cast<const int32_t*>(w.offsets),
                                   w.cursor, w.pos, top_k, H / 8));
     const int epi = activation == 1 ? B200_EPILOGUE_GEGLU_ERF : B200_EPILOGUE_SWIGLU;
     // A token picks distinct experts, so no expert gets more rows than there are tokens.
-    err = launch_grouped_gemm(w.hact, w.xp, gate_up, w.counts, w.offsets, E, tokens, pairs, 2 * I, H, epi,
-                              status, stream);
+    // gate_up / down hold the local experts only, so group g is expert expert_begin + g.
+    const int32_t* counts = w.counts + expert_begin;
+    const int32_t* offsets = w.offsets + expert_begin;
+    err = launch_grouped_gemm(w.hact, w.xp, gate_up, counts, offsets, num_local_experts, tokens, pairs, 2 * I, H,
+                              epi, status, stream);
     if (err != B200_OK) return err;
-    err = launch_grouped_gemm(w.y2, w.hact, down, w.counts, w.offsets, E, tokens, pairs, H, I,
+    err = launch_grouped_gemm(w.y2, w.hact, down, counts, offsets, num_local_experts, tokens, pairs, H, I,
                               B200_EPILOGUE_NONE, status, stream);
     if (err != B200_OK) return err;
     B200_CHECK_CUDA(launch_kernel(moe_combine_kernel, dim3(tokens), dim3(128), 0, stream, dim3(1, 1, 1),
@@ -249,10 +261,11 @@ int b200_moe_route(int32_t* topk_ids, float* topk_weights, int32_t* expert_count
                                   top_k, renormalize, static_cast<cudaStream_t>(stream));
 }
 
-int b200_moe_forward(void* out, const void* hidden_states, const void* router_logits, const void* gate_up_proj,
-                     const void* down_proj, int tokens, int num_experts, int top_k, int hidden_size,
-                     int intermediate_size, int renormalize, int activation, void* workspace,
-                     int64_t workspace_bytes, b200_stream_t stream) {
+int b200_moe_forward_local(void* out, const void* hidden_states, const void* router_logits,
+                           const void* gate_up_proj, const void* down_proj, int tokens, int num_experts,
+                           int top_k, int hidden_size, int intermediate_size, int renormalize,
+                           int activation, int expert_begin, int num_local_experts, void* workspace,
+                           int64_t workspace_bytes, b200_stream_t stream) {
     B200_CHECK_ARG(tokens >= 0, "MoELayer token count must be >= 0");
     B200_CHECK_ARG(num_experts > 0 && num_experts <= 256, "MoELayer requires 0 < num_experts <= 256");
     B200_CHECK_ARG(top_k > 0 && top_k <= b200::kMaxTopK, "MoELayer requires 0 < top_k <= 16");
@@ -261,6 +274,8 @@ int b200_moe_forward(void* out, const void* hidden_states, const void* router_lo
     B200_CHECK_ARG(intermediate_size > 0 && intermediate_size % 64 == 0,
                    "MoELayer intermediate size must be a positive multiple of 64");
     B200_CHECK_ARG(activation == 0 || activation == 1, "Unsupported MoE activation function");
+    B200_CHECK_ARG(expert_begin >= 0 && num_local_experts > 0 && expert_begin + num_local_experts <= num_experts,
+                   "moe_forward: local expert range outside [0, num_experts)");
     if (tokens == 0) return B200_OK;
     B200_CHECK_ARG(out && hidden_states && router_logits && gate_up_proj && down_proj && workspace,
                    "moe_forward: NULL tensor");
@@ -271,7 +286,17 @@ int b200_moe_forward(void* out, const void* hidden_states, const void* router_lo
     if (err != B200_OK) return err;
     return b200::launch_moe_forward(out, hidden_states, router_logits, gate_up_proj, down_proj, tokens,
                                     num_experts, top_k, hidden_size, intermediate_size, renormalize, activation,
-                                    workspace, status, static_cast<cudaStream_t>(stream));
+                                    expert_begin, num_local_experts, workspace, status,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int b200_moe_forward(void* out, const void* hidden_states, const void* router_logits, const void* gate_up_proj,
+                     const void* down_proj, int tokens, int num_experts, int top_k, int hidden_size,
+                     int intermediate_size, int renormalize, int activation, void* workspace,
+                     int64_t workspace_bytes, b200_stream_t stream) {
+    return b200_moe_forward_local(out, hidden_states, router_logits, gate_up_proj, down_proj, tokens, num_experts,
+                                  top_k, hidden_size, intermediate_size, renormalize, activation, 0,
+                                  num_experts > 0 ? num_experts : 1, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

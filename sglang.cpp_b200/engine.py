@@ -32,6 +32,7 @@ class EngineConfig:
     max_extend_tokens: int = 8192
     tp_rank: int = 0
     tp_size: int = 1
+    expert_parallel: bool = False   # MoE under TP: whole experts per rank instead of slices of each
 
 
 def _i32(a) -> np.ndarray:
@@ -66,7 +67,7 @@ class Engine:
             int(model_config.norm_topk_prob))
         c = EngineConfigStruct(config.page_size, config.num_pages, config.max_running_req,
                                config.max_seq_len, config.max_extend_tokens, config.tp_rank,
-                               config.tp_size)
+                               config.tp_size, int(config.expert_parallel))
         self._h = ctypes.c_void_p()
         call("b200_engine_create", ctypes.byref(m), ctypes.byref(c), ctypes.byref(self._h))
         self._next_tokens_cpu = torch.empty(config.max_running_req + 1, dtype=torch.int32).pin_memory()
@@ -108,7 +109,7 @@ class Engine:
             self.load("lm_head", 0, w["lm_head"])
         self.load("final_norm", 0, w["final_norm"])
         for l, L in enumerate(w["layers"]):
-            for name, t in shard_layer(cfg, L, tp_rank, tp_size).items():
+            for name, t in shard_layer(cfg, L, tp_rank, tp_size, self.config.expert_parallel).items():
                 self.load(name, l, t)
 
     def connect_tp(self, group=None) -> None:

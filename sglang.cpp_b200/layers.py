@@ -343,7 +343,10 @@ class MoELayer:
     """include/sglang/moe/moe.h:9-35, src/moe/moe.cc:7-96 (tp_size 1)."""
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
-                 renormalize: bool = False, activation: str = "silu", device="cuda"):
+                 renormalize: bool = False, activation: str = "silu", device="cuda",
+                 expert_begin: int = 0, num_local_experts: Optional[int] = None):
+        """expert_begin / num_local_experts (not in the reference): hold only that slice of the
+        router's experts; forward then returns this rank's partial sum."""
         _check(num_experts > 0, "MoELayer requires num_experts > 0")
         _check(top_k > 0, "MoELayer requires top_k > 0")
         _check(top_k <= num_experts, "MoELayer top_k must be <= num_experts")
@@ -353,8 +356,10 @@ class MoELayer:
         self.num_experts_, self.top_k_ = num_experts, top_k
         self.hidden_size_, self.intermediate_size_ = hidden_size, intermediate_size
         self.renormalize_, self.activation_ = renormalize, activation
-        self.gate_up_proj = torch.empty(num_experts, 2 * intermediate_size, hidden_size, dtype=bf16, device=device)
-        self.down_proj = torch.empty(num_experts, hidden_size, intermediate_size, dtype=bf16, device=device)
+        self.expert_begin_ = expert_begin
+        self.num_local_ = num_experts if num_local_experts is None else num_local_experts
+        self.gate_up_proj = torch.empty(self.num_local_, 2 * intermediate_size, hidden_size, dtype=bf16, device=device)
+        self.down_proj = torch.empty(self.num_local_, hidden_size, intermediate_size, dtype=bf16, device=device)
         self.w1, self.w2 = self.gate_up_proj, self.down_proj
         self._ws = None
 
@@ -372,11 +377,11 @@ class MoELayer:
         if self._ws is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=hidden_states.device)
         out = torch.empty_like(hidden_states)
-        call("b200_moe_forward", out.data_ptr(), hidden_states.contiguous().data_ptr(),
+        call("b200_moe_forward_local", out.data_ptr(), hidden_states.contiguous().data_ptr(),
              router_logits.contiguous().data_ptr(), self.gate_up_proj.data_ptr(), self.down_proj.data_ptr(), T,
              self.num_experts_, self.top_k_, self.hidden_size_, self.intermediate_size_,
-             1 if self.renormalize_ else 0, 1 if self.activation_ == "gelu" else 0, self._ws.data_ptr(),
-             self._ws.numel(), _stream())
+             1 if self.renormalize_ else 0, 1 if self.activation_ == "gelu" else 0, self.expert_begin_,
+             self.num_local_, self._ws.data_ptr(), self._ws.numel(), _stream())
         return out
 
 

@@ -60,6 +60,35 @@ def test_moe_forward_matches_oracle(L, T, E, k, H, I, renorm, act):
     assert L.read_device_status() == (0, 0)
 
 
+@pytest.mark.parametrize("T,E,k,H,I,parts", [(64, 16, 4, 256, 128, 4), (256, 128, 8, 2048, 768, 8), (5, 8, 2, 64, 64, 2)])
+def test_moe_expert_partition_matches_oracle_share(L, T, E, k, H, I, parts):
+    """Expert parallelism: a rank holding experts [b, b + E/parts) returns exactly the oracle's
+    share for that range, rows whose experts all live elsewhere come back zero, and the shares
+    add up (in fp32) to the whole layer within the rounding of the partial sums."""
+    gen = torch.Generator().manual_seed(T + E + parts)
+    hidden = randn_bf16(gen, T, H)
+    logits = distinct_router_logits(gen, T, E)
+    gu = randn_bf16(gen, E, 2 * I, H, std=H ** -0.5)
+    dn = randn_bf16(gen, E, H, I, std=I ** -0.5)
+    el = E // parts
+    total = torch.zeros(T, H)
+    for r in range(parts):
+        moe = L.MoELayer(E, k, H, I, True, "silu", expert_begin=r * el, num_local_experts=el)
+        moe.gate_up_proj.copy_(gu[r * el:(r + 1) * el].cuda())
+        moe.down_proj.copy_(dn[r * el:(r + 1) * el].cuda())
+        got = moe.forward(hidden.cuda(), logits.cuda())
+        want = O.moe_forward(hidden, logits, gu[r * el:(r + 1) * el], dn[r * el:(r + 1) * el], k, True, "silu",
+                             O.store_bf16, expert_begin=r * el)
+        assert_close_bf16(got, want, 2e-2, 4 * 2 ** -7, f"moe share of rank {r}/{parts}")
+        ids = torch.softmax(logits.float(), -1).topk(k, -1).indices
+        nothing_here = ~((ids >= r * el) & (ids < (r + 1) * el)).any(-1)
+        assert torch.all(got.cpu()[nothing_here] == 0)
+        total += got.float().cpu()
+    whole = O.moe_forward(hidden, logits, gu, dn, k, True, "silu", O.store_bf16)
+    assert_close_bf16(total, whole, 3e-2, 8 * 2 ** -7, "sum of the shares")
+    assert L.read_device_status() == (0, 0)
+
+
 def test_moe_rejects_bad_arguments(L, pkg):
     with pytest.raises(pkg.B200Error):
         L.MoELayer(4, 5, 64, 64)            # top_k > num_experts

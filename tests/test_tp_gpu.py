@@ -18,9 +18,12 @@ def _free_port():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tp2_engine_matches_unsharded_oracle(tmp_path):
+@pytest.mark.parametrize("kind", ["llama", "moe_ep"])
+def test_tp2_engine_matches_unsharded_oracle(tmp_path, kind):
+    """llama: heads and MLP columns split over the two GPUs.  moe_ep: experts partitioned over the
+    GPUs (expert parallelism riding on the fused all-reduce) and the single kv head replicated."""
     out = tmp_path / "tp_gpu.pt"
-    mp.spawn(tp_workers.gpu_engine_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    mp.spawn(tp_workers.gpu_engine_worker, args=(2, _free_port(), str(out), kind), nprocs=2, join=True)
     r = torch.load(out)
     assert r["ranks_agree"], "the two ranks produced different logits or tokens"
     d = (r["prefill"].float() - r["want_prefill"].float()).abs()

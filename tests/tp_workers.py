@@ -12,9 +12,14 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 
-def _cfg():
+def _cfg(kind="llama"):
     from oracle import token_loop_oracle as O
 
+    if kind == "moe_ep":
+        # Qwen3-MoE wiring, 8 experts top-2 partitioned over the ranks, and ONE kv head for 4 q heads
+        # so that the kv head is replicated on both ranks (the shape of the 30B-A3B config at 8 GPUs)
+        return O.ModelConfig(2, 256, 4, 1, 128, 512, 1024, 1e-6, 1e6, 256, False, True, True, "silu",
+                             8, 2, 128, True)
     # Llama wiring (the TP benchmark architecture), 2 layers, 4 q / 2 kv heads so that 2 ranks divide them
     return O.ModelConfig(2, 256, 4, 2, 128, 512, 1024, 1e-5, 5e5, 256, False, False, False)
 
@@ -37,7 +42,7 @@ def _batch(cfg, prompts):
                        np.array(qo, np.int32), True), pt, cur
 
 
-def cpu_oracle_worker(rank, world, port, out_path):
+def cpu_oracle_worker(rank, world, port, out_path, kind="llama"):
     """Each gloo rank runs the oracle on its weight shard with dist.all_reduce where the reference
     all-reduces; rank 0 saves the logits for comparison with the unsharded oracle."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -48,8 +53,9 @@ def cpu_oracle_worker(rank, world, port, out_path):
     entry.load_package()
     from sglang_cpp_b200 import tp
 
-    cfg = _cfg()
-    w = O.init_weights(cfg, seed=0, std=0.05)
+    cfg = _cfg(kind)
+    ep = kind == "moe_ep"
+    w = O.init_weights(cfg, seed=0, std=0.05, router_std=1.0 if ep else None)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (7, 19)]
     batch, pt, slots = _batch(cfg, prompts)
@@ -59,8 +65,10 @@ def cpu_oracle_worker(rank, world, port, out_path):
         dist.all_reduce(t)
         return t
 
-    local = O.OracleModel(tp.local_config(cfg, world), tp.shard_weights(cfg, w, rank, world), O.store_fp32, all_reduce)
-    kv = O.KVState.create(tp.local_config(cfg, world), slots + 1)
+    lcfg = tp.local_config(cfg, world, ep)
+    local = O.OracleModel(lcfg, tp.shard_weights(cfg, w, rank, world, ep), O.store_fp32, all_reduce,
+                          expert_begin=rank * cfg.num_experts // world if ep else 0)
+    kv = O.KVState.create(lcfg, slots + 1)
     logits = local.forward(batch, kv, pt)
     if rank == 0:
         full = O.OracleModel(cfg, w, O.store_fp32)
@@ -70,7 +78,7 @@ def cpu_oracle_worker(rank, world, port, out_path):
     dist.destroy_process_group()
 
 
-def gpu_engine_worker(rank, world, port, out_path):
+def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     """Two processes, one GPU each: the engine with tp_size = 2 (fused all-reduce over peer memory)
     against the unsharded oracle, prefill then decode."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -84,9 +92,10 @@ def gpu_engine_worker(rank, world, port, out_path):
     from sglang_cpp_b200.engine import Engine, EngineConfig
     from sglang_cpp_b200.host_batch import HostBatcher
 
-    cfg = _cfg()
-    w = O.init_weights(cfg, seed=0, std=0.02)
-    eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world))
+    cfg = _cfg(kind)
+    ep = kind == "moe_ep"
+    w = O.init_weights(cfg, seed=0, std=0.02, router_std=1.0 if ep else None)
+    eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world, ep))
     eng.load_weights(w, rank, world)
     cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
     eng.load_rope_tables(cos, sin)
