@@ -63,6 +63,7 @@ struct DecodeParams {
     int* counters;      // [kMaxBatch], zero between calls
     int max_items;
     int* status;
+    L2PrefetchList pf;
 };
 
 struct ItemInfo {
@@ -103,8 +104,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
         tma_prefetch_desc(&tmap_v);
     }
 
+    // Programmatic dependent launch: what the kernel before this one (the K/V store of the same
+    // layer) writes is only q and the newest token's K/V.  seq_lens, the page table and every older
+    // K/V row were complete before that kernel could start, so the split and most K/V loads run
+    // ahead of griddepcontrol.wait; consumers wait before reading q, the producer before the first
+    // stage that holds a request's newest key.
     pdl_launch_dependents();
-    pdl_wait_prior();
 
     // ---- device-side split ----
     // All stages of all requests form one global sequence; CTA i takes the contiguous run
@@ -171,6 +176,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if (warp == kConsumerWarps) {
         // ================= producer warp =================
         const uint32_t copy_bytes = static_cast<uint32_t>(p.kpc) * Hkv * 128u;  // one half-tile box
+        const uint64_t kv_policy = l2_policy_evict_first();
+        bool waited = false;
         for (int gpos = g_begin; gpos < g_end && !failed;) {
             const ItemInfo it = locate(gpos);
             gpos += it.s_end - it.s_begin;
@@ -194,6 +201,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 const int k0 = st * SK;
                 const int valid = min(SK, it.len - k0);
                 const int ncopies = (valid + p.kpc - 1) / p.kpc;
+                if (!waited && k0 + valid >= it.len) {  // this stage holds the key written just now
+                    pdl_wait_prior();
+                    waited = true;
+                }
                 const uint32_t bar = smem_u32(&full_bar[slot]);
                 if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ncopies) * 4u * copy_bytes);
                 __syncwarp();
@@ -207,9 +218,25 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         sl = 0;
                     }
                     const uint32_t dst = stage_base + which * kHalfBytes + copy * copy_bytes;
-                    tma_load_3d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
-                                static_cast<int>(sl), 0, bar);
+                    if (p.pf.kv_evict_first)
+                        tma_load_3d_hint(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
+                                         static_cast<int>(sl), 0, bar, kv_policy);
+                    else
+                        tma_load_3d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
+                                    static_cast<int>(sl), 0, bar);
                 }
+            }
+        }
+        // All of this CTA's K/V is on its way: while the consumers drain the ring, ask for this
+        // CTA's share of the weights the next kernels read, in 8 KB pieces spread over all CTAs.
+        constexpr uint32_t kPiece = 8192;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t bytes = p.pf.bytes[i];
+            const uint32_t pieces = (bytes + kPiece - 1) / kPiece;
+            for (uint32_t c = blockIdx.x * 32 + lane; c < pieces; c += gridDim.x * 32) {
+                const uint32_t off = c * kPiece;
+                l2_prefetch_bulk(static_cast<const uint8_t*>(p.pf.ptr[i]) + off, min(kPiece, bytes - off));
             }
         }
         return;
@@ -302,6 +329,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
     };
 
+    pdl_wait_prior();  // q comes from the kernel before this one
     int npend = 0;  // cross-CTA items whose merge is decided after this CTA's last stage
     int gpos = g_begin;
     bool have = gpos < g_end;
@@ -515,7 +543,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                             const int32_t* page_table, int64_t pt_stride, const int32_t* table_idx,
                             const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
                             int page_size, float sm_scale, void* workspace, int64_t workspace_bytes,
-                            int* status, cudaStream_t stream) {
+                            int* status, cudaStream_t stream, const L2PrefetchList* prefetch) {
     const int kg = kConsumerWarps / kv_heads;
     const int grid = sm_count();
     // Workspace layout: counters | ws_ml | ws_o
@@ -553,6 +581,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
     p.ws_o = p.ws_ml + max_items * kg * q_heads * 2;
     p.max_items = static_cast<int>(max_items < (1 << 30) ? max_items : (1 << 30));
     p.status = status;
+    if (prefetch) p.pf = *prefetch;
 
     const int smem = kStages * kStageBytes + 1024;
     static bool attr_set = false;

@@ -114,6 +114,7 @@ struct SkinnyParams {
     const int32_t* group_counts;
     const int32_t* group_offsets;
     int w_rows_per_group;
+    int w_evict_first;   // B200_W_EVICT_FIRST=1: weight tiles loaded with the evict-first L2 policy (measured: no gain)
 };
 
 template <int NUM_A>
@@ -196,14 +197,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (warp == 0) {
         if (lane == 0) {
             // Weight tiles first: they do not depend on the kernel before this one.
+            const uint64_t wpol = l2_policy_evict_first();
+            auto load_w = [&](uint32_t dst, int kc, int row, uint32_t bar) {
+                if (p.w_evict_first) tma_load_2d_hint(dst, &tmap_w, kc, row, bar, wpol);
+                else tma_load_2d(dst, &tmap_w, kc, row, bar);
+            };
             const int early = min(my_kb, p.stages);
             for (int i = 0; i < early; ++i) {
                 const uint32_t bar = smem_u32(&full_bar[i]);
                 const uint32_t dst = smem_base + i * stage_bytes;
                 const int kc = (kb_begin + i) * kBlockK;
                 mbar_arrive_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
-                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
+                load_w(dst, kc, w_row0 + n0, bar);
+                if (NUM_A == 2) load_w(dst + a_bytes, kc, w_row0 + p.up_row_offset + n0, bar);
             }
             pdl_wait_prior();
             for (int i = 0; i < my_kb && !failed; ++i) {
@@ -218,9 +224,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                         break;
                     }
                     mbar_arrive_expect_tx(bar, stage_bytes);
-                    tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
-                    if (NUM_A == 2)
-                        tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
+                    load_w(dst, kc, w_row0 + n0, bar);
+                    if (NUM_A == 2) load_w(dst + a_bytes, kc, w_row0 + p.up_row_offset + n0, bar);
                 }
                 tma_load_2d(dst + NUM_A * a_bytes, tx, kc, x_row0, bar);
             }
@@ -424,6 +429,14 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t out
     return B200_OK;
 }
 
+static int w_evict_first_default() {
+    static const int v = [] {
+        const char* e = getenv("B200_W_EVICT_FIRST");
+        return (e && *e) ? atoi(e) : 0;
+    }();
+    return v;
+}
+
 static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return (v && *v) ? atoi(v) : dflt;
@@ -497,6 +510,7 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.group_counts = nullptr;
     p.group_offsets = nullptr;
     p.w_rows_per_group = 0;
+    p.w_evict_first = w_evict_first_default();
 
     auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -553,6 +567,7 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     p.group_counts = counts;
     p.group_offsets = offsets;
     p.w_rows_per_group = N;
+    p.w_evict_first = w_evict_first_default();
     auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));

@@ -17,19 +17,28 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
     return a;
 }
 
-// One CTA per row; 16-byte loads; first index on ties.
+// A cluster of kArgmaxCluster CTAs per row (one CTA for short rows), each scanning a slice with
+// 16-byte loads; the slices' winners meet in the first CTA's shared memory.  Larger value wins,
+// first index on ties, so the result does not depend on how the row is cut.
+constexpr int kArgmaxCluster = 8;
+
 __global__ void __launch_bounds__(512)
 argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logits, int vocab,
-                   int64_t ld) {
+                   int64_t ld, int ncta) {
     __shared__ float s_v[16];
     __shared__ int s_i[16];
+    __shared__ float s_cv[kArgmaxCluster];
+    __shared__ int s_ci[kArgmaxCluster];
     pdl_launch_dependents();
     pdl_wait_prior();
-    const __nv_bfloat16* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+    const int row_id = blockIdx.x / ncta, rank = blockIdx.x % ncta;
+    const __nv_bfloat16* row = logits + static_cast<int64_t>(row_id) * ld;
     MaxIdx best{-INFINITY, 0x7fffffff};
     const int nvec = vocab >> 3;
+    const int per = (nvec + ncta - 1) / ncta;
+    const int v_begin = rank * per, v_end = min(nvec, v_begin + per);
     const uint4* rv = reinterpret_cast<const uint4*>(row);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    for (int v = v_begin + threadIdx.x; v < v_end; v += blockDim.x) {
         const uint4 a = rv[v];
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
@@ -38,8 +47,9 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
             best = better(best, MaxIdx{bf16_hi(w[j]), v * 8 + 2 * j + 1});
         }
     }
-    for (int i = nvec * 8 + threadIdx.x; i < vocab; i += blockDim.x)
-        best = better(best, MaxIdx{__bfloat162float(row[i]), i});
+    if (rank == ncta - 1)
+        for (int i = nvec * 8 + threadIdx.x; i < vocab; i += blockDim.x)
+            best = better(best, MaxIdx{__bfloat162float(row[i]), i});
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -59,7 +69,25 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
             MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
             best = better(best, other);
         }
-        if (lane == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+        if (ncta == 1) {
+            if (lane == 0) out[row_id] = best.i == 0x7fffffff ? 0 : best.i;
+        } else if (lane == 0) {
+            // hand this slice's winner to the first CTA of the cluster
+            uint32_t rv_addr, ri_addr;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rv_addr) : "r"(smem_u32(&s_cv[rank])), "r"(0));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ri_addr) : "r"(smem_u32(&s_ci[rank])), "r"(0));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(rv_addr), "f"(best.v) : "memory");
+            asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(ri_addr), "r"(best.i) : "memory");
+        }
+    }
+    if (ncta > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (rank == 0 && threadIdx.x == 0) {
+            MaxIdx b0{-INFINITY, 0x7fffffff};
+            for (int r = 0; r < ncta; ++r) b0 = better(b0, MaxIdx{s_cv[r], s_ci[r]});
+            out[row_id] = b0.i == 0x7fffffff ? 0 : b0.i;
+        }
     }
 }
 
@@ -68,8 +96,9 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   cudaStream_t stream) {
     if (rows == 0) return B200_OK;
-    B200_CHECK_CUDA(launch_kernel(argmax_bf16_kernel, dim3(rows), dim3(512), 0, stream, dim3(1, 1, 1), out,
-                                  static_cast<const __nv_bfloat16*>(logits), vocab, ld));
+    const int ncta = vocab >= 32768 ? kArgmaxCluster : 1;
+    B200_CHECK_CUDA(launch_kernel(argmax_bf16_kernel, dim3(rows * ncta), dim3(512), 0, stream, dim3(ncta, 1, 1),
+                                  out, static_cast<const __nv_bfloat16*>(logits), vocab, ld, ncta));
     return B200_OK;
 }
 
