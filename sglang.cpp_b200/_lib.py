@@ -8,6 +8,7 @@ build it.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p, POINTER
 from pathlib import Path
 
@@ -134,12 +135,16 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = LIB_PATH
+    if os.environ.get("B200_LIBRARY"):
+        # another build of the same library (for example one compiled with tuning hooks)
+        path = Path(os.environ["B200_LIBRARY"])
+    if not path.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
             "(nvcc, sm_100a).  There is no fallback path."
         )
-    lib = ctypes.CDLL(str(LIB_PATH))
+    lib = ctypes.CDLL(str(path))
     for name, (restype, argtypes) in PROTOTYPES.items():
         fn = getattr(lib, name)
         fn.restype = restype

@@ -101,6 +101,18 @@ struct Tensor {
 
 using namespace b200;
 
+// Tuning builds only (-DB200_TUNE): B200_TUNE_SKIP is a bit mask of launches to leave out of the
+// step, to read each kernel family's cost inside the real launch chain.  Results are then garbage.
+#ifdef B200_TUNE
+static int tune_skip_mask() {
+    static const int v = getenv("B200_TUNE_SKIP") ? atoi(getenv("B200_TUNE_SKIP")) : 0;
+    return v;
+}
+#define B200_TUNE_SKIP(bit) ((tune_skip_mask() & (bit)) != 0)
+#else
+#define B200_TUNE_SKIP(bit) false
+#endif
+
 struct b200_comm;
 extern "C" {
 int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out);
@@ -295,6 +307,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             }
             return rc;
         }
+        if (B200_TUNE_SKIP(4)) return B200_OK;
         return launch_fused_add_rmsnorm(e->x, e->residual, w, T, hidden, m.rms_norm_eps, round_first, s);
     };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
@@ -302,13 +315,15 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     for (int l = 0; l < m.num_layers; ++l) {
         LayerWeights& L = e->layers[l];
         B200_TRY(add_norm(L.input_norm));
-        B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
-                               B200_EPILOGUE_NONE, e->status, s));
+        if (!B200_TUNE_SKIP(8))
+            B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                                   B200_EPILOGUE_NONE, e->status, s));
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
         __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
-        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
-                                          e->positions, e->out_loc, k_cache, v_cache, T, e->hq, e->hkv,
-                                          d, m.max_position, e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        if (!B200_TUNE_SKIP(2))
+            B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
+                                              e->positions, e->out_loc, k_cache, v_cache, T, e->hq, e->hkv,
+                                              d, m.max_position, e->num_slots, m.rms_norm_eps, 0, e->status, s));
         const bool timed = e->profile_attention && !e->capturing;
         if (timed) {
             while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
@@ -318,7 +333,8 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             }
             B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l], s));
         }
-        if (phase == B200_PHASE_DECODE) {
+        if (phase == B200_PHASE_DECODE && B200_TUNE_SKIP(1)) {
+        } else if (phase == B200_PHASE_DECODE) {
             // The weights of the kernels between this attention launch and the next one (o, the MLP,
             // the next layer's qkv) are brought into L2 while the attention pipeline drains.
             L2PrefetchList pf;
@@ -355,8 +371,9 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
             e->prof_pairs_recorded = l + 1;
         }
-        B200_TRY(launch_linear(proj_out(), e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
-                               B200_EPILOGUE_NONE, e->status, s));
+        if (!B200_TUNE_SKIP(16))
+            B200_TRY(launch_linear(proj_out(), e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
+                                   B200_EPILOGUE_NONE, e->status, s));
         B200_TRY(add_norm(L.post_norm));
         if (m.num_experts > 0) {
             // MoEMLP::forward (src/models/utils.cc:82-91): router logits, then the expert layer.
@@ -368,10 +385,12 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                         e->experts_local, e->moe_ws, e->status, s));
             continue;
         }
-        B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
-                               e->status, s));
-        B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
-                               B200_EPILOGUE_NONE, e->status, s));
+        if (!B200_TUNE_SKIP(32))
+            B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
+                                   e->status, s));
+        if (!B200_TUNE_SKIP(64))
+            B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
+                                   B200_EPILOGUE_NONE, e->status, s));
     }
     B200_TRY(add_norm(e->final_norm));
     const __nv_bfloat16* head_in = e->x;

@@ -24,6 +24,7 @@
 #include "kernels.h"
 #include "tensormap.cuh"
 #include "tcgen05.cuh"
+#include <cstdio>
 
 namespace b200 {
 namespace {
@@ -75,9 +76,12 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float gated_act(int epilogue, float g) {
-    if (epilogue == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
-    if (epilogue == B200_EPILOGUE_GEGLU_ERF) return gelu_erf_f(g);
+// The activation is a template parameter: a run-time switch makes the compiler keep all three
+// bodies (erff and tanhf are long) in the epilogue of every gated GEMM.
+template <int EPI>
+__device__ __forceinline__ float gated_act(float g) {
+    if (EPI == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
+    if (EPI == B200_EPILOGUE_GEGLU_ERF) return gelu_erf_f(g);
     return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
 }
 __device__ __forceinline__ float gelu_tanh_f(float x) {
@@ -117,13 +121,14 @@ struct SkinnyParams {
     int w_evict_first;   // B200_W_EVICT_FIRST=1: weight tiles loaded with the evict-first L2 policy (measured: no gain)
 };
 
-template <int NUM_A>
+template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_x,
                    const __grid_constant__ CUtensorMap tmap_x64,
                    const __grid_constant__ CUtensorMap tmap_x128,
                    const __grid_constant__ CUtensorMap tmap_x256, const SkinnyParams p) {
+    constexpr int NUM_A = EPI == B200_EPILOGUE_NONE ? 1 : 2;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -327,7 +332,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                 if (NUM_A == 2) {
                                     const float gv = round_bf16(__uint_as_float(g[j]));
                                     const float uv = round_bf16(__uint_as_float(u[j]));
-                                    v = gated_act(p.epilogue, gv) * uv;
+                                    v = gated_act<EPI>(gv) * uv;
                                 } else {
                                     v = __uint_as_float(g[j]) + bias;
                                 }
@@ -350,22 +355,35 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         if (split == 1) continue;
 
-        cluster_sync_all();
         B200_TRACE(5);
+        cluster_sync_all();
+        B200_TRACE(6);
         if (is_epi) {
-            const int f4_per_col = F / 4;
+            // F / 4 is a power of two (split is 2, 4 or 8): shifts instead of divisions.
+            const int f4_shift = 31 - __clz(F / 4);
             const int te = (warp - 2) * 32 + lane;  // 0..127
             const float* rb = xbuf + buf_off / 4u;
-            for (int i = te; i < cpr * f4_per_col; i += 128) {
-                const int col = i / f4_per_col;
-                const int f = (i - col * f4_per_col) * 4;   // owned-feature index
+            for (int i = te; i < (cpr << f4_shift); i += 128) {
+                const int col = i >> f4_shift;
+                const int f = (i & ((1 << f4_shift) - 1)) * 4;   // owned-feature index
+                // All partials first (independent loads), then the sum in rank order.
+                float4 pg[8], pu[8];
+#pragma unroll
+                for (uint32_t rr = 0; rr < 8; ++rr) {
+                    if (rr < split) {
+                        pg[rr] = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + col) * F + f));
+                        if (NUM_A == 2)
+                            pu[rr] = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + cpr + col) * F + f));
+                    }
+                }
                 float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), su = sg;
-                for (uint32_t rr = 0; rr < split; ++rr) {
-                    const float4 a = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + col) * F + f));
-                    sg.x += a.x; sg.y += a.y; sg.z += a.z; sg.w += a.w;
-                    if (NUM_A == 2) {
-                        const float4 b2 = *reinterpret_cast<const float4*>(rb + ((rr * NUM_A * cpr + cpr + col) * F + f));
-                        su.x += b2.x; su.y += b2.y; su.z += b2.z; su.w += b2.w;
+#pragma unroll
+                for (uint32_t rr = 0; rr < 8; ++rr) {
+                    if (rr < split) {
+                        sg.x += pg[rr].x; sg.y += pg[rr].y; sg.z += pg[rr].z; sg.w += pg[rr].w;
+                        if (NUM_A == 2) {
+                            su.x += pu[rr].x; su.y += pu[rr].y; su.z += pu[rr].z; su.w += pu[rr].w;
+                        }
                     }
                 }
                 const int m = r * cpr + col;
@@ -377,7 +395,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     for (int e = 0; e < 4; ++e) {
                         if (NUM_A == 2) {
                             const float gv = round_bf16(v[e]), uv = round_bf16(uu[e]);
-                            v[e] = gated_act(p.epilogue, gv) * uv;
+                            v[e] = gated_act<EPI>(gv) * uv;
                         } else if (p.bias) {
                             v[e] += __bfloat162float(p.bias[n + e]);
                         }
@@ -388,13 +406,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
         }
     }
-    B200_TRACE(6);
-    B200_TRACE(6);
+    B200_TRACE(7);
 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
-    B200_TRACE(7);
+}
+
+using SkinnyKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, SkinnyParams);
+SkinnyKernel skinny_kernel_for(int epilogue) {
+    switch (epilogue) {
+        case B200_EPILOGUE_SWIGLU: return skinny_gemm_kernel<B200_EPILOGUE_SWIGLU>;
+        case B200_EPILOGUE_GEGLU: return skinny_gemm_kernel<B200_EPILOGUE_GEGLU>;
+        case B200_EPILOGUE_GEGLU_ERF: return skinny_gemm_kernel<B200_EPILOGUE_GEGLU_ERF>;
+        default: return skinny_gemm_kernel<B200_EPILOGUE_NONE>;
+    }
 }
 
 }  // namespace
@@ -454,7 +480,14 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
 
     // K split: up to one CTA per SM in total, at most 8 ranks (portable cluster size).
     int split = 1;
-    const int forced = env_int("B200_GEMM_SPLIT", 0);
+    int forced = env_int("B200_GEMM_SPLIT", 0);
+#ifdef B200_TUNE
+    {   // tuning builds: B200_SPLIT_N<N>=<split> overrides the split of GEMMs with that many W rows
+        char name[48];
+        snprintf(name, sizeof(name), "B200_SPLIT_N%d_K%d", N, K);
+        forced = env_int(name, forced);
+    }
+#endif
     if (forced > 0) {
         split = forced;
     } else {
@@ -512,7 +545,7 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.w_rows_per_group = 0;
     p.w_evict_first = w_evict_first_default();
 
-    auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
+    auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, split, 1), dim3(kThreads), smem_bytes, stream,
@@ -568,7 +601,7 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     p.group_offsets = offsets;
     p.w_rows_per_group = N;
     p.w_evict_first = w_evict_first_default();
-    auto kernel = gated ? skinny_gemm_kernel<2> : skinny_gemm_kernel<1>;
+    auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, slabs, num_groups), dim3(kThreads), smem_bytes, stream,

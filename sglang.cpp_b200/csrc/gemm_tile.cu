@@ -41,9 +41,10 @@ struct TileParams {
     int* status;
 };
 
-__device__ __forceinline__ float gated_act_tile(int epilogue, float g) {
-    if (epilogue == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
-    if (epilogue == B200_EPILOGUE_GEGLU_ERF) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+template <int EPI>
+__device__ __forceinline__ float gated_act_tile(float g) {
+    if (EPI == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
+    if (EPI == B200_EPILOGUE_GEGLU_ERF) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
     return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
 }
 
@@ -57,10 +58,11 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
     mt = band * kBand + (r - ntile * bm);
 }
 
-template <bool GATED>
+template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const TileParams p) {
+    constexpr bool GATED = EPI != B200_EPILOGUE_NONE;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages];
     __shared__ __align__(8) uint64_t empty_bar[kStages];
@@ -198,7 +200,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         if (GATED) {
                             const float gv = round_bf16(__uint_as_float(g[j]));
                             const float uv = round_bf16(__uint_as_float(u[j]));
-                            v[j] = gated_act_tile(p.epilogue, gv) * uv;
+                            v[j] = gated_act_tile<EPI>(gv) * uv;
                         } else {
                             v[j] = __uint_as_float(g[j]);
                         }
@@ -261,7 +263,10 @@ int launch_tile_gemm(void* y, const void* x, const void* w, const void* bias, in
     const uint32_t smem_bytes = kStages * kStageBytes + 1024;
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    auto kernel = gated ? tile_gemm_kernel<true> : tile_gemm_kernel<false>;
+    void (*kernel)(CUtensorMap, CUtensorMap, TileParams) = tile_gemm_kernel<B200_EPILOGUE_NONE>;
+    if (epilogue == B200_EPILOGUE_SWIGLU) kernel = tile_gemm_kernel<B200_EPILOGUE_SWIGLU>;
+    if (epilogue == B200_EPILOGUE_GEGLU) kernel = tile_gemm_kernel<B200_EPILOGUE_GEGLU>;
+    if (epilogue == B200_EPILOGUE_GEGLU_ERF) kernel = tile_gemm_kernel<B200_EPILOGUE_GEGLU_ERF>;
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, dim3(1, 1, 1),
