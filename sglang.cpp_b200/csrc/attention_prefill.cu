@@ -303,6 +303,16 @@ int launch_attention_prefill(void* out, const void* q, int64_t q_st, int64_t q_s
                              int kv_heads, int page_size, float sm_scale, int* status,
                              cudaStream_t stream) {
     if (batch == 0 || max_extend_len == 0) return B200_OK;
+    // The tensor-core kernel takes every call with 16-byte aligned query rows; the mma.sync kernel
+    // below stays for the rest (and for comparison: B200_PREFILL_ATTN=mma).
+    static const bool force_mma = [] {
+        const char* v = getenv("B200_PREFILL_ATTN");
+        return v && v[0] == 'm';
+    }();
+    if (!force_mma && attention_prefill_tc_supported(q, q_st, q_sh, out))
+        return launch_attention_prefill_tc(out, q, q_st, q_sh, k_cache, v_cache, num_slots, page_table, pt_stride,
+                                           table_idx, seq_lens, qo_indptr, batch, max_extend_len, q_heads,
+                                           kv_heads, page_size, sm_scale, status, stream);
     PrefillParams p;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.q = static_cast<const __nv_bfloat16*>(q);

@@ -42,7 +42,7 @@ class PagedSetup:
     write_page_table lay them out (src/scheduler/prefill.cc:144-206)."""
 
     def __init__(self, seq_lens, page_size: int, kv_heads: int, head_dim: int = 128, seed: int = 0,
-                 extra_pages: int = 3, shared_prefix: int = 0, std: float = 1.0):
+                 extra_pages: int = 3, shared_prefix: int = 0, std: float = 1.0, shuffle_pages: bool = True):
         gen = torch.Generator().manual_seed(seed)
         rng = np.random.default_rng(seed)
         B = len(seq_lens)
@@ -55,7 +55,9 @@ class PagedSetup:
         cols = (math.ceil(max_len / page_size) * page_size + 31) // 32 * 32
         self.page_table = np.zeros((B + 2, cols), dtype=np.int32)
         self.table_idx = rng.permutation(B + 2)[:B].astype(np.int32)
-        order = rng.permutation(total_pages)
+        # shuffle_pages=False: each request's pages are consecutive slots, as they are when a
+        # prompt's pages are allocated in one go
+        order = rng.permutation(total_pages) if shuffle_pages else np.arange(total_pages)
         cur = 0
         shared_pages = None
         for b in range(B):
@@ -108,10 +110,10 @@ def decode_attention_case(L, seq_lens, page_size, q_heads, kv_heads, seed=0, poi
     return got, want, attn
 
 
-def prefill_attention_case(L, seq_lens, extend_lens, page_size, q_heads, kv_heads, seed=0):
+def prefill_attention_case(L, seq_lens, extend_lens, page_size, q_heads, kv_heads, seed=0, shuffle_pages=True):
     dev = "cuda"
     d = 128
-    ps = PagedSetup(seq_lens, page_size, kv_heads, d, seed)
+    ps = PagedSetup(seq_lens, page_size, kv_heads, d, seed, shuffle_pages=shuffle_pages)
     gen = torch.Generator().manual_seed(seed + 1)
     B = len(seq_lens)
     qo = np.zeros(B + 1, dtype=np.int32)

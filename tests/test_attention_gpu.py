@@ -70,10 +70,21 @@ def test_decode_empty_batch_and_bad_args(L, pkg):
     ([150], [150], 16, 32, 4),                               # group 8
     ([190, 65], [64, 65], 16, 4, 1),                         # one KV head per rank
     ([130], [130], 4, 8, 2),
+    ([2048, 1500], [2048, 1500], 16, 16, 8),                 # prompts of the decode benchmark's size
 ])
 def test_prefill_matches_oracle(L, seq_lens, extend_lens, page_size, hq, hkv):
     got, want = prefill_attention_case(L, seq_lens, extend_lens, page_size, hq, hkv, seed=sum(seq_lens))
     assert_close_bf16(got, want, ATOL, RTOL, "prefill attention")
+    assert L.read_device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("seq_lens,extend_lens,page_size", [
+    ([700, 300], [700, 300], 16), ([513], [200], 4), ([260, 130], [260, 2], 1)])
+def test_prefill_with_consecutive_pages(L, seq_lens, extend_lens, page_size):
+    """Pages in consecutive slots take the whole-tile copies; the ragged last tile and the other
+    requests still go page by page."""
+    got, want = prefill_attention_case(L, seq_lens, extend_lens, page_size, 16, 8, seed=5, shuffle_pages=False)
+    assert_close_bf16(got, want, ATOL, RTOL, "prefill attention, consecutive pages")
     assert L.read_device_status() == (0, 0)
 
 
