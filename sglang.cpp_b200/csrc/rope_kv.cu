@@ -85,16 +85,28 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
                          const int32_t* __restrict__ out_loc, __nv_bfloat16* __restrict__ k_cache,
                          __nv_bfloat16* __restrict__ v_cache, int tokens, int q_heads,
                          int kv_heads, int max_pos, int64_t num_slots, float eps, int write_k_back,
-                         int* status) {
-    constexpr int EPL = D / 64;  // elements per lane per half
+                         int* status, int rows_per_warp) {
+    // Eight lanes per row, 16-byte vectors (head_dim 128): lane `sub` of a row holds elements
+    // [sub*EPL, sub*EPL + EPL) of each half, so the NeoX partner of an element is in the same lane.
+    constexpr int LPR = 8;                  // lanes per row
+    constexpr int RPP = 32 / LPR;           // rows a warp handles per pass
+    constexpr int EPL = D / (2 * LPR);      // elements per lane per half
     using Vec = BfVec<EPL>;
     const int lane = threadIdx.x & 31;
+    const int sub = lane % LPR;
+    const unsigned group_mask = ((1u << LPR) - 1u) << (lane / LPR * LPR);
     const int rows_per_token = q_heads + 2 * kv_heads;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t total_rows = static_cast<int64_t>(tokens) * rows_per_token;
+    const int64_t row0 =
+        (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * rows_per_warp * RPP +
+        lane / LPR;
 
     pdl_launch_dependents();
     pdl_wait_prior();
-    if (row >= static_cast<int64_t>(tokens) * rows_per_token) return;
+    if (row0 >= total_rows) return;
+
+    // One row: a, b are its two halves, already loaded.
+    auto process = [&](int64_t row, Vec a, Vec b) {
     const int64_t t = row / rows_per_token;
     const int r = static_cast<int>(row - t * rows_per_token);
     __nv_bfloat16* src = qkv + (t * rows_per_token + r) * D;
@@ -107,19 +119,16 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
     if (!is_q) {
         slot = out_loc[t];
         if (slot < 0 || slot >= num_slots) {
-            if (lane == 0) atomicExch(&status[kStatusBadIndex], static_cast<int>(slot) + 1);
+            if (sub == 0) atomicExch(&status[kStatusBadIndex], static_cast<int>(slot) + 1);
             slot = -1;
         }
     }
 
-    Vec a = *reinterpret_cast<const Vec*>(src + lane * EPL);
-    Vec b = *reinterpret_cast<const Vec*>(src + D / 2 + lane * EPL);
-
     if (!is_q && !is_k) {  // v row: plain copy into the pool
         if (slot >= 0) {
             __nv_bfloat16* dst = v_cache + (slot * kv_heads + kvh) * D;
-            *reinterpret_cast<Vec*>(dst + lane * EPL) = a;
-            *reinterpret_cast<Vec*>(dst + D / 2 + lane * EPL) = b;
+            *reinterpret_cast<Vec*>(dst + sub * EPL) = a;
+            *reinterpret_cast<Vec*>(dst + D / 2 + sub * EPL) = b;
         }
         return;
     }
@@ -136,10 +145,11 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
         float ss = 0.f;
 #pragma unroll
         for (int e = 0; e < EPL; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
-        ss = warp_sum(ss);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
         const float scale = rsqrtf(ss / static_cast<float>(D) + eps);
-        Vec wa = *reinterpret_cast<const Vec*>(w + lane * EPL);
-        Vec wb = *reinterpret_cast<const Vec*>(w + D / 2 + lane * EPL);
+        Vec wa = *reinterpret_cast<const Vec*>(w + sub * EPL);
+        Vec wb = *reinterpret_cast<const Vec*>(w + D / 2 + sub * EPL);
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
             // bf16 rounding here is where the unfused norm kernel stores its result.
@@ -150,11 +160,11 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
 
     int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
-        if (lane == 0) atomicExch(&status[kStatusBadIndex], pos + 1);
+        if (sub == 0) atomicExch(&status[kStatusBadIndex], pos + 1);
         pos = min(max(pos, 0), max_pos - 1);
     }
-    const float* c = cos_t + static_cast<int64_t>(pos) * (D / 2) + lane * EPL;
-    const float* s = sin_t + static_cast<int64_t>(pos) * (D / 2) + lane * EPL;
+    const float* c = cos_t + static_cast<int64_t>(pos) * (D / 2) + sub * EPL;
+    const float* s = sin_t + static_cast<int64_t>(pos) * (D / 2) + sub * EPL;
     Vec oa, ob;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
@@ -164,13 +174,30 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
     }
 
     if (is_q || write_k_back) {
-        *reinterpret_cast<Vec*>(src + lane * EPL) = oa;
-        *reinterpret_cast<Vec*>(src + D / 2 + lane * EPL) = ob;
+        *reinterpret_cast<Vec*>(src + sub * EPL) = oa;
+        *reinterpret_cast<Vec*>(src + D / 2 + sub * EPL) = ob;
     }
     if (is_k && slot >= 0) {
         __nv_bfloat16* dst = k_cache + (slot * kv_heads + kvh) * D;
-        *reinterpret_cast<Vec*>(dst + lane * EPL) = oa;
-        *reinterpret_cast<Vec*>(dst + D / 2 + lane * EPL) = ob;
+        *reinterpret_cast<Vec*>(dst + sub * EPL) = oa;
+        *reinterpret_cast<Vec*>(dst + D / 2 + sub * EPL) = ob;
+    }
+    };
+
+    // Rows of this warp, the next row's loads in flight while the current one is processed
+    // (rows are adjacent in the qkv buffer: row * D elements from its start).
+    const int64_t row_end = min(row0 + static_cast<int64_t>(rows_per_warp) * RPP, total_rows);
+    Vec a = *reinterpret_cast<const Vec*>(qkv + row0 * D + sub * EPL);
+    Vec b = *reinterpret_cast<const Vec*>(qkv + row0 * D + D / 2 + sub * EPL);
+    for (int64_t row = row0; row < row_end; row += RPP) {
+        Vec an = a, bn = b;
+        if (row + RPP < row_end) {
+            an = *reinterpret_cast<const Vec*>(qkv + (row + RPP) * D + sub * EPL);
+            bn = *reinterpret_cast<const Vec*>(qkv + (row + RPP) * D + D / 2 + sub * EPL);
+        }
+        process(row, a, b);
+        a = an;
+        b = bn;
     }
 }
 
@@ -184,14 +211,18 @@ int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weig
                              int* status, cudaStream_t stream) {
     const int64_t rows = static_cast<int64_t>(tokens) * (q_heads + 2 * kv_heads);
     if (rows == 0) return B200_OK;
-    const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
+    // Few rows (decode): one row per warp for the most parallelism; many rows (prefill): four per
+    // warp with the next row's loads in flight.
+    const int rows_per_warp = rows >= 32768 ? 4 : 1;   // passes of 4 rows each
+    const int64_t rows_per_block = 4 * 4 * rows_per_warp;
+    const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
 #define B200_LAUNCH_QRS(D)                                                                       \
     B200_CHECK_CUDA(launch_kernel(                                                               \
         qknorm_rope_store_kernel<D>, dim3(blocks), dim3(128), 0, stream, dim3(1, 1, 1),          \
         static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_weight),           \
         static_cast<const __nv_bfloat16*>(k_weight), cos_table, sin_table, positions, out_loc,   \
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), tokens,      \
-        q_heads, kv_heads, max_pos, num_slots, eps, write_k_back, status))
+        q_heads, kv_heads, max_pos, num_slots, eps, write_k_back, status, rows_per_warp))
     switch (head_dim) {
         case 64: B200_LAUNCH_QRS(64); break;
         case 128: B200_LAUNCH_QRS(128); break;

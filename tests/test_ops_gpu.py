@@ -107,13 +107,14 @@ def test_store_kv(L, tokens, hkv, d):
     assert float(cache.k_cache(0).abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("tokens,hq,hkv,qk_norm", [(64, 16, 8, True), (128, 32, 8, False), (7, 32, 4, True), (1, 4, 1, True)])
+@pytest.mark.parametrize("tokens,hq,hkv,qk_norm", [(64, 16, 8, True), (128, 32, 8, False), (7, 32, 4, True), (1, 4, 1, True),
+                                                  (1401, 16, 8, True)])   # a prefill batch: several rows per warp
 def test_qknorm_rope_store_matches_unfused_sequence(L, tokens, hq, hkv, qk_norm):
     d = 128
     gen = torch.Generator().manual_seed(tokens + hq * 3)
     qkv = randn_bf16(gen, tokens, (hq + 2 * hkv) * d)
     pos = torch.randint(0, 2048, (tokens,), generator=gen, dtype=torch.int32)
-    cache = L.MHAKVCache(hkv, 1, d, 64, 16)
+    cache = L.MHAKVCache(hkv, 1, d, max(64, tokens // 16 + 2), 16)
     loc = torch.randperm(cache.total_slots, generator=gen)[:tokens].to(torch.int32)
     rot = L.RotaryEmbedding(d, d, 2048, 1e6)
     qn = kn = None
