@@ -72,6 +72,7 @@ def test_gate_up_swiglu_epilogue(L, pkg, M, I, K):
     (2048, 4096, 1024),   # one full band, Qwen3-0.6B qkv
     (4500, 1024, 3072),   # more than two bands, down_proj
     (8192, 512, 128),     # more tiles per CTA than accumulators
+    (8192, 4096, 1024),   # a full prefill batch of Qwen3-0.6B qkv: 1.7 tiles per CTA per band
 ])
 def test_linear_prefill_tiles_match_oracle(L, M, N, K):
     """Batches of more than 256 rows take the persistent 128 x 256 tile kernel."""
