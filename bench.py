@@ -345,14 +345,18 @@ def run_gpu_tp(args):
     from sglang_cpp_b200.engine import Engine, EngineConfig
     from sglang_cpp_b200.host_batch import HostBatcher
 
-    cfg = O.llama3_8b()
-    B, PROMPT = 128, 1024
+    moe = args.workload == "c5"
+    cfg = O.qwen3_30b_a3b() if moe else O.llama3_8b()
+    B, PROMPT = (256, 512) if moe else (128, 1024)
     K, W = args.steps, args.warmup
     total_new = (K + W) + 24
     rng = np.random.default_rng(3)
     prompts = [rng.integers(0, cfg.vocab_size, size=PROMPT).astype(np.int32) for _ in range(B)]
     num_pages = B * math.ceil((PROMPT + total_new + 1) / PAGE_SIZE) + 8
-    engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, B, PROMPT + total_new + 1, MAX_EXTEND_TOKENS, rank, world))
+    # MoE under more than one GPU: whole experts per rank (expert parallelism), attention heads split,
+    # a KV head replicated where there are more ranks than KV heads
+    engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, B, PROMPT + total_new + 1, MAX_EXTEND_TOKENS, rank, world,
+                                      expert_parallel=moe and world > 1))
     engine.fill_random(seed=0)
     if world > 1:
         engine.connect_tp()
@@ -422,18 +426,28 @@ def run_gpu_tp(args):
     engine.set_profiling(False)
     peak, peak_kind = measured_peaks()
     d, L = cfg.head_dim, cfg.num_layers
-    per_layer = ((cfg.num_qo_heads + 2 * cfg.num_kv_heads) * d * cfg.hidden_size + cfg.hidden_size * cfg.num_qo_heads * d
-                 + 3 * cfg.intermediate_size * cfg.hidden_size)
+    attn_w = (cfg.num_qo_heads + 2 * cfg.num_kv_heads) * d * cfg.hidden_size + cfg.hidden_size * cfg.num_qo_heads * d
+    if moe:   # every expert is hit at batch 256 with top-8 routing: all expert weights are read each step
+        mlp_w = cfg.num_experts * 3 * cfg.moe_intermediate_size * cfg.hidden_size + cfg.num_experts * cfg.hidden_size
+    else:
+        mlp_w = 3 * cfg.intermediate_size * cfg.hidden_size
+    per_layer = attn_w + mlp_w
     mean_ctx = ctx0 + (K - 1) / 2
     kv_tok = 2 * cfg.num_kv_heads * d * L * 2
+    kv_share = max(world, 1) if cfg.num_kv_heads >= world else cfg.num_kv_heads   # replicated KV heads do not shrink
     # per GPU: sharded layers and KV, replicated lm_head
-    bytes_gpu = 2 * L * per_layer / world + 2 * cfg.vocab_size * cfg.hidden_size + B * mean_ctx * kv_tok / world
+    bytes_gpu = 2 * L * per_layer / world + 2 * cfg.vocab_size * cfg.hidden_size + B * mean_ctx * kv_tok / kv_share
     line = {
-        "metric": "decode tokens/s at bs=128 (Llama-3-8B, TP over all GPUs)", "value": round(B * K / (dev_ms * 1e-3), 1),
+        "metric": ("decode tokens/s at bs=256 (Qwen3-30B-A3B, EP + attention TP over all GPUs)" if moe else
+                   "decode tokens/s at bs=128 (Llama-3-8B, TP over all GPUs)"),
+        "value": round(B * K / (dev_ms * 1e-3), 1),
         "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy",
-                   "parallelism": f"tp{world}", "mean_context": mean_ctx, "ranks_in_lockstep": lockstep},
+        "config": {"workload": ("c5: Qwen3-30B-A3B decode, batch 256, prompts of 512 random tokens, page size 16, greedy"
+                                if moe else
+                                "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy"),
+                   "parallelism": (f"ep{world}+tp{world}" if moe else f"tp{world}"), "mean_context": mean_ctx,
+                   "ranks_in_lockstep": lockstep},
         "step_roofline": {"algorithmic_bytes_per_step_per_gpu": int(bytes_gpu),
                           "frac_of_measured_hbm": round(bytes_gpu / (dev_ms / K * 1e-3) / 1e9 / peak, 4)},
         "prefill": {"tokens": B * PROMPT, "seconds": round(prefill_s, 3)},
@@ -534,9 +548,10 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"],
                     help="c2 (default, the headline metric): Qwen3-0.6B decode, replicas when N > 1; "
-                         "c4: Llama-3-8B decode, tensor parallel over the N ranks")
+                         "c4: Llama-3-8B decode, tensor parallel over the N ranks; "
+                         "c5: Qwen3-30B-A3B decode, experts and attention heads split over the N ranks")
     ap.add_argument("--context", type=int, default=0,
                     help="c2 only: give every prompt this length instead of U[512,2048]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -552,7 +567,7 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "c4":
+    elif args.workload in ("c4", "c5"):
         run_gpu_tp(args)
     else:
         run_gpu(args)
