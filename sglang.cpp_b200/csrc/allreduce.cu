@@ -32,6 +32,8 @@ struct CommDevice {
     const __nv_bfloat16* peer_buf[2][kMaxRanks];  // [parity][rank] -> that rank's exchange buffer
     uint32_t* peer_flags[kMaxRanks];              // [rank] -> that rank's flag table [blocks][ranks]
     uint32_t* self_counter;                       // [blocks] calls this CTA slot has completed
+    const __nv_bfloat16* peer_gather[kMaxRanks];  // [rank] -> that rank's buffer of reduced rows (two-shot)
+    uint32_t* peer_ready[kMaxRanks];              // [rank] -> that rank's "row reduced" flags [blocks]
     int rank, world;
 };
 
@@ -150,6 +152,152 @@ allreduce_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat
     }
 }
 
+
+// Two-shot variant for larger groups: row `row` is reduced by rank row % world alone, which reads
+// that row of every rank's partial (1/world of what the one-shot kernel reads), writes the bf16
+// sum into its gather buffer and raises a per-row flag on every peer; the other ranks wait for
+// that flag and fetch the finished row.  Every rank then runs the same add + norm on the same
+// bits, so the replicated residual stays replicated.  One CTA per row, grid = rows on every rank.
+//   flag A (peer_flags of the owner, slot = row, one word per source rank): "my partial is written";
+//   flag B (peer_ready of every rank, one word per row): "the owner's sum of this row is written".
+// The gather buffer needs no parity: a rank can only reach this call's write of a row after every
+// peer announced this call's partial, which each does after finishing all reads of the call before.
+template <int MODE, bool ROUND_FIRST>
+__global__ void __launch_bounds__(256)
+allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat16* residual,
+                         const __nv_bfloat16* __restrict__ weight, int rows, int hidden, float eps, int* status) {
+    __shared__ float red[32];
+    __shared__ int s_ok;
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int row = blockIdx.x;          // also the flag slot
+    const int owner = row % c.world;
+    const uint32_t call = c.self_counter[row] + 1;
+    const int nvec = hidden >> 3;
+    const int64_t base = static_cast<int64_t>(row) * nvec;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    // announce this rank's partial to the row's owner (see comm_barrier for why a relaxed store is enough)
+    if (threadIdx.x == 0)
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(c.peer_flags[owner] + row * kMaxRanks + c.rank),
+                     "r"(call)
+                     : "memory");
+    uint32_t y[kArVecPerThread][4];   // the bf16 sum of this thread's vectors
+    if (c.rank == owner) {
+        if (threadIdx.x < c.world) {
+            const volatile uint32_t* f = c.peer_flags[c.rank] + row * kMaxRanks + threadIdx.x;
+            const uint64_t t0 = global_timer_ns();
+            uint32_t spins = 0;
+            while (static_cast<int32_t>(*f - call) < 0) {
+                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+                    atomicExch(&status[kStatusTimeout], 402);
+                    s_ok = 0;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kArVecPerThread; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            if (v >= nvec) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < c.world; ++r) {  // rank order
+                const uint4 a = __ldcv(reinterpret_cast<const uint4*>(c.peer_buf[parity][r]) + base + v);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += bf16_lo(aw[j]);
+                    acc[2 * j + 1] += bf16_hi(aw[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[i][j] = pack_bf16(acc[2 * j], acc[2 * j + 1]);
+            reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(c.peer_gather[c.rank]))[base + v] =
+                make_uint4(y[i][0], y[i][1], y[i][2], y[i][3]);
+        }
+        // the row must be visible to the other GPUs before the flag that announces it
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < c.world && threadIdx.x != c.rank)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(c.peer_ready[threadIdx.x] + row), "r"(call)
+                         : "memory");
+    } else {
+        if (threadIdx.x == 0) {
+            const uint32_t* f = c.peer_ready[c.rank] + row;
+            const uint64_t t0 = global_timer_ns();
+            uint32_t spins = 0;
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (static_cast<int32_t>(v - call) >= 0) break;
+                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+                    atomicExch(&status[kStatusTimeout], 403);
+                    s_ok = 0;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kArVecPerThread; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            if (v >= nvec) continue;
+            const uint4 a = __ldcv(reinterpret_cast<const uint4*>(c.peer_gather[owner]) + base + v);
+            y[i][0] = a.x; y[i][1] = a.y; y[i][2] = a.z; y[i][3] = a.w;
+        }
+    }
+    if (threadIdx.x == 0) c.self_counter[row] = call;
+
+    // every rank: the same add + norm on the same sum
+    float vals[kArVecPerThread][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kArVecPerThread; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v >= nvec) continue;
+        if (MODE == 0) {
+            reinterpret_cast<uint4*>(out)[base + v] = make_uint4(y[i][0], y[i][1], y[i][2], y[i][3]);
+        } else {
+            const uint4 rr = reinterpret_cast<const uint4*>(residual)[base + v];
+            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+            uint32_t packed[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = bf16_lo(y[i][j]) + bf16_lo(rw[j]);
+                const float hi = bf16_hi(y[i][j]) + bf16_hi(rw[j]);
+                packed[j] = pack_bf16(lo, hi);
+                vals[i][2 * j] = ROUND_FIRST ? bf16_lo(packed[j]) : lo;
+                vals[i][2 * j + 1] = ROUND_FIRST ? bf16_hi(packed[j]) : hi;
+            }
+            reinterpret_cast<uint4*>(residual)[base + v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+        }
+    }
+    if (MODE == 0) return;
+    ss = warp_sum(ss);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    tot = warp_sum(tot);
+    const float scale = rsqrtf(tot / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int i = 0; i < kArVecPerThread; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v >= nvec) continue;
+        const uint4 w4 = reinterpret_cast<const uint4*>(weight)[v];
+        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            o[j] = pack_bf16(vals[i][2 * j] * scale * bf16_lo(ww[j]), vals[i][2 * j + 1] * scale * bf16_hi(ww[j]));
+        reinterpret_cast<uint4*>(out)[base + v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -163,7 +311,8 @@ struct b200_comm {
     void* peer_base[kMaxRanks] = {};  // mapped bases (own entry = local_base)
     bool connected = false;
     CommDevice dev = {};
-    int64_t flags_bytes = 0, counters_bytes = 0;
+    int64_t flags_bytes = 0, counters_bytes = 0, ready_bytes = 0;
+    int two_shot_min_world = 4;   // B200_AR_TWO_SHOT_MIN_WORLD: groups of at least this size use the two-shot kernel
 };
 
 namespace {
@@ -184,7 +333,10 @@ int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out)
     c->buffer_bytes = align_up(buffer_bytes, 256);
     c->flags_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * kMaxRanks * 4, 256);
     c->counters_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
-    const int64_t total = c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
+    c->ready_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
+    if (const char* v = getenv("B200_AR_TWO_SHOT_MIN_WORLD")) c->two_shot_min_world = atoi(v);
+    // [flags | counters | buffer 0 | buffer 1 | ready flags | gather buffer]
+    const int64_t total = c->flags_bytes + c->counters_bytes + 3 * c->buffer_bytes + c->ready_bytes;
     if (cudaMalloc(&c->local_base, static_cast<size_t>(total)) != cudaSuccess ||
         cudaMemset(c->local_base, 0, static_cast<size_t>(total)) != cudaSuccess ||
         cudaDeviceSynchronize() != cudaSuccess) {
@@ -224,6 +376,9 @@ int b200_comm_connect(b200_comm* c, const void* all_handles) {
         for (int p = 0; p < 2; ++p)
             c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
                                                                           p * c->buffer_bytes);
+        char* tail = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
+        c->dev.peer_ready[r] = reinterpret_cast<uint32_t*>(tail);
+        c->dev.peer_gather[r] = reinterpret_cast<const __nv_bfloat16*>(tail + c->ready_bytes);
     }
     c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
     c->dev.rank = c->rank;
@@ -266,6 +421,14 @@ int launch_allreduce(b200_comm* c, int parity, int mode, void* out, void* residu
         return B200_ERR_INVALID_ARGUMENT;
     }
     if (rows == 0) return B200_OK;
+    if (c->world >= c->two_shot_min_world && rows <= kMaxCommBlocks) {
+        auto k2 = mode == 0 ? allreduce_twoshot_kernel<0, false>
+                            : (round_first ? allreduce_twoshot_kernel<1, true> : allreduce_twoshot_kernel<1, false>);
+        B200_CHECK_CUDA(launch_kernel(k2, dim3(rows), dim3(256), 0, stream, dim3(1, 1, 1), c->dev, parity,
+                                      static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(residual),
+                                      static_cast<const __nv_bfloat16*>(weight), rows, hidden, eps, status));
+        return B200_OK;
+    }
     // Every rank must launch the same number of CTAs: the handshake pairs CTA slots.
     const int grid = rows < kMaxCommBlocks ? rows : kMaxCommBlocks;
     auto kernel = mode == 0 ? allreduce_kernel<0, false>

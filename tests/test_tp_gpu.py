@@ -18,10 +18,13 @@ def _free_port():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("kind", ["llama", "moe_ep"])
-def test_tp2_engine_matches_unsharded_oracle(tmp_path, kind):
+@pytest.mark.parametrize("kind,two_shot", [("llama", False), ("moe_ep", False), ("llama", True)])
+def test_tp2_engine_matches_unsharded_oracle(tmp_path, monkeypatch, kind, two_shot):
     """llama: heads and MLP columns split over the two GPUs.  moe_ep: experts partitioned over the
-    GPUs (expert parallelism riding on the fused all-reduce) and the single kv head replicated."""
+    GPUs (expert parallelism riding on the fused all-reduce) and the single kv head replicated.
+    two_shot: the reduce-scatter + gather form of the all-reduce that larger groups use."""
+    if two_shot:
+        monkeypatch.setenv("B200_AR_TWO_SHOT_MIN_WORLD", "2")   # read when the communicator is created
     out = tmp_path / "tp_gpu.pt"
     mp.spawn(tp_workers.gpu_engine_worker, args=(2, _free_port(), str(out), kind), nprocs=2, join=True)
     r = torch.load(out)
