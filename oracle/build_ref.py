@@ -4,7 +4,7 @@ Only the part of the reference's path that is CPU-capable and self-contained is 
 layer (src/moe/moe.cc).  The dense forward cannot be: its layers are CUDA-only and depend on
 FlashInfer v0.2.0.post1, which the reference fetches at configure time and which is not on this
 machine.  Sources are compiled from the reference tree where they lie; nothing is copied.
-Needs the reference tree (REFERENCE_DIR, default /root/reference); without it the function
+Needs the reference tree (REFERENCE_DIR, default: a `reference` directory beside this repository); without it the function
 returns None and the golden fixtures committed under tests/golden/ stand in.
 """
 from __future__ import annotations
@@ -18,7 +18,7 @@ OUT = HERE / "_ref" / "libsglang_ref_cpu.so"
 
 
 def build(reference_dir: str | None = None, verbose: bool = False):
-    ref = Path(reference_dir or os.environ.get("REFERENCE_DIR", "/root/reference"))
+    ref = Path(reference_dir or os.environ.get("REFERENCE_DIR", str(HERE.parent.parent / "reference")))
     src = ref / "src" / "moe" / "moe.cc"
     if not src.exists():
         return None
