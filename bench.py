@@ -303,7 +303,11 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": "attention_decode_kernel",
                      "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(attn_gbs / peak, 4), "peak_kind": peak_kind + " (copy bandwidth)",
-                     "traffic": None, "launch_ms": round(attn_launch_ms, 5),
+                     # DRAM bytes per launch: the ncu capture of this kernel on the batch-64 parity case
+                     # (profiles/attention_decode_kernel_batch64.md) moved 394.5 MB for 383.8 MB of K/V;
+                     # traffic grows with the sum of contexts, so that ratio is applied to this launch
+                     "traffic": int(kv_layer_bytes * 394.5 / 383.8), "traffic_source": "ncu capture of a smaller case, scaled by bytes of K/V",
+                     "launch_ms": round(attn_launch_ms, 5),
                      "algorithmic_bytes_per_launch": int(kv_layer_bytes), "launches_timed": attn_n},
         "step_roofline": {"algorithmic_bytes_per_step": int(step_bytes),
                           "achieved_gbs": round(step_bytes / (dev_ms / K * 1e-3) / 1e9, 1),
