@@ -182,9 +182,24 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         mbar_init(smem_u32(&tmem_full_bar), 1);
         fence_mbar_init();
-    }
-    if (warp == 0 && lane == 0) {
-        tma_prefetch_desc(&tmap_w);
+        // Weight tiles first, from the thread that has just initialised the barriers: they do not
+        // depend on the kernel before this one, nor on the TMEM allocation and the block-wide
+        // barrier below, so the requests leave about half a microsecond earlier.
+        const uint64_t wpol = l2_policy_evict_first();
+        const int early = min(my_kb, p.stages);
+        for (int i = 0; i < early; ++i) {
+            const uint32_t bar = smem_u32(&full_bar[i]);
+            const uint32_t dst = smem_base + i * stage_bytes;
+            const int kc = (kb_begin + i) * kBlockK;
+            mbar_arrive_expect_tx(bar, stage_bytes);
+            if (p.w_evict_first) {
+                tma_load_2d_hint(dst, &tmap_w, kc, w_row0 + n0, bar, wpol);
+                if (NUM_A == 2) tma_load_2d_hint(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar, wpol);
+            } else {
+                tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
+                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
+            }
+        }
         tma_prefetch_desc(tx);
     }
     if (warp == 1) {
@@ -201,21 +216,12 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
     if (warp == 0) {
         if (lane == 0) {
-            // Weight tiles first: they do not depend on the kernel before this one.
+            // (the first ring-full of weight tiles was requested during set-up)
             const uint64_t wpol = l2_policy_evict_first();
             auto load_w = [&](uint32_t dst, int kc, int row, uint32_t bar) {
                 if (p.w_evict_first) tma_load_2d_hint(dst, &tmap_w, kc, row, bar, wpol);
                 else tma_load_2d(dst, &tmap_w, kc, row, bar);
             };
-            const int early = min(my_kb, p.stages);
-            for (int i = 0; i < early; ++i) {
-                const uint32_t bar = smem_u32(&full_bar[i]);
-                const uint32_t dst = smem_base + i * stage_bytes;
-                const int kc = (kb_begin + i) * kBlockK;
-                mbar_arrive_expect_tx(bar, stage_bytes);
-                load_w(dst, kc, w_row0 + n0, bar);
-                if (NUM_A == 2) load_w(dst + a_bytes, kc, w_row0 + p.up_row_offset + n0, bar);
-            }
             pdl_wait_prior();
             for (int i = 0; i < my_kb && !failed; ++i) {
                 const int s = i % p.stages;

@@ -214,11 +214,12 @@ int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weig
     // Few rows (decode): one row per warp for the most parallelism; many rows (prefill): four per
     // warp with the next row's loads in flight.
     const int rows_per_warp = rows >= 32768 ? 4 : 1;   // passes of 4 rows each
-    const int64_t rows_per_block = 4 * 4 * rows_per_warp;
+    const int warps_per_block = rows >= 32768 ? 4 : 1; // decode: one warp per CTA, spread over all SMs
+    const int64_t rows_per_block = 4 * warps_per_block * rows_per_warp;
     const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
 #define B200_LAUNCH_QRS(D)                                                                       \
     B200_CHECK_CUDA(launch_kernel(                                                               \
-        qknorm_rope_store_kernel<D>, dim3(blocks), dim3(128), 0, stream, dim3(1, 1, 1),          \
+        qknorm_rope_store_kernel<D>, dim3(blocks), dim3(32 * warps_per_block), 0, stream, dim3(1, 1, 1), \
         static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_weight),           \
         static_cast<const __nv_bfloat16*>(k_weight), cos_table, sin_table, positions, out_loc,   \
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), tokens,      \
