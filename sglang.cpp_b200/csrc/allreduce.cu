@@ -32,8 +32,8 @@ struct CommDevice {
     const __nv_bfloat16* peer_buf[2][kMaxRanks];  // [parity][rank] -> that rank's exchange buffer
     uint32_t* peer_flags[kMaxRanks];              // [rank] -> that rank's flag table [blocks][ranks]
     uint32_t* self_counter;                       // [blocks] calls this CTA slot has completed
-    const __nv_bfloat16* peer_gather[kMaxRanks];  // [rank] -> that rank's buffer of reduced rows (two-shot)
-    uint32_t* peer_ready[kMaxRanks];              // [rank] -> that rank's "row reduced" flags [blocks]
+    void* peer_gather[kMaxRanks];                 // [rank] -> that rank's buffer of reduced rows (two-shot):
+                                                  // 8-byte words of two bf16 values + the call number
     int rank, world;
 };
 
@@ -153,15 +153,18 @@ allreduce_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat
 }
 
 
-// Two-shot variant for larger groups: row `row` is reduced by rank row % world alone, which reads
-// that row of every rank's partial (1/world of what the one-shot kernel reads), writes the bf16
-// sum into its gather buffer and raises a per-row flag on every peer; the other ranks wait for
-// that flag and fetch the finished row.  Every rank then runs the same add + norm on the same
-// bits, so the replicated residual stays replicated.  One CTA per row, grid = rows on every rank.
-//   flag A (peer_flags of the owner, slot = row, one word per source rank): "my partial is written";
-//   flag B (peer_ready of every rank, one word per row): "the owner's sum of this row is written".
-// The gather buffer needs no parity: a rank can only reach this call's write of a row after every
-// peer announced this call's partial, which each does after finishing all reads of the call before.
+// Two-shot variant: row `row` is reduced by rank row % world alone, which reads that row of every
+// rank's partial (1/world of what the one-shot kernel reads) and pushes the bf16 sum into every
+// peer's gather buffer.  Every rank then runs the same add + norm on the same bits, so the
+// replicated residual stays replicated.  One CTA per row, grid = rows on every rank.
+//   flag A (peer_flags of the owner, slot = row, one word per source rank): "my partial is written".
+//   The pushed row needs no flag of its own and no fence: every 8-byte word of the gather buffer
+//   holds two bf16 values and the call number, is written with one store and is polled by the
+//   thread that consumes it (the low-latency protocol of collective libraries: half the link
+//   bandwidth for one NVLink traversal instead of data + fence + flag + fetch).
+// The gather buffer needs no parity: a rank can only reach this call's push of a row after every
+// peer announced this call's partial, which each does after consuming the call before; words of
+// earlier calls carry earlier numbers.
 template <int MODE, bool ROUND_FIRST>
 __global__ void __launch_bounds__(256)
 allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat16* residual,
@@ -213,38 +216,44 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) y[i][j] = pack_bf16(acc[2 * j], acc[2 * j + 1]);
-            reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(c.peer_gather[c.rank]))[base + v] =
-                make_uint4(y[i][0], y[i][1], y[i][2], y[i][3]);
-        }
-        // the row must be visible to the other GPUs before the flag that announces it
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x < c.world && threadIdx.x != c.rank)
-            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(c.peer_ready[threadIdx.x] + row), "r"(call)
-                         : "memory");
-    } else {
-        if (threadIdx.x == 0) {
-            const uint32_t* f = c.peer_ready[c.rank] + row;
-            const uint64_t t0 = global_timer_ns();
-            uint32_t spins = 0;
-            for (;;) {
-                uint32_t v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                if (static_cast<int32_t>(v - call) >= 0) break;
-                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
-                    atomicExch(&status[kStatusTimeout], 403);
-                    s_ok = 0;
-                    break;
-                }
+            // two bf16 pairs + call number per 16-byte store, to every peer
+            const uint4 w0 = make_uint4(y[i][0], call, y[i][1], call);
+            const uint4 w1 = make_uint4(y[i][2], call, y[i][3], call);
+            for (int r = 0; r < c.world; ++r) {
+                if (r == c.rank) continue;
+                uint4* dst = reinterpret_cast<uint4*>(c.peer_gather[r]) + (base + v) * 2;
+                asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(w0.x), "r"(w0.y),
+                             "r"(w0.z), "r"(w0.w)
+                             : "memory");
+                asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 1), "r"(w1.x), "r"(w1.y),
+                             "r"(w1.z), "r"(w1.w)
+                             : "memory");
             }
         }
-        __syncthreads();
+    } else {
+        const uint64_t t0 = global_timer_ns();
 #pragma unroll
         for (int i = 0; i < kArVecPerThread; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
             if (v >= nvec) continue;
-            const uint4 a = __ldcv(reinterpret_cast<const uint4*>(c.peer_gather[owner]) + base + v);
-            y[i][0] = a.x; y[i][1] = a.y; y[i][2] = a.z; y[i][3] = a.w;
+            const uint4* src = reinterpret_cast<const uint4*>(c.peer_gather[c.rank]) + (base + v) * 2;
+            uint32_t spins = 0;
+            for (;;) {
+                uint4 w0, w1;
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "l"(src) : "memory");
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "l"(src + 1) : "memory");
+                if (w0.y == call && w0.w == call && w1.y == call && w1.w == call) {
+                    y[i][0] = w0.x; y[i][1] = w0.z; y[i][2] = w1.x; y[i][3] = w1.z;
+                    break;
+                }
+                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+                    atomicExch(&status[kStatusTimeout], 403);
+                    y[i][0] = y[i][1] = y[i][2] = y[i][3] = 0u;
+                    break;
+                }
+            }
         }
     }
     if (threadIdx.x == 0) c.self_counter[row] = call;
@@ -311,8 +320,8 @@ struct b200_comm {
     void* peer_base[kMaxRanks] = {};  // mapped bases (own entry = local_base)
     bool connected = false;
     CommDevice dev = {};
-    int64_t flags_bytes = 0, counters_bytes = 0, ready_bytes = 0;
-    int two_shot_min_world = 4;   // B200_AR_TWO_SHOT_MIN_WORLD: groups of at least this size use the two-shot kernel
+    int64_t flags_bytes = 0, counters_bytes = 0;
+    int two_shot_min_world = 8;   // B200_AR_TWO_SHOT_MIN_WORLD: groups of at least this size use the two-shot kernel
 };
 
 namespace {
@@ -333,10 +342,9 @@ int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out)
     c->buffer_bytes = align_up(buffer_bytes, 256);
     c->flags_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * kMaxRanks * 4, 256);
     c->counters_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
-    c->ready_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
     if (const char* v = getenv("B200_AR_TWO_SHOT_MIN_WORLD")) c->two_shot_min_world = atoi(v);
-    // [flags | counters | buffer 0 | buffer 1 | ready flags | gather buffer]
-    const int64_t total = c->flags_bytes + c->counters_bytes + 3 * c->buffer_bytes + c->ready_bytes;
+    // [flags | counters | buffer 0 | buffer 1 | gather buffer (2 x: half of every word is the call number)]
+    const int64_t total = c->flags_bytes + c->counters_bytes + 4 * c->buffer_bytes;
     if (cudaMalloc(&c->local_base, static_cast<size_t>(total)) != cudaSuccess ||
         cudaMemset(c->local_base, 0, static_cast<size_t>(total)) != cudaSuccess ||
         cudaDeviceSynchronize() != cudaSuccess) {
@@ -376,9 +384,7 @@ int b200_comm_connect(b200_comm* c, const void* all_handles) {
         for (int p = 0; p < 2; ++p)
             c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
                                                                           p * c->buffer_bytes);
-        char* tail = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
-        c->dev.peer_ready[r] = reinterpret_cast<uint32_t*>(tail);
-        c->dev.peer_gather[r] = reinterpret_cast<const __nv_bfloat16*>(tail + c->ready_bytes);
+        c->dev.peer_gather[r] = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
     }
     c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
     c->dev.rank = c->rank;
