@@ -1,5 +1,6 @@
-// One-shot all-reduce over NVLink peer memory, alone or fused with the residual add + RMSNorm
-// that follows every row-parallel projection under tensor parallelism.
+// All-reduce over NVLink peer memory (a one-shot kernel, and a two-shot kernel for groups of eight),
+// alone or fused with the residual add + RMSNorm that follows every row-parallel projection under
+// tensor parallelism.
 //
 // Stands where tensor_model_parallel_all_reduce does (src/distributed/distributed.cc:205-226,
 // called from LinearRowParallel / LinearOProj::forward, src/layers/linear.cc:52-55,73-76), and
