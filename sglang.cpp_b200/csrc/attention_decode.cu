@@ -63,7 +63,7 @@ struct DecodeParams {
     int* counters;      // [kMaxBatch], zero between calls
     int max_items;
     int* status;
-    L2PrefetchList pf;
+    int kv_evict_first;   // stream K/V through L2 with the evict-first policy (read once per step)
 };
 
 struct ItemInfo {
@@ -218,25 +218,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         sl = 0;
                     }
                     const uint32_t dst = stage_base + which * kHalfBytes + copy * copy_bytes;
-                    if (p.pf.kv_evict_first)
+                    if (p.kv_evict_first)
                         tma_load_3d_hint(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
                                          static_cast<int>(sl), 0, bar, kv_policy);
                     else
                         tma_load_3d(dst, which < 2 ? &tmap_k : &tmap_v, (which & 1) * 64,
                                     static_cast<int>(sl), 0, bar);
                 }
-            }
-        }
-        // All of this CTA's K/V is on its way: while the consumers drain the ring, ask for this
-        // CTA's share of the weights the next kernels read, in 8 KB pieces spread over all CTAs.
-        constexpr uint32_t kPiece = 8192;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t bytes = p.pf.bytes[i];
-            const uint32_t pieces = (bytes + kPiece - 1) / kPiece;
-            for (uint32_t c = blockIdx.x * 32 + lane; c < pieces; c += gridDim.x * 32) {
-                const uint32_t off = c * kPiece;
-                l2_prefetch_bulk(static_cast<const uint8_t*>(p.pf.ptr[i]) + off, min(kPiece, bytes - off));
             }
         }
         return;
@@ -543,7 +531,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                             const int32_t* page_table, int64_t pt_stride, const int32_t* table_idx,
                             const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
                             int page_size, float sm_scale, void* workspace, int64_t workspace_bytes,
-                            int* status, cudaStream_t stream, const L2PrefetchList* prefetch) {
+                            int* status, cudaStream_t stream, bool kv_evict_first) {
     const int kg = kConsumerWarps / kv_heads;
     const int grid = sm_count();
     // Workspace layout: counters | ws_ml | ws_o
@@ -581,7 +569,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
     p.ws_o = p.ws_ml + max_items * kg * q_heads * 2;
     p.max_items = static_cast<int>(max_items < (1 << 30) ? max_items : (1 << 30));
     p.status = status;
-    if (prefetch) p.pf = *prefetch;
+    p.kv_evict_first = kv_evict_first ? 1 : 0;
 
     const int smem = kStages * kStageBytes + 1024;
     static bool attr_set = false;

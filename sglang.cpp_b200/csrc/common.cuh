@@ -204,15 +204,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
         : "memory");
 }
 
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap, int c0, int c1,
-                                                 uint32_t bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar), "l"(policy)
-        : "memory");
-}
-
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2,
                                             uint32_t bar) {
     asm volatile(
@@ -236,12 +227,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
-// Ask for [ptr, ptr + bytes) to be brought into L2 (16-byte aligned address and size); returns at once.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* ptr, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(ptr)), "r"(bytes)
-                 : "memory");
-}
-
 // ---- warp-level matrix helpers ----------------------------------------------
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1,

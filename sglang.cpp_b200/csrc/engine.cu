@@ -182,7 +182,6 @@ struct b200_engine {
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
-    bool l2_prefetch = false;    // B200_L2_PREFETCH=1: weight prefetch from the attention kernel (measured: no gain)
     bool kv_evict_first = true;  // B200_KV_EVICT_FIRST=0: K/V loads with the default L2 policy
     // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
     static int seed_offset(int Bp) { return (7 * Bp + 1 + 1) & ~1; }
@@ -335,32 +334,10 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         }
         if (phase == B200_PHASE_DECODE && B200_TUNE_SKIP(1)) {
         } else if (phase == B200_PHASE_DECODE) {
-            // The weights of the kernels between this attention launch and the next one (o, the MLP,
-            // the next layer's qkv) are brought into L2 while the attention pipeline drains.
-            L2PrefetchList pf;
-            pf.kv_evict_first = e->kv_evict_first ? 1 : 0;
-            if (e->l2_prefetch) {
-                auto bytes_of = [](int64_t elems) { return static_cast<uint32_t>(elems * 2 / 16 * 16); };
-                pf.ptr[0] = L.o;
-                pf.bytes[0] = bytes_of(static_cast<int64_t>(hidden) * e->hq * d);
-                if (m.num_experts == 0) {
-                    pf.ptr[1] = L.gate_up;
-                    pf.bytes[1] = bytes_of(2 * static_cast<int64_t>(e->inter) * hidden);
-                    pf.ptr[2] = L.down;
-                    pf.bytes[2] = bytes_of(static_cast<int64_t>(hidden) * e->inter);
-                } else {
-                    pf.ptr[1] = L.router;
-                    pf.bytes[1] = bytes_of(static_cast<int64_t>(m.num_experts) * hidden);
-                }
-                if (l + 1 < m.num_layers) {
-                    pf.ptr[3] = e->layers[l + 1].qkv;
-                    pf.bytes[3] = bytes_of(static_cast<int64_t>(e->qkv_dim) * hidden);
-                }
-            }
             B200_TRY(launch_attention_decode(e->attn_out, e->qkv, e->qkv_dim, d, L.tmap_k, L.tmap_v,
                                              e->num_slots, e->page_table, e->pt_cols, meta_table_idx,
                                              e->seq_lens, Bp, e->hq, e->hkv, e->c.page_size, e->sm_scale,
-                                             e->attn_ws, e->attn_ws_bytes, e->status, s, &pf));
+                                             e->attn_ws, e->attn_ws_bytes, e->status, s, e->kv_evict_first));
         } else {
             B200_TRY(launch_attention_prefill(e->attn_out, e->qkv, e->qkv_dim, d, k_cache, v_cache,
                                               e->num_slots, e->page_table, e->pt_cols, meta_table_idx,
@@ -534,7 +511,6 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     e->status = device_status_words(&err);
     if (err != B200_OK) { delete e; return err; }
     if (const char* v = getenv("B200_PDL")) e->use_pdl = atoi(v) != 0;
-    if (const char* v = getenv("B200_L2_PREFETCH")) e->l2_prefetch = atoi(v) != 0;
     if (const char* v = getenv("B200_KV_EVICT_FIRST")) e->kv_evict_first = atoi(v) != 0;
 
     auto fail = [&](int code) { b200_engine_destroy(e); return code; };

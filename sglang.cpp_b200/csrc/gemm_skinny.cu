@@ -118,7 +118,6 @@ struct SkinnyParams {
     const int32_t* group_counts;
     const int32_t* group_offsets;
     int w_rows_per_group;
-    int w_evict_first;   // B200_W_EVICT_FIRST=1: weight tiles loaded with the evict-first L2 policy (measured: no gain)
 };
 
 template <int EPI>
@@ -185,20 +184,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         // Weight tiles first, from the thread that has just initialised the barriers: they do not
         // depend on the kernel before this one, nor on the TMEM allocation and the block-wide
         // barrier below, so the requests leave about half a microsecond earlier.
-        const uint64_t wpol = l2_policy_evict_first();
         const int early = min(my_kb, p.stages);
         for (int i = 0; i < early; ++i) {
             const uint32_t bar = smem_u32(&full_bar[i]);
             const uint32_t dst = smem_base + i * stage_bytes;
             const int kc = (kb_begin + i) * kBlockK;
             mbar_arrive_expect_tx(bar, stage_bytes);
-            if (p.w_evict_first) {
-                tma_load_2d_hint(dst, &tmap_w, kc, w_row0 + n0, bar, wpol);
-                if (NUM_A == 2) tma_load_2d_hint(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar, wpol);
-            } else {
-                tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
-                if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
-            }
+            tma_load_2d(dst, &tmap_w, kc, w_row0 + n0, bar);
+            if (NUM_A == 2) tma_load_2d(dst + a_bytes, &tmap_w, kc, w_row0 + p.up_row_offset + n0, bar);
         }
         tma_prefetch_desc(tx);
     }
@@ -217,11 +210,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (warp == 0) {
         if (lane == 0) {
             // (the first ring-full of weight tiles was requested during set-up)
-            const uint64_t wpol = l2_policy_evict_first();
-            auto load_w = [&](uint32_t dst, int kc, int row, uint32_t bar) {
-                if (p.w_evict_first) tma_load_2d_hint(dst, &tmap_w, kc, row, bar, wpol);
-                else tma_load_2d(dst, &tmap_w, kc, row, bar);
-            };
+            auto load_w = [&](uint32_t dst, int kc, int row, uint32_t bar) { tma_load_2d(dst, &tmap_w, kc, row, bar); };
             pdl_wait_prior();
             for (int i = 0; i < my_kb && !failed; ++i) {
                 const int s = i % p.stages;
@@ -461,14 +450,6 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t out
     return B200_OK;
 }
 
-static int w_evict_first_default() {
-    static const int v = [] {
-        const char* e = getenv("B200_W_EVICT_FIRST");
-        return (e && *e) ? atoi(e) : 0;
-    }();
-    return v;
-}
-
 static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return (v && *v) ? atoi(v) : dflt;
@@ -549,7 +530,6 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.group_counts = nullptr;
     p.group_offsets = nullptr;
     p.w_rows_per_group = 0;
-    p.w_evict_first = w_evict_first_default();
 
     auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -606,7 +586,6 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     p.group_counts = counts;
     p.group_offsets = offsets;
     p.w_rows_per_group = N;
-    p.w_evict_first = w_evict_first_default();
     auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));

@@ -53,14 +53,6 @@ int launch_moe_forward(void* out, const void* hidden, const void* router_logits,
                        int activation, int expert_begin, int num_local_experts, void* workspace,
                        int* status, cudaStream_t stream);
 
-// Weights the kernels after a decode-attention launch will read: the attention kernel asks for
-// them to be brought into L2 while its own pipeline drains.
-struct L2PrefetchList {
-    const void* ptr[4] = {nullptr, nullptr, nullptr, nullptr};
-    uint32_t bytes[4] = {0, 0, 0, 0};   // multiples of 16
-    int kv_evict_first = 0;             // stream K/V through L2 with the evict-first policy
-};
-
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);
 int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,
@@ -68,7 +60,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                             const int32_t* page_table, int64_t pt_stride, const int32_t* table_idx,
                             const int32_t* seq_lens, int batch, int q_heads, int kv_heads,
                             int page_size, float sm_scale, void* workspace, int64_t workspace_bytes,
-                            int* status, cudaStream_t stream, const L2PrefetchList* prefetch = nullptr);
+                            int* status, cudaStream_t stream, bool kv_evict_first = false);
 bool attention_prefill_tc_supported(const void* q, int64_t q_st, int64_t q_sh, const void* out);
 int launch_attention_prefill_tc(void* out, const void* q, int64_t q_st, int64_t q_sh, const void* k_cache,
                                 const void* v_cache, int64_t num_slots, const int32_t* page_table,
