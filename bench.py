@@ -14,6 +14,12 @@ host arrays go through the C ABI from host memory, the step's metadata is copied
 from pinned memory and the sampled tokens are copied device-to-host and waited for.  With
 --gpus N > 1 (launched under torchrun) every rank runs an independent replica of the workload
 (the 0.6B model does not shard); the job's time is the max over ranks.
+
+Other workloads (not the headline metric): --context N gives every prompt N tokens (the
+"batch 64 / 2048-token context" point); --workload c4 is Llama-3-8B under tensor parallelism and
+--workload c5 Qwen3-30B-A3B under expert parallelism + attention TP over the N ranks (strong
+scaling, weights drawn on the device); --eager / --profile-region / --profile-prefill shape a run
+for a profiler's launch list.
 """
 from __future__ import annotations
 

@@ -33,3 +33,22 @@ def test_tp2_engine_matches_unsharded_oracle(tmp_path, monkeypatch, kind, two_sh
     rms = float(r["want_prefill"].float().pow(2).mean().sqrt())
     assert float(d.max()) <= 2e-2, f"max-abs {float(d.max()):.4g}"
     assert float(d.mean()) <= 1e-3 + rms * 2 ** -8, f"mean-abs {float(d.mean()):.4g}"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("two_shot", [False, True])
+def test_allreduce_calls_of_the_c_abi(tmp_path, monkeypatch, two_shot):
+    """b200_allreduce is bit-exact (fp32 sum in rank order, one bf16 rounding); the fused form
+    leaves the same residual and the norm of it, over five calls alternating the buffer parity."""
+    if two_shot:
+        monkeypatch.setenv("B200_AR_TWO_SHOT_MIN_WORLD", "2")
+    out = tmp_path / "ar.pt"
+    mp.spawn(tp_workers.gpu_allreduce_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    r = torch.load(out)
+    assert len(r["plain"]) == 3 and len(r["fused_x"]) == 2
+    for got, want in zip(r["plain"], r["want_plain"]):
+        assert torch.equal(got, want)
+    for got, want in zip(r["fused_res"], r["want_res"]):
+        assert torch.equal(got, want)
+    for got, want in zip(r["fused_x"], r["want_x"]):
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2 ** -7)

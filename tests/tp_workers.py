@@ -138,3 +138,63 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     dist.barrier()
     eng.close()
     dist.destroy_process_group()
+
+
+def gpu_allreduce_worker(rank, world, port, out_path):
+    """The all-reduce calls of the C ABI on their own (tensor_model_parallel_all_reduce and its
+    fusion with add + norm), several calls in a row so that both buffer parities and the call
+    numbering are exercised; rank 0 saves what it got and what the sums should be."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import ctypes
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+
+    pkg = entry.load_package()
+    lib = pkg.load_library()
+    from sglang_cpp_b200._lib import call
+    from sglang_cpp_b200.tp import exchange_handles
+
+    rows, hidden = 37, 1024
+    comm = ctypes.c_void_p()
+    call("b200_comm_create", rank, world, rows * hidden * 2, ctypes.byref(comm))
+    n = lib.b200_comm_handle_bytes()
+    buf = ctypes.create_string_buffer(n)
+    call("b200_comm_export", comm, buf)
+    call("b200_comm_connect", comm, exchange_handles(buf.raw, rank, world))
+    gen = torch.Generator().manual_seed(17)
+    res = {"plain": [], "want_plain": [], "fused_x": [], "fused_res": [], "want_x": [], "want_res": []}
+    weight = (torch.randn(hidden, generator=gen) * 0.1 + 1).to(torch.bfloat16)
+    residual0 = (torch.randn(rows, hidden, generator=gen)).to(torch.bfloat16)
+    residual = residual0.cuda()
+    want_res = residual0.clone()
+    stream = torch.cuda.current_stream().cuda_stream
+    for c in range(5):
+        parts = [(torch.randn(rows, hidden, generator=gen)).to(torch.bfloat16) for _ in range(world)]
+        total = sum(p.float() for p in parts).to(torch.bfloat16)        # fp32 sum in rank order, one rounding
+        ptr = lib.b200_comm_buffer(comm, c & 1)
+        from sglang_cpp_b200.engine import _as_cuda_tensor
+        _as_cuda_tensor(ptr, rows * hidden * 2).view(torch.bfloat16).copy_(parts[rank].cuda().flatten())
+        torch.cuda.synchronize()
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda")
+        if c % 2 == 0:
+            call("b200_allreduce", comm, c & 1, out.data_ptr(), rows, hidden, stream)
+            torch.cuda.synchronize()
+            res["plain"].append(out.cpu())
+            res["want_plain"].append(total)
+        else:
+            call("b200_allreduce_fused_add_rmsnorm", comm, c & 1, out.data_ptr(), residual.data_ptr(),
+                 weight.cuda().data_ptr(), rows, hidden, 1e-6, 1, stream)
+            torch.cuda.synchronize()
+            want_res = (total.float() + want_res.float()).to(torch.bfloat16)
+            res["fused_x"].append(out.cpu())
+            res["fused_res"].append(residual.cpu().clone())
+            res["want_x"].append(O.rmsnorm(want_res, weight, 1e-6))
+            res["want_res"].append(want_res.clone())
+        dist.barrier()
+    if rank == 0:
+        torch.save(res, out_path)
+    dist.barrier()
+    call("b200_comm_destroy", comm)
+    dist.destroy_process_group()
