@@ -244,20 +244,26 @@ def run_gpu(args):
     _, _, launches_per_step = engine.read_profile()
 
     # ---- phase B: end to end, the host waits for every step's tokens ----
+    # Driven the way the scheduler's decode loop drives the engine: per step the host arrays cross
+    # the C ABI, the metadata goes host-to-device from pinned memory, the tokens come back and are
+    # waited for.  (DecodeSession keeps the per-step host bookkeeping in vector form.)
+    from sglang_cpp_b200.host_batch import DecodeSession
     reset()
     for _ in range(W):
         hb.decode(reqs).synchronize()
     barrier()
+    session = DecodeSession(hb, reqs)
     step_ms = []
     t0 = time.perf_counter()
     for _ in range(K):
         ts = time.perf_counter()
-        out = hb.decode(reqs)
-        out.synchronize()
-        _ = out.next_tokens_cpu[0].item()
+        toks = session.step()
+        engine.synchronize()
+        _ = toks[0].item()
         step_ms.append((time.perf_counter() - ts) * 1e3)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    session.sync_back()
     clocks = sampler.stop()
 
     # ---- phase C: attention launches timed one by one (eager steps, event pair per launch) ----

@@ -170,3 +170,59 @@ class HostBatcher:
         for r in reqs:
             r.complete_one()
         return out
+
+
+class DecodeSession:
+    """A fixed set of running requests stepped many times: what the scheduler's decode loop does
+    (src/scheduler/scheduler.cc:391-422, decode.cc:10-27) with the per-step host work kept to a few
+    vector operations, as the reference's C++ loop keeps it.  The request lengths live in numpy
+    arrays between ``step()`` calls; ``sync_back()`` writes them to the ``Req`` objects again."""
+
+    def __init__(self, batcher: HostBatcher, reqs, padded_size: Optional[int] = None):
+        import ctypes
+
+        from ._lib import StepStruct
+
+        self.hb, self.reqs, self.engine = batcher, list(reqs), batcher.engine
+        n = len(self.reqs)
+        bp = max(padded_size or n, n)
+        dummy = self.engine.dummy_table_idx
+        self.n = n
+        self.table_idx = np.array([r.table_idx for r in self.reqs] + [dummy] * (bp - n), dtype=np.int32)
+        self.cached = np.zeros(bp, dtype=np.int32)
+        self.extend = np.ones(bp, dtype=np.int32)
+        self.write_pos = np.full(max(n, 1), -1, dtype=np.int32)
+        self.device_len = np.array([r.device_len for r in self.reqs], dtype=np.int64)
+        self.max_len = np.array([r.max_device_len for r in self.reqs], dtype=np.int64)
+        self.cached[:n] = [r.cached_len for r in self.reqs]
+        self.pages_have = np.array([-(-len(batcher.slots_of(r)) // batcher.page_size) for r in self.reqs], dtype=np.int64)
+        self._st = StepStruct(1, n, bp, self.table_idx.ctypes.data, self.cached.ctypes.data, self.extend.ctypes.data,
+                              self.write_pos.ctypes.data, None, None, None, None, 0)
+        self._st_ref = ctypes.byref(self._st)
+
+    def step(self):
+        """One decode step of every request (asynchronous, like Engine.forward_batch)."""
+        from ._lib import call
+
+        hb, P = self.hb, self.hb.page_size
+        # pages for the position this step writes (CacheManager::allocate_paged): rare, so per request
+        need = np.nonzero(-(-self.device_len // P) > self.pages_have)[0]
+        for i in need:
+            r = self.reqs[int(i)]
+            r.device_len = int(self.device_len[i])
+            hb.allocate([r])
+            self.pages_have[i] = -(-len(hb.slots_of(r)) // P)
+        can = self.device_len < self.max_len
+        self.write_pos[:self.n] = np.where(can, self.device_len, -1)
+        eng = self.engine
+        self._st.step_index = eng._step_index
+        eng._step_index += 1
+        call("b200_engine_step", eng._h, self._st_ref, eng._next_tokens_cpu.data_ptr())
+        # Req::complete_one for every request
+        self.cached[:self.n] = self.device_len
+        self.device_len += can
+        return eng._next_tokens_cpu[:self.n]
+
+    def sync_back(self) -> None:
+        for i, r in enumerate(self.reqs):
+            r.cached_len, r.device_len = int(self.cached[i]), int(self.device_len[i])

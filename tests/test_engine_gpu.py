@@ -363,3 +363,38 @@ def test_config3_chunked_prefill_interleaved_with_sampled_decode(pkg):
     other = run(500, check=False)
     assert first == again
     assert first != other
+
+
+def test_decode_session_equals_step_by_step_batcher(pkg):
+    """The vector-form decode loop (DecodeSession) issues exactly the steps HostBatcher.decode does:
+    same tokens over 20 steps that cross page boundaries, same request state and pages afterwards."""
+    from sglang_cpp_b200.host_batch import DecodeSession
+
+    cfg = small_cfg("qwen3")
+    runs = []
+    for fast in (False, True):
+        pr = Pair(pkg, cfg, 16)
+        rng = np.random.default_rng(21)
+        news = (30, 30, 30)
+        reqs = [pr.hb.add_request(rng.integers(0, cfg.vocab_size, size=n).astype(np.int32), m)
+                for n, m in zip((12, 40, 7), news)]
+        pr.hb.prefill(reqs).synchronize()
+        toks = []
+        if fast:
+            s = DecodeSession(pr.hb, reqs, padded_size=4)
+            for _ in range(20):
+                t = s.step()
+                pr.engine.synchronize()
+                toks.append(t.clone())
+            s.sync_back()
+        else:
+            for _ in range(20):
+                out = pr.hb.decode(reqs, padded_size=4)
+                out.synchronize()
+                toks.append(out.next_tokens_cpu.clone())
+        runs.append((torch.stack(toks), [(r.cached_len, r.device_len) for r in reqs],
+                     [list(pr.hb.slots_of(r)) for r in reqs]))
+        pr.engine.close()
+    assert torch.equal(runs[0][0], runs[1][0])
+    assert runs[0][1] == runs[1][1]
+    assert runs[0][2] == runs[1][2]
