@@ -553,6 +553,10 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     const int n_tiles = div_ceil(n_out, kTileN);
     const int slabs = div_ceil(max_rows_per_group, 256);
     if (num_groups == 0 || slabs == 0 || total_rows == 0) return B200_OK;
+    // Many rows per group on average (prefill batches): tensor-bound, take the tile kernel.
+    if (total_rows >= static_cast<int64_t>(num_groups) * env_int("B200_GROUPED_TILE_MIN_ROWS", 128) && num_groups <= 256)
+        return launch_grouped_tile_gemm(y, x, w, counts, offsets, num_groups, total_rows, N, K, epilogue, status,
+                                        stream);
     int nt_max = 32;
     while (nt_max < 256 && nt_max < max_rows_per_group) nt_max *= 2;
     const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt_max * kBlockK * 2;

@@ -39,6 +39,21 @@ struct TileParams {
     int epilogue;       // B200_EPILOGUE_*
     int m_tiles, n_tiles;
     int* status;
+    // Grouped mode (expert GEMMs with many rows per expert): group g multiplies rows
+    // [offsets[g], offsets[g] + counts[g]) of x by rows [g * w_rows_per_group, ...) of w; counts and
+    // offsets live in device memory, so the tile list is built on the device by every CTA.
+    const int32_t* group_counts;
+    const int32_t* group_offsets;
+    int num_groups;
+    int w_rows_per_group;
+};
+
+constexpr int kMaxGroups = 256;
+
+// Where a tile lives: first row of x / y, rows of it that belong to the tile, first feature, first
+// row of the weights (of the "gate" half when gated).
+struct TileAt {
+    int row0, valid, n0, w_row0;
 };
 
 template <int EPI>
@@ -73,7 +88,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -100,15 +114,61 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const uint32_t tmem_base = tmem_base_slot;
     pdl_wait_prior();
 
+    __shared__ int s_first_tile[kMaxGroups + 1];   // grouped mode: first tile of every group
+    __shared__ int s_cnt[kMaxGroups], s_off[kMaxGroups];
+    const bool grouped = p.group_counts != nullptr;
+    constexpr int kOutTile = GATED ? kTN / 2 : kTN;
+    if (grouped) {
+        for (int g = threadIdx.x; g < p.num_groups; g += kThreads) {
+            s_cnt[g] = p.group_counts[g];
+            s_off[g] = p.group_offsets[g];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = 0;
+            for (int g = 0; g < p.num_groups; ++g) {
+                s_first_tile[g] = run;
+                run += ((max(s_cnt[g], 0) + kTM - 1) / kTM) * p.n_tiles;
+            }
+            s_first_tile[p.num_groups] = run;
+        }
+        __syncthreads();
+    }
+    const int total_tiles = grouped ? s_first_tile[p.num_groups] : p.m_tiles * p.n_tiles;
+    auto locate = [&](int t) -> TileAt {
+        TileAt a;
+        if (!grouped) {
+            int mt, ntile;
+            tile_coords(t, p.m_tiles, p.n_tiles, mt, ntile);
+            a.row0 = mt * kTM;
+            a.valid = min(kTM, p.M - a.row0);
+            a.n0 = ntile * kOutTile;
+            a.w_row0 = 0;
+            return a;
+        }
+        int lo = 0, hi = p.num_groups;   // largest g with s_first_tile[g] <= t
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_first_tile[mid] <= t) lo = mid; else hi = mid;
+        }
+        const int r = t - s_first_tile[lo];
+        const int mtiles = (s_cnt[lo] + kTM - 1) / kTM;
+        const int ntile = r / mtiles, mt = r - ntile * mtiles;   // token block fastest: neighbours share W
+        a.row0 = s_off[lo] + mt * kTM;
+        a.valid = min(kTM, s_cnt[lo] - mt * kTM);
+        a.n0 = ntile * kOutTile;
+        a.w_row0 = lo * p.w_rows_per_group;
+        return a;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;
             bool failed = false;
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
-                int mt, ntile;
-                tile_coords(t, p.m_tiles, p.n_tiles, mt, ntile);
-                const int m0 = mt * kTM;
-                const int n0 = ntile * (GATED ? kTN / 2 : kTN);
+                const TileAt at = locate(t);
+                const int m0 = at.row0;
+                const int n0 = at.w_row0 + at.n0;
                 for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages) {
@@ -172,8 +232,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         int tcount = 0;
         bool failed = false;
         for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, ++tcount) {
-            int mt, ntile;
-            tile_coords(t, p.m_tiles, p.n_tiles, mt, ntile);
+            const TileAt at = locate(t);
             const int acc = tcount & 1;
             const uint32_t par = static_cast<uint32_t>(tcount >> 1) & 1u;
             if (!mbar_wait_bounded(smem_u32(&acc_full_bar[acc]), par, p.status, 114)) {
@@ -181,10 +240,11 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 break;
             }
             tc_fence_after();
-            const int m = mt * kTM + q * 32 + lane;
+            const int m_local = q * 32 + lane;
+            const int m = at.row0 + m_local;
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kTN);
-            constexpr int kOutCols = GATED ? kTN / 2 : kTN;
-            const int n_base = ntile * kOutCols;
+            constexpr int kOutCols = kOutTile;
+            const int n_base = at.n0;
             __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.n_out;
 #pragma unroll 1
             for (int c = 0; c < kOutCols / 32; ++c) {
@@ -193,7 +253,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 if (GATED) tmem_ld_32x32b_x32(t0 + static_cast<uint32_t>(kTN / 2 + c * 32), u);
                 tmem_ld_wait();
                 const int n = n_base + c * 32;
-                if (m < p.M && n < p.n_out) {
+                if (m_local < at.valid && n < p.n_out) {
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -251,6 +311,10 @@ int launch_tile_gemm(void* y, const void* x, const void* w, const void* bias, in
     p.m_tiles = div_ceil(M, kTM);
     p.n_tiles = div_ceil(n_out, gated ? kTN / 2 : kTN);
     p.status = status;
+    p.group_counts = nullptr;
+    p.group_offsets = nullptr;
+    p.num_groups = 0;
+    p.w_rows_per_group = 0;
 
     CUtensorMap tmap_x, tmap_w;
     int err = cached_tmap(&tmap_x, x, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
@@ -270,6 +334,52 @@ int launch_tile_gemm(void* y, const void* x, const void* w, const void* bias, in
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, dim3(1, 1, 1),
+                                  tmap_x, tmap_w, p));
+    return B200_OK;
+}
+
+// Grouped form (expert layers with many rows per expert): group g multiplies rows
+// [offsets[g], offsets[g] + counts[g]) of x [total_rows, K] by w[g] ([N, K], groups stacked).
+int launch_grouped_tile_gemm(void* y, const void* x, const void* w, const int32_t* counts,
+                             const int32_t* offsets, int num_groups, int64_t total_rows, int N, int K,
+                             int epilogue, int* status, cudaStream_t stream) {
+    if (num_groups > kMaxGroups) {
+        set_last_error("grouped GEMM: %d groups exceed %d", num_groups, kMaxGroups);
+        return B200_ERR_UNSUPPORTED;
+    }
+    const bool gated = epilogue != B200_EPILOGUE_NONE;
+    const int n_out = gated ? N / 2 : N;
+    TileParams p;
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.bias = nullptr;
+    p.M = static_cast<int>(total_rows);
+    p.n_out = n_out;
+    p.up_row_offset = N / 2;
+    p.kb_total = K / kBK;
+    p.epilogue = epilogue;
+    p.m_tiles = 0;
+    p.n_tiles = div_ceil(n_out, gated ? kTN / 2 : kTN);
+    p.status = status;
+    p.group_counts = counts;
+    p.group_offsets = offsets;
+    p.num_groups = num_groups;
+    p.w_rows_per_group = N;
+    CUtensorMap tmap_x, tmap_w;
+    int err = cached_tmap(&tmap_x, x, static_cast<uint64_t>(K), static_cast<uint64_t>(total_rows),
+                          static_cast<uint64_t>(K) * 2, kBK, kTM);
+    if (err != B200_OK) return err;
+    err = cached_tmap(&tmap_w, w, static_cast<uint64_t>(K), static_cast<uint64_t>(num_groups) * N,
+                      static_cast<uint64_t>(K) * 2, kBK, gated ? kTN / 2 : kTN);
+    if (err != B200_OK) return err;
+    const uint32_t smem_bytes = kStages * kStageBytes + 1024;
+    void (*kernel)(CUtensorMap, CUtensorMap, TileParams) = tile_gemm_kernel<B200_EPILOGUE_NONE>;
+    if (epilogue == B200_EPILOGUE_SWIGLU) kernel = tile_gemm_kernel<B200_EPILOGUE_SWIGLU>;
+    if (epilogue == B200_EPILOGUE_GEGLU) kernel = tile_gemm_kernel<B200_EPILOGUE_GEGLU>;
+    if (epilogue == B200_EPILOGUE_GEGLU_ERF) kernel = tile_gemm_kernel<B200_EPILOGUE_GEGLU_ERF>;
+    B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem_bytes)));
+    // the number of tiles is only known on the device: one persistent CTA per SM
+    B200_CHECK_CUDA(launch_kernel(kernel, dim3(sm_count()), dim3(kThreads), smem_bytes, stream, dim3(1, 1, 1),
                                   tmap_x, tmap_w, p));
     return B200_OK;
 }

@@ -38,6 +38,10 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t out
 int launch_tile_gemm(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                      int64_t ldx, int epilogue, int* status, cudaStream_t stream);
 
+int launch_grouped_tile_gemm(void* y, const void* x, const void* w, const int32_t* counts,
+                             const int32_t* offsets, int num_groups, int64_t total_rows, int N, int K,
+                             int epilogue, int* status, cudaStream_t stream);
+
 // y[M, n_out] = x[M, K] w[N, K]^T (+bias / gated epilogue); any M (slabs of 256 rows).
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
                   int64_t ldx, int epilogue, int* status, cudaStream_t stream);

@@ -42,7 +42,9 @@ def test_route_matches_torch_topk(L, T, E, k, renorm):
     (64, 16, 4, 256, 128, True, "silu"),
     (256, 128, 8, 2048, 768, True, "silu"),     # Qwen3-30B-A3B decode step at batch 256
     (40, 8, 2, 128, 192, False, "gelu"),
-    (300, 4, 2, 128, 64, True, "silu"),         # more than 256 rows for one expert
+    (300, 4, 2, 128, 64, True, "silu"),         # 150 rows per expert: the tile kernel's grouped mode
+    (2048, 16, 4, 256, 128, True, "silu"),      # a prefill batch: ~512 rows per expert, ragged
+    (1500, 6, 3, 128, 192, False, "gelu"),      # tile kernel, exact-GELU epilogue, k-loop of 3
     (1, 8, 8, 64, 64, True, "silu"),
 ])
 def test_moe_forward_matches_oracle(L, T, E, k, H, I, renorm, act):
@@ -60,7 +62,8 @@ def test_moe_forward_matches_oracle(L, T, E, k, H, I, renorm, act):
     assert L.read_device_status() == (0, 0)
 
 
-@pytest.mark.parametrize("T,E,k,H,I,parts", [(64, 16, 4, 256, 128, 4), (256, 128, 8, 2048, 768, 8), (5, 8, 2, 64, 64, 2)])
+@pytest.mark.parametrize("T,E,k,H,I,parts", [(64, 16, 4, 256, 128, 4), (256, 128, 8, 2048, 768, 8), (5, 8, 2, 64, 64, 2),
+                                             (900, 8, 2, 128, 64, 2)])   # tile kernel on a rank's experts
 def test_moe_expert_partition_matches_oracle_share(L, T, E, k, H, I, parts):
     """Expert parallelism: a rank holding experts [b, b + E/parts) returns exactly the oracle's
     share for that range, rows whose experts all live elsewhere come back zero, and the shares
