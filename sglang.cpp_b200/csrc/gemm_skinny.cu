@@ -80,7 +80,7 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f +
 // bodies (erff and tanhf are long) in the epilogue of every gated GEMM.
 template <int EPI>
 __device__ __forceinline__ float gated_act(float g) {
-    if (EPI == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
+    if (EPI == B200_EPILOGUE_SWIGLU) return __fdividef(g, 1.0f + __expf(-g));  // 2 ulp in fp32, far below the bf16 step
     if (EPI == B200_EPILOGUE_GEGLU_ERF) return gelu_erf_f(g);
     return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
 }

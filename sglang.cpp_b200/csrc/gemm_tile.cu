@@ -58,7 +58,7 @@ struct TileAt {
 
 template <int EPI>
 __device__ __forceinline__ float gated_act_tile(float g) {
-    if (EPI == B200_EPILOGUE_SWIGLU) return g / (1.0f + __expf(-g));
+    if (EPI == B200_EPILOGUE_SWIGLU) return __fdividef(g, 1.0f + __expf(-g));  // 2 ulp in fp32, far below the bf16 step
     if (EPI == B200_EPILOGUE_GEGLU_ERF) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
     return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
 }
