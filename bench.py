@@ -330,7 +330,7 @@ def run_gpu(args):
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
+        line["cpu_baseline"] = cpu_baseline(seconds_budget=12.0)
     engine.close()
     if dist is not None:
         dist.barrier()
@@ -484,7 +484,7 @@ def run_gpu_tp(args):
 CPU_SAMPLE_REQS = 8
 
 
-def cpu_decode_sample(steps: int, warmup: int):
+def cpu_decode_sample(steps: int, warmup: int, seconds_budget: float = 0.0):
     """Times the CPU oracle (a port: the reference has no CPU forward) on a bounded sample of the
     workload: the first CPU_SAMPLE_REQS requests of the batch at their real context lengths, KV
     contents random (the cost does not depend on the values), `steps` decode steps."""
@@ -519,16 +519,18 @@ def cpu_decode_sample(steps: int, warmup: int):
         tok = logits.argmax(-1).numpy().astype(np.int32)
         if s >= warmup:
             times.append(time.perf_counter() - t0)
+            if seconds_budget and len(times) >= 2 and sum(times) >= seconds_budget:
+                break   # the sample is bounded by time: at most `steps` steps, about `seconds_budget` seconds
     return times, torch.get_num_threads()
 
 
 def cpu_baseline(seconds_budget: float):
-    times, cores = cpu_decode_sample(steps=2, warmup=1)
+    times, cores = cpu_decode_sample(steps=64, warmup=1, seconds_budget=seconds_budget)
     per_step = statistics.mean(times)
     return {"value": round(CPU_SAMPLE_REQS / per_step, 2), "unit": "tokens/s", "cores": cores,
             "kind": "port",
             "sample": f"CPU oracle (torch fp32 restatement; the reference has no CPU forward), first "
-                      f"{CPU_SAMPLE_REQS} of the 64 requests at their real contexts, 2 decode steps after 1 warm-up, "
+                      f"{CPU_SAMPLE_REQS} of the 64 requests at their real contexts, {len(times)} decode steps after 1 warm-up, "
                       f"{per_step * 1e3:.0f} ms per step"}
 
 
@@ -536,7 +538,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 8))
+    steps = max(1, min(args.steps, 64))   # each step is a bounded sample (8 of the 64 requests): ~0.2 s
     warmup = max(1, min(args.warmup, 2))
     times, cores = cpu_decode_sample(steps, warmup)
     total = sum(times)
