@@ -562,6 +562,11 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt_max * kBlockK * 2;
     const uint32_t smem_limit = 200 * 1024;
     int stages = kb_total < kMaxStages ? kb_total : kMaxStages;
+    // Many more CTAs than SMs (every expert active): keep the ring small enough for two CTAs per
+    // SM, so one CTA's start-up and epilogue overlap the other's streaming.
+    const int ring_cap_kb = env_int("B200_GROUPED_RING_KB", 100);
+    if (static_cast<int64_t>(n_tiles) * num_groups > 2 * sm_count())
+        while (stages > 2 && stages * stage_bytes > static_cast<uint32_t>(ring_cap_kb) * 1024u) --stages;
     while (stages > 1 && stages * stage_bytes > smem_limit) --stages;
     const uint32_t smem_bytes = stages * stage_bytes + 1024;
 
