@@ -169,8 +169,6 @@ def run_gpu(args):
     num_pages = sum(math.ceil((len(p) + total_new + 1) / PAGE_SIZE) for p in prompts) + 8
     engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, BATCH, max_len, MAX_EXTEND_TOKENS))
     engine.load_weights(O.init_weights(cfg, seed=0, std=0.02))
-    cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
-    engine.load_rope_tables(cos, sin)
     hb = HostBatcher(engine, num_pages, PAGE_SIZE, BATCH)
 
     # ---- prefill through the engine, in scheduler-sized batches; prefixes are cached as they finish

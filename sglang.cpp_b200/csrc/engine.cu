@@ -217,20 +217,22 @@ int named_alloc(b200_engine* e, T** out, const std::string& name, int64_t elems,
     } while (0)
 
 int build_rope_tables(b200_engine* e) {
-    // cos/sin [max_position, head_dim / 2] in fp32.  Computed here in double and
-    // rounded once; a caller that needs the bit pattern of another generator (the
-    // reference builds them with fp32 torch ops) overwrites "rope_cos"/"rope_sin".
+    // cos/sin [max_position, head_dim / 2] in fp32, with the reference's sequence of fp32
+    // operations (src/layers/rotary_embedding.cu:80-93): inv_freq = 1 / base^(2j / d),
+    // freq = t * inv_freq, cos(freq), sin(freq), every step rounded to fp32.  The reference runs
+    // these steps as torch CPU ops, whose vectorised pow / cos / sin differ from libm's in the last
+    // bit of some entries; a host that needs torch's exact bit pattern loads its own tables over
+    // "rope_cos" / "rope_sin" (b200_engine_load).
     const int half = e->m.head_dim / 2;
     const int64_t n = static_cast<int64_t>(e->m.max_position) * half;
-    std::vector<float> c(n), s(n);
-    std::vector<double> inv(half);
-    for (int j = 0; j < half; ++j)
-        inv[j] = 1.0 / pow(static_cast<double>(e->m.rope_theta), static_cast<double>(2 * j) / e->m.head_dim);
+    std::vector<float> c(n), s(n), inv(half);
+    const float base = e->m.rope_theta, dim = static_cast<float>(e->m.head_dim);
+    for (int j = 0; j < half; ++j) inv[j] = 1.0f / powf(base, static_cast<float>(2 * j) / dim);
     for (int64_t t = 0; t < e->m.max_position; ++t)
         for (int j = 0; j < half; ++j) {
-            const double f = static_cast<double>(t) * inv[j];
-            c[t * half + j] = static_cast<float>(cos(f));
-            s[t * half + j] = static_cast<float>(sin(f));
+            const float f = static_cast<float>(t) * inv[j];
+            c[t * half + j] = cosf(f);
+            s[t * half + j] = sinf(f);
         }
     B200_CHECK_CUDA(cudaMemcpy(e->rope_cos, c.data(), n * sizeof(float), cudaMemcpyHostToDevice));
     B200_CHECK_CUDA(cudaMemcpy(e->rope_sin, s.data(), n * sizeof(float), cudaMemcpyHostToDevice));

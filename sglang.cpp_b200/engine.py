@@ -73,6 +73,7 @@ class Engine:
         self._next_tokens_cpu = torch.empty(config.max_running_req + 1, dtype=torch.int32).pin_memory()
         self.page_size = config.page_size
         self.dummy_table_idx = config.max_running_req
+        self.pt_cols = (config.max_seq_len + 31) // 32 * 32   # page-table row length (src/engine/engine.cc:452-459)
         self._step_index = 0
 
     def close(self) -> None:

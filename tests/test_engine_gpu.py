@@ -43,8 +43,6 @@ class Pair:
         self.w = O.init_weights(cfg, seed=seed, std=0.02)
         self.engine = Engine(cfg, EngineConfig(page_size, num_pages, max_running_req, 512, 1024))
         self.engine.load_weights(self.w)
-        cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
-        self.engine.load_rope_tables(cos, sin)
         self.hb = HostBatcher(self.engine, num_pages, page_size, max_running_req)
         self.oracle = O.OracleModel(cfg, self.w, store)
         self.kv = O.KVState.create(cfg, (num_pages + 1) * page_size)
@@ -180,19 +178,39 @@ def test_prefix_cache_hit_reuses_pages_and_gives_same_logits(pkg):
     pr.hb.cache_prefix(ra)
     rb = pr.hb.add_request(b, 2)
     assert rb.cached_len == 48                       # three 16-token pages matched
-    assert pr.hb.slots_of(rb)[:48] == pr.hb.slots_of(ra)[:48]
+    assert np.array_equal(pr.hb.slots_of(rb)[:48], pr.hb.slots_of(ra)[:48])
     pr.hb.prefill([rb]).synchronize()
     with_hit = pr.engine.logits(1).clone()
     pr.engine.close()
     # the same request on a fresh engine without the cache
     pr2 = Pair(pkg, cfg, 16)
-    pr2.hb.enable_prefix_cache = False
+    pr2.hb.cache_manager.enabled = False
     rb2 = pr2.hb.add_request(b, 2)
     pr2.hb.prefill([rb2]).synchronize()
     cold = pr2.engine.logits(1)
     d = (with_hit.float() - cold.float()).abs()
     assert float(d.max()) <= MAX_ABS
     pr2.engine.close()
+
+
+def test_engine_builds_the_rope_tables_with_the_reference_fp32_steps(pkg):
+    """The step runner's own table builder (what a C++ host gets; nothing loads tables into the
+    engine in these tests or in the benchmark) follows the reference's fp32 sequence
+    (src/layers/rotary_embedding.cu:80-93).  The reference runs it as torch CPU ops, whose vectorised
+    pow / cos / sin and libm's differ in the last bit of some results: one inv_freq entry of 64 is
+    an ulp apart for theta 1e6, which grows to 2e-6 at position 40959.  Tolerance: 4e-6 absolute,
+    and more than 90 % of the entries bit-equal."""
+    for cfg in (O.qwen3_0_6b(), O.llama3_8b()):
+        small = O.ModelConfig(**{**cfg.__dict__, "num_layers": 1, "vocab_size": 256, "intermediate_size": 256,
+                                 "hidden_size": 256, "num_qo_heads": 2, "num_kv_heads": 1})
+        from sglang_cpp_b200.engine import Engine, EngineConfig
+        eng = Engine(small, EngineConfig(16, 8, 2, 64, 64))
+        want_c, want_s = O.rope_tables(small.head_dim, small.max_position, small.rope_theta)
+        for name, want in (("rope_cos", want_c), ("rope_sin", want_s)):
+            got = eng.device_view(name).view(torch.float32).cpu().view_as(want)
+            assert float((got - want).abs().max()) <= 4e-6, name
+            assert float((got == want).float().mean()) > 0.9, name
+        eng.close()
 
 
 def test_step_rejects_bad_batches(pkg):
@@ -224,8 +242,6 @@ def test_config1_full_size_greedy_32_steps(pkg):
     w = O.init_weights(cfg, seed=0, std=0.02)
     engine = Engine(cfg, EngineConfig(1, 128, 1, 128, 128))
     engine.load_weights(w)
-    cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
-    engine.load_rope_tables(cos, sin)
     hb = HostBatcher(engine, 128, 1, 1)
     oracle = O.OracleModel(cfg, w, O.store_bf16)
     kv = O.KVState.create(cfg, 129)

@@ -97,8 +97,6 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     w = O.init_weights(cfg, seed=0, std=0.02, router_std=1.0 if ep else None)
     eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world, ep))
     eng.load_weights(w, rank, world)
-    cos, sin = O.rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
-    eng.load_rope_tables(cos, sin)
     eng.connect_tp()
     hb = HostBatcher(eng, 32, 16, 4, enable_prefix_cache=False)
     rng = np.random.default_rng(0)
