@@ -15,6 +15,12 @@ from pinned memory and the sampled tokens are copied device-to-host and waited f
 --gpus N > 1 (launched under torchrun) every rank runs an independent replica of the workload
 (the 0.6B model does not shard); the job's time is the max over ranks.
 
+The K timed steps are repeated from the same state (re-warmed each time) until at least a second
+has been timed, and the median repeat is reported, so that the clock samples taken beside it mean
+something.  After the headline the same ranks run workload "c4" (Llama-3-8B, tensor parallel over
+all N ranks, the fused all-reduce kernels on the data path) and attach it as the `tp` key: that is
+the part of the path that shards, and the replicas of the headline cannot show it.
+
 Other workloads (not the headline metric): --context N gives every prompt N tokens (the
 "batch 64 / 2048-token context" point); --workload c4 is Llama-3-8B under tensor parallelism and
 --workload c5 Qwen3-30B-A3B under expert parallelism + attention TP over the N ranks (strong
@@ -41,6 +47,7 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+METRIC = "decode tokens/s at bs=64 (Qwen3-0.6B, ctx 512-2048 + generated, page 16)"
 PAGE_SIZE = 16
 BATCH = 64
 PROMPT_LO, PROMPT_HI = 512, 2048
@@ -54,6 +61,30 @@ def measured_peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def dram_traffic_ratio(kernel: str):
+    """DRAM bytes per algorithmic byte of a kernel, from the table of ncu captures kept in
+    profiles/dram_traffic_ratios.md (None when the kernel has no row)."""
+    p = ROOT / "profiles" / "dram_traffic_ratios.md"
+    if not p.exists():
+        return None
+    for line in p.read_text().splitlines():
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) >= 4 and cells[0] == kernel:
+            try:
+                return float(cells[3])
+            except ValueError:
+                return None
+    return None
+
+
+def workload_config(world: int, context: int = 0):
+    """The `config` object of the JSON line: the same for this arm and for --impl reference."""
+    return {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts %s seed 2, 256-token shared prefix per 4 "
+                        "requests, page size 16, greedy" % ("of %d tokens" % context if context else "U[512,2048]"),
+            "l2": "inputs larger than L2: every step streams about 10 GB of K/V and 1.19 GB of weights",
+            "parallelism": "replicas" if world > 1 else "single GPU"}
 
 
 def make_prompts(vocab: int, fixed_len: int = 0):
@@ -222,46 +253,67 @@ def run_gpu(args):
     sampler = ClockSampler(local_rank)
 
     # ---- phase A: device-timed, steps enqueued back to back ----
-    reset()
-    for _ in range(W):
-        hb.decode(reqs)
-    barrier()
-    ctx_a = [r.device_len for r in reqs]
+    # The K steps are repeated from the same state until at least a second has been timed; every
+    # repeat is re-warmed with W steps and bracketed by barrier + synchronize on both sides.
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if args.profile_region:
-        torch.cuda.profiler.start()
-    ev0.record(stream)
-    for _ in range(K):
-        hb.decode(reqs)
-    ev1.record(stream)
-    barrier()
-    if args.profile_region:
-        torch.cuda.profiler.stop()
-    dev_ms = ev0.elapsed_time(ev1)
-    _, _, launches_per_step = engine.read_profile()
+    dev_ms_all, ctx_a, launches_per_step = [], None, 0
+    while True:
+        reset()
+        for _ in range(W):
+            hb.decode(reqs)
+        barrier()
+        ctx_a = [r.device_len for r in reqs]
+        if args.profile_region and not dev_ms_all:
+            torch.cuda.profiler.start()
+        ev0.record(stream)
+        for _ in range(K):
+            hb.decode(reqs)
+        ev1.record(stream)
+        barrier()
+        if args.profile_region and not dev_ms_all:
+            torch.cuda.profiler.stop()
+        ms = ev0.elapsed_time(ev1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)   # the job's time is the slowest rank's
+            ms = float(t[0])
+        dev_ms_all.append(ms)
+        _, _, launches_per_step = engine.read_profile()
+        if sum(dev_ms_all) >= args.min_timed_ms or len(dev_ms_all) >= 64 or args.profile_region:
+            break
+    dev_ms = statistics.median(dev_ms_all)
 
     # ---- phase B: end to end, the host waits for every step's tokens ----
     # Driven the way the scheduler's decode loop drives the engine: per step the host arrays cross
     # the C ABI, the metadata goes host-to-device from pinned memory, the tokens come back and are
     # waited for.  (DecodeSession keeps the per-step host bookkeeping in vector form.)
     from sglang_cpp_b200.host_batch import DecodeSession
-    reset()
-    for _ in range(W):
-        hb.decode(reqs).synchronize()
-    barrier()
-    session = DecodeSession(hb, reqs)
-    step_ms = []
-    t0 = time.perf_counter()
-    for _ in range(K):
-        ts = time.perf_counter()
-        toks = session.step()
-        engine.synchronize()
-        _ = toks[0].item()
-        step_ms.append((time.perf_counter() - ts) * 1e3)
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    session.sync_back()
+    e2e_ms_all, step_ms = [], []
+    while True:
+        reset()
+        for _ in range(W):
+            hb.decode(reqs).synchronize()
+        barrier()
+        session = DecodeSession(hb, reqs)
+        t0 = time.perf_counter()
+        for _ in range(K):
+            ts = time.perf_counter()
+            toks = session.step()
+            engine.synchronize()
+            _ = toks[0].item()
+            step_ms.append((time.perf_counter() - ts) * 1e3)
+        barrier()
+        ms = (time.perf_counter() - t0) * 1e3
+        session.sync_back()
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        e2e_ms_all.append(ms)
+        if sum(e2e_ms_all) >= args.min_timed_ms or len(e2e_ms_all) >= 64:
+            break
+    e2e_ms = statistics.median(e2e_ms_all)
     clocks = sampler.stop()
 
     # ---- phase C: attention launches timed one by one (eager steps, event pair per launch) ----
@@ -279,11 +331,6 @@ def run_gpu(args):
         attn_n += n
     engine.set_profiling(False)
 
-    if dist is not None:
-        t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
-
     peak, peak_kind = measured_peaks()
     mean_ctx = [c + (K - 1) / 2 for c in ctx_a]  # context grows by one per step
     step_bytes, _ = algorithmic_bytes(cfg, mean_ctx)
@@ -292,31 +339,31 @@ def run_gpu(args):
     attn_gbs = kv_layer_bytes / (attn_launch_ms * 1e-3) / 1e9 if attn_launch_ms > 0 else 0.0
     value = world * BATCH * K / (dev_ms * 1e-3)
     e2e_value = world * BATCH * K / (e2e_ms * 1e-3)
+    ratio = dram_traffic_ratio("attention_decode_kernel")
     line = {
-        "metric": "decode tokens/s at bs=64 (Qwen3-0.6B, ctx 512-2048 + generated, page 16)",
+        "metric": METRIC,
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts %s seed 2, "
-                               "256-token shared prefix per 4 requests, page size 16, greedy"
-                               % ("of %d tokens" % args.context if args.context else "U[512,2048]"),
-                   "l2": "inputs larger than L2: each step streams ~%.1f GB of KV and 1.19 GB of weights"
-                         % (sum(mean_ctx) * 114688 / 1e9),
-                   "parallelism": "replicas" if world > 1 else "single GPU",
-                   "mean_context": round(statistics.mean(mean_ctx), 1),
-                   "prefix_cache_hit_tokens": hb.prefix_hits},
+        "config": workload_config(world, args.context),
+        "workload_stats": {"mean_context": round(statistics.mean(mean_ctx), 1),
+                           "kv_gb_per_step": round(sum(mean_ctx) * 114688 / 1e9, 2),
+                           "prefix_cache_hit_tokens": hb.prefix_hits,
+                           "timed_repeats": len(dev_ms_all), "timed_ms_total": round(sum(dev_ms_all), 1),
+                           "repeat_ms_min_max": [round(min(dev_ms_all), 3), round(max(dev_ms_all), 3)]},
         "p50_tpot_ms": round(statistics.median(step_ms), 4),
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": (4 * BATCH + 1) * 4, "d2h_bytes_per_step": BATCH * 4,
-                "ms_per_step": round(e2e_ms / K, 4)},
+                "ms_per_step": round(e2e_ms / K, 4), "timed_repeats": len(e2e_ms_all)},
         "gpu_launches": int(launches_per_step) * K,
         "roofline": {"bound": "hbm", "kernel": "attention_decode_kernel",
                      "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(attn_gbs / peak, 4), "peak_kind": peak_kind + " (copy bandwidth)",
-                     # DRAM bytes per launch: the ncu capture of this kernel on the batch-64 parity case
-                     # (profiles/attention_decode_kernel_batch64.md) moved 394.5 MB for 383.8 MB of K/V;
-                     # traffic grows with the sum of contexts, so that ratio is applied to this launch
-                     "traffic": int(kv_layer_bytes * 394.5 / 383.8), "traffic_source": "ncu capture of a smaller case, scaled by bytes of K/V",
+                     # DRAM bytes per launch: the ratio of DRAM traffic to algorithmic bytes that ncu measured
+                     # for this kernel on a smaller case (traffic grows with the sum of contexts), from
+                     # profiles/dram_traffic_ratios.md, applied to this launch's algorithmic bytes
+                     "traffic": int(kv_layer_bytes * ratio) if ratio else None,
+                     "traffic_source": "profiles/dram_traffic_ratios.md (ncu capture of a smaller case, scaled by bytes of K/V)",
                      "launch_ms": round(attn_launch_ms, 5),
                      "algorithmic_bytes_per_launch": int(kv_layer_bytes), "launches_timed": attn_n},
         "step_roofline": {"algorithmic_bytes_per_step": int(step_bytes),
@@ -327,9 +374,17 @@ def run_gpu(args):
                     "tokens_per_s": round(prefill_tokens / prefill_s, 1)},
         "clocks": clocks,
     }
+    engine.close()
+    del engine, hb, reqs
+    torch.cuda.empty_cache()
+    if not args.no_tp_record and not args.context and not args.profile_region and not args.eager:
+        # the part of the path that shards: Llama-3-8B, tensor parallel over the same ranks
+        try:
+            line["tp"] = run_gpu_tp(args, dist_ready=dist is not None, as_record=True)
+        except Exception as e:   # the headline stands on its own
+            line["tp"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(seconds_budget=12.0)
-    engine.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -338,7 +393,7 @@ def run_gpu(args):
 
 
 # ------------------------------------------------------------------------------- TP workload
-def run_gpu_tp(args):
+def run_gpu_tp(args, dist_ready=False, as_record=False):
     """Workload "c4": Llama-3-8B architecture, bf16, random-init weights drawn on the device,
     tensor parallel over all ranks (heads and MLP columns split, the post-projection all-reduce
     fused with add + norm over NVLink peer memory), batch 128, prompts of 1024 uniform-random
@@ -351,7 +406,7 @@ def run_gpu_tp(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    if world > 1:
+    if world > 1 and not dist_ready:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg = entry.load_package()
@@ -359,7 +414,7 @@ def run_gpu_tp(args):
     from sglang_cpp_b200.engine import Engine, EngineConfig
     from sglang_cpp_b200.host_batch import HostBatcher
 
-    moe = args.workload == "c5"
+    moe = args.workload == "c5" and not as_record
     cfg = O.qwen3_30b_a3b() if moe else O.llama3_8b()
     B, PROMPT = (256, 512) if moe else (128, 1024)
     K, W = args.steps, args.warmup
@@ -471,6 +526,17 @@ def run_gpu_tp(args):
         "clocks": clocks,
     }
     engine.close()
+    if as_record:
+        # attached to the headline line: the sharded path on the same ranks.  Speed-up over one GPU is
+        # this `ms_per_step` against the `tp.ms_per_step` of the N = 1 run of the same command.
+        return {"workload": line["config"]["workload"], "parallelism": line["config"]["parallelism"],
+                "scaling": "strong", "steps": K, "warmup": W, "ms_per_step": line["ms_per_step"],
+                "tokens_per_s": line["value"], "ranks_in_lockstep": lockstep,
+                "frac_of_measured_hbm_per_gpu": line["step_roofline"]["frac_of_measured_hbm"],
+                "attention_us_per_launch": line["kernels"]["attention_us_per_launch"],
+                "allreduce_us_per_launch": line["kernels"]["allreduce_us_per_launch"],
+                "allreduce_launches_per_step": line["kernels"]["allreduce_launches_per_step"],
+                "data_path": "allreduce kernels of csrc/allreduce.cu over CUDA-IPC peer memory; NCCL only for the rendezvous"}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -479,29 +545,33 @@ def run_gpu_tp(args):
 
 
 # ------------------------------------------------------------------------------- CPU side
-CPU_SAMPLE_REQS = 8
-
-
-def cpu_decode_sample(steps: int, warmup: int, seconds_budget: float = 0.0):
-    """Times the CPU oracle (a port: the reference has no CPU forward) on a bounded sample of the
-    workload: the first CPU_SAMPLE_REQS requests of the batch at their real context lengths, KV
-    contents random (the cost does not depend on the values), `steps` decode steps."""
+def cpu_decode_sample(steps: int, warmup: int, seconds_budget: float = 0.0, num_reqs: int = BATCH):
+    """Times the CPU oracle (a port: the reference has no CPU forward) on decode steps of the
+    workload's batch: `num_reqs` requests (all 64 unless host memory is short) at their real context
+    lengths.  The K/V contents are whatever the allocation holds (the cost does not depend on the
+    values) and are kept in bf16, as the GPU pool keeps them."""
     from oracle import token_loop_oracle as O
 
     cfg = O.qwen3_0_6b()
     torch.set_num_threads(os.cpu_count() or 1)
+    prompts = make_prompts(cfg.vocab_size)[:num_reqs]
+    lens = np.array([len(p) for p in prompts], dtype=np.int32)
+    n_slots = int(lens.sum()) + (steps + warmup + 1) * num_reqs
+    kv_bytes = 2 * cfg.num_layers * n_slots * cfg.num_kv_heads * cfg.head_dim * 2
+    try:
+        import psutil
+        if kv_bytes + (8 << 30) > psutil.virtual_memory().available and num_reqs > 8:
+            return cpu_decode_sample(steps, warmup, seconds_budget, max(8, num_reqs // 2))
+    except ImportError:
+        pass
     w = O.init_weights(cfg, seed=0, std=0.02)
     model = O.OracleModel(cfg, w, O.store_bf16)
-    prompts = make_prompts(cfg.vocab_size)[:CPU_SAMPLE_REQS]
-    lens = np.array([len(p) for p in prompts], dtype=np.int32)
-    n_slots = int(lens.sum()) + (steps + warmup + 1) * CPU_SAMPLE_REQS
-    gen = torch.Generator().manual_seed(0)
-    kv = O.KVState(torch.randn(cfg.num_layers, n_slots, cfg.num_kv_heads, cfg.head_dim, generator=gen),
-                   torch.randn(cfg.num_layers, n_slots, cfg.num_kv_heads, cfg.head_dim, generator=gen))
+    shape = (cfg.num_layers, n_slots, cfg.num_kv_heads, cfg.head_dim)
+    kv = O.KVState(torch.zeros(shape, dtype=torch.bfloat16), torch.zeros(shape, dtype=torch.bfloat16))
     cols = int(lens.max()) + steps + warmup + 2
-    pt = np.zeros((CPU_SAMPLE_REQS, cols), dtype=np.int32)
+    pt = np.zeros((num_reqs, cols), dtype=np.int32)
     cur = 0
-    for b in range(CPU_SAMPLE_REQS):
+    for b in range(num_reqs):
         n = int(lens[b]) + steps + warmup + 1
         pt[b, :n] = np.arange(cur, cur + n)
         cur += n
@@ -509,9 +579,9 @@ def cpu_decode_sample(steps: int, warmup: int, seconds_budget: float = 0.0):
     times = []
     for s in range(warmup + steps):
         pos = lens + s
-        batch = O.StepBatch(tok, pos.astype(np.int32), pt[np.arange(CPU_SAMPLE_REQS), pos].copy(),
-                            np.arange(CPU_SAMPLE_REQS, dtype=np.int32), (pos + 1).astype(np.int32),
-                            np.arange(CPU_SAMPLE_REQS + 1, dtype=np.int32), False)
+        batch = O.StepBatch(tok, pos.astype(np.int32), pt[np.arange(num_reqs), pos].copy(),
+                            np.arange(num_reqs, dtype=np.int32), (pos + 1).astype(np.int32),
+                            np.arange(num_reqs + 1, dtype=np.int32), False)
         t0 = time.perf_counter()
         logits = model.forward(batch, kv, pt)
         tok = logits.argmax(-1).numpy().astype(np.int32)
@@ -519,16 +589,16 @@ def cpu_decode_sample(steps: int, warmup: int, seconds_budget: float = 0.0):
             times.append(time.perf_counter() - t0)
             if seconds_budget and len(times) >= 2 and sum(times) >= seconds_budget:
                 break   # the sample is bounded by time: at most `steps` steps, about `seconds_budget` seconds
-    return times, torch.get_num_threads()
+    return times, torch.get_num_threads(), num_reqs
 
 
 def cpu_baseline(seconds_budget: float):
-    times, cores = cpu_decode_sample(steps=64, warmup=1, seconds_budget=seconds_budget)
+    times, cores, n = cpu_decode_sample(steps=16, warmup=1, seconds_budget=seconds_budget)
     per_step = statistics.mean(times)
-    return {"value": round(CPU_SAMPLE_REQS / per_step, 2), "unit": "tokens/s", "cores": cores,
+    return {"value": round(n / per_step, 2), "unit": "tokens/s", "cores": cores,
             "kind": "port",
-            "sample": f"CPU oracle (torch fp32 restatement; the reference has no CPU forward), first "
-                      f"{CPU_SAMPLE_REQS} of the 64 requests at their real contexts, {len(times)} decode steps after 1 warm-up, "
+            "sample": f"CPU oracle (torch fp32 restatement; the reference has no CPU forward), decode steps of "
+                      f"{n} of the 64 requests at their real contexts, {len(times)} steps after 1 warm-up, "
                       f"{per_step * 1e3:.0f} ms per step"}
 
 
@@ -536,23 +606,22 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 64))   # each step is a bounded sample (8 of the 64 requests): ~0.2 s
-    warmup = max(1, min(args.warmup, 2))
-    times, cores = cpu_decode_sample(steps, warmup)
+    steps = max(1, min(args.steps, 32))   # one step of the whole batch takes a second or two on the host cores
+    warmup = max(1, min(args.warmup, 8))
+    times, cores, n = cpu_decode_sample(steps, warmup)
     total = sum(times)
-    value = CPU_SAMPLE_REQS * len(times) / total
+    value = n * len(times) / total
     line = {
         "impl": "reference",
-        "metric": "decode tokens/s at bs=64 (Qwen3-0.6B, ctx 512-2048 + generated, page 16)",
+        "metric": METRIC,
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(times), "warmup": warmup,
         "ms_per_step": round(total / len(times) * 1e3, 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "c2: Qwen3-0.6B decode, batch 64, prompts U[512,2048] seed 2, "
-                               "256-token shared prefix per 4 requests, page size 16, greedy"},
+        "config": workload_config(args.gpus),
         "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"CPU oracle, each step = one decode step of the first {CPU_SAMPLE_REQS} of the 64 "
-                                   f"requests at their real contexts (random KV contents); the reference's own dense "
-                                   f"forward is CUDA-only, so this is a port"},
+                         "sample": f"CPU oracle, each step = one decode step of {n} of the 64 requests at their real "
+                                   f"contexts (K/V contents arbitrary); the reference's own dense forward is CUDA-only, "
+                                   f"so this is a port"},
         "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -571,6 +640,10 @@ def main():
     ap.add_argument("--context", type=int, default=0,
                     help="c2 only: give every prompt this length instead of U[512,2048]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-record", action="store_true",
+                    help="c2 only: do not run the tensor-parallel workload after the headline")
+    ap.add_argument("--min-timed-ms", type=float, default=1000.0,
+                    help="repeat the K timed steps until this much time has been timed; the median repeat is reported")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="c2 only: bracket the second prefill batch with cudaProfilerStart/Stop")
     ap.add_argument("--eager", action="store_true",

@@ -237,7 +237,9 @@ B200_API int b200_attention_decode(void* out, const void* q, int64_t q_stride_to
  * array's device address (cudaGetSymbolAddress) with that device current; make that first call
  * before any stream capture begins.  All calls share the one array and it keeps the previous
  * call's contents (the call clears the words that must start at zero): two calls whose kernels
- * overlap on the GPU race. */
+ * overlap on the GPU race.  What the kernel reports (a wait that ran out, a page-table slot out of
+ * range) goes to two words inside the same array, NOT to the words b200_read_device_status reads:
+ * read them with b200_attention_decode_noalloc_status. */
 B200_API int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_token,
                                            int64_t q_stride_head, const void* k_cache,
                                            const void* v_cache, int64_t num_slots,
@@ -245,6 +247,13 @@ B200_API int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_s
                                            const int32_t* table_idx, const int32_t* seq_lens,
                                            int batch, int q_heads, int kv_heads, int head_dim,
                                            int page_size, float sm_scale, b200_stream_t stream);
+
+/* No counterpart in the reference.  Reads what the kernels of b200_attention_decode_noalloc reported
+ * on the current device since the last read, after synchronising `stream`: out[0] = site of a wait
+ * that ran out (0 = none), out[1] = offending slot + 1 of a page-table entry outside the pool (0 =
+ * none; the kernel read slot 0 instead, nothing faulted).  Non-zero words are cleared by the read, so
+ * a report survives later calls until somebody looks.  Allocates nothing. */
+B200_API int b200_attention_decode_noalloc_status(int32_t out[2], b200_stream_t stream);
 
 /* FlashInferBackend::forward for a prefill (extend) batch
  * (src/attention/flashinfer_backend.cu:596-678): causal attention of ragged
@@ -298,6 +307,18 @@ B200_API int b200_comm_connect(b200_comm* comm, const void* all_handles);
  * partial sum (the row-parallel GEMM) writes there. */
 B200_API void* b200_comm_buffer(b200_comm* comm, int parity);
 B200_API int b200_comm_destroy(b200_comm* comm);
+/* The longest one kernel waits for its peers' announcement before it gives up, leaves its outputs
+ * untouched and reports through the device status words (sites 401-403).  Default 2 s; the
+ * reference's only time-out is the NCCL rendezvous (src/distributed/distributed.cc:106-120,145). */
+B200_API int b200_comm_set_wait_limit_ns(b200_comm* comm, uint64_t nanoseconds);
+/* Failure-path testing on ONE GPU, no counterpart in the reference: instead of b200_comm_connect,
+ * map every peer onto this rank's own buffers.  A peer's announcement then never arrives by
+ * itself, so a call runs into the wait limit and returns — unless the host plays the peers' part
+ * first with b200_comm_loopback_announce(call_number), call numbers counting from 1 per
+ * communicator (failed calls count too).  The all-reduce of such a communicator returns
+ * world x this rank's partial. */
+B200_API int b200_comm_connect_loopback(b200_comm* comm);
+B200_API int b200_comm_loopback_announce(b200_comm* comm, uint32_t call_number, b200_stream_t stream);
 
 /* tensor_model_parallel_all_reduce (src/distributed/distributed.cc:205-226): out[rows, hidden]
  * = bf16(sum over ranks, in rank order, fp32) of the partials in the exchange buffers of
@@ -417,6 +438,9 @@ B200_API int b200_engine_read_logits(b200_engine* engine, void* host, int rows);
  * (b200_comm_handle_bytes bytes) and connect to all ranks' handles before the first step. */
 B200_API int b200_engine_comm_export(b200_engine* engine, void* handle_out);
 B200_API int b200_engine_comm_connect(b200_engine* engine, const void* all_handles);
+/* The engine's communicator, for b200_comm_set_wait_limit_ns and the loop-back test hooks
+ * (NULL when the engine was created with tp_size 1). */
+B200_API b200_comm* b200_engine_comm(b200_engine* engine);
 
 /* The stream the engine enqueues on (Engine::stream_), as a cudaStream_t. */
 B200_API b200_stream_t b200_engine_stream(b200_engine* engine);

@@ -367,6 +367,10 @@ class OracleModel:
         self.store = store
         self.cos, self.sin = rope_tables(cfg.head_dim, cfg.max_position, cfg.rope_theta)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        # Set to a list to record, per decoder layer of the fused-residual wiring, the tensors that
+        # enter it (x, residual) and leave it (x, residual): the per-layer parity test feeds the
+        # former to the CUDA operators and compares with the latter.
+        self.layer_trace: Optional[list] = None
 
     def _attn(self, L, li: int, x, batch: StepBatch, kv: KVState, page_table: np.ndarray):
         cfg, st = self.cfg, self.store
@@ -383,8 +387,8 @@ class OracleModel:
         q = rope_neox(q, pos, self.cos, self.sin, store=st)
         k = rope_neox(k, pos, self.cos, self.sin, store=st)
         loc = torch.from_numpy(batch.out_loc.astype(np.int64))
-        kv.k[li][loc] = k
-        kv.v[li][loc] = v
+        kv.k[li][loc] = k.to(kv.k.dtype)
+        kv.v[li][loc] = v.to(kv.v.dtype)
         o = paged_attention(q, kv.k[li], kv.v[li], page_table, batch.table_idx, batch.seq_lens,
                             batch.qo_indptr, self.sm_scale, st)
         return self._reduce(linear(o.reshape(T, qd), L["o"], None, st))
@@ -410,6 +414,7 @@ class OracleModel:
         residual = None
         for li, L in enumerate(self.w["layers"]):
             if cfg.fused_residual:
+                entering = (x, residual)
                 if residual is None:
                     residual = x
                     x = rmsnorm(x, L["input_norm"], cfg.rms_norm_eps, st)
@@ -418,6 +423,8 @@ class OracleModel:
                 a = self._attn(L, li, x, batch, kv, page_table)
                 a, residual = fused_add_rmsnorm(a, residual, L["post_norm"], cfg.rms_norm_eps, st)
                 x = self._mlp(L, a)
+                if self.layer_trace is not None:
+                    self.layer_trace.append({"x_in": entering[0], "res_in": entering[1], "x_out": x, "res_out": residual})
             else:
                 res = x
                 a = self._attn(L, li, rmsnorm(x, L["input_norm"], cfg.rms_norm_eps, st), batch, kv, page_table)

@@ -66,6 +66,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_attention_decode_workspace_bytes": (_L, [_I, _I, _I, _I]),
     "b200_attention_decode": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P]),
     "b200_attention_decode_noalloc": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
+    "b200_attention_decode_noalloc_status": (_I, [POINTER(c_int32), _P]),
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
     "b200_sample": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, ctypes.c_uint64, _P, _P]),
@@ -75,6 +76,10 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_comm_connect": (_I, [_P, _P]),
     "b200_comm_buffer": (c_void_p, [_P, _I]),
     "b200_comm_destroy": (_I, [_P]),
+    "b200_comm_set_wait_limit_ns": (_I, [_P, ctypes.c_uint64]),
+    "b200_comm_connect_loopback": (_I, [_P]),
+    "b200_comm_loopback_announce": (_I, [_P, ctypes.c_uint32, _P]),
+    "b200_engine_comm": (c_void_p, [_P]),
     "b200_allreduce": (_I, [_P, _I, _P, _I, _I, _P]),
     "b200_allreduce_fused_add_rmsnorm": (_I, [_P, _I, _P, _P, _P, _I, _I, _F, _I, _P]),
     "b200_engine_comm_export": (_I, [_P, _P]),
@@ -136,9 +141,6 @@ def load() -> ctypes.CDLL:
     if _lib is not None:
         return _lib
     path = LIB_PATH
-    if os.environ.get("B200_LIBRARY"):
-        # another build of the same library (for example one compiled with tuning hooks)
-        path = Path(os.environ["B200_LIBRARY"])
     if not path.exists():
         raise ImportError(
             f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "

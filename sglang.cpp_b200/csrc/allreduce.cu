@@ -36,7 +36,16 @@ struct CommDevice {
     void* peer_gather[kMaxRanks];                 // [rank] -> that rank's buffer of reduced rows (two-shot):
                                                   // 8-byte words of two bf16 values + the call number
     int rank, world;
+    uint64_t wait_limit_ns;                       // longest a CTA waits for its peers before it gives up
 };
+
+// The poll side of every flag: an acquire load at system scope, so the data loads that follow the
+// poll loop (after the CTA barrier) are ordered behind the flag they wait for.
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // Handshake of one CTA slot with the same slot on every peer.  Returns false on time-out.
 __device__ __forceinline__ bool comm_barrier(const CommDevice& c, int* status) {
@@ -49,21 +58,21 @@ __device__ __forceinline__ bool comm_barrier(const CommDevice& c, int* status) {
         const int peer = threadIdx.x;
         // This rank's partial was written by the kernel before this one; make it visible to
         // the other GPUs before the flag that announces it.
-        // No fence and no release/acquire pair is needed around the flag.  What it announces was
-        // written by the kernel BEFORE this one, so it has been performed at this GPU's L2 (the
-        // point the peers read from) before this kernel started; the peers read it with
-        // uncached loads issued after their poll loop exits; and the loads of this rank's
+        // No fence is needed before the flag store.  What it announces was written by the kernel
+        // BEFORE this one, so it has been performed at this GPU's L2 (the point the peers read
+        // from) before this kernel started; the peers poll with an acquire load and read the data
+        // with uncached loads issued after their poll loop exits; and the loads of this rank's
         // previous call finished before that kernel ended, so a peer that sees the new flag may
         // overwrite the other parity's buffer.  (Measured on 2 x B200: 9 us per call with
-        // fence.sys + st.release / ld.acquire, 2 us with the relaxed pair.)
+        // fence.sys + st.release, 2 us with the relaxed store.)
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(c.peer_flags[peer] + slot * kMaxRanks + c.rank),
                      "r"(call)
                      : "memory");
-        const volatile uint32_t* mine = c.peer_flags[c.rank] + slot * kMaxRanks + peer;
+        const uint32_t* mine = c.peer_flags[c.rank] + slot * kMaxRanks + peer;
         const uint64_t t0 = global_timer_ns();
         uint32_t spins = 0;
-        while (static_cast<int32_t>(*mine - call) < 0) {
-            if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+        while (static_cast<int32_t>(ld_acquire_sys(mine) - call) < 0) {
+            if ((++spins & 0xffu) == 0 && global_timer_ns() - t0 > c.wait_limit_ns) {
                 atomicExch(&status[kStatusTimeout], 401);
                 s_ok = 0;
                 break;
@@ -87,7 +96,9 @@ allreduce_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __nv_bfloat
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait_prior();
-    comm_barrier(c, status);
+    // A peer that never announced: leave `residual` and `out` as they are and let the host read
+    // the status word (site 401).
+    if (!comm_barrier(c, status)) return;
     const int nvec = hidden >> 3;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const int64_t base = static_cast<int64_t>(row) * nvec;
@@ -189,11 +200,11 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
     uint32_t y[kArVecPerThread][4];   // the bf16 sum of this thread's vectors
     if (c.rank == owner) {
         if (threadIdx.x < c.world) {
-            const volatile uint32_t* f = c.peer_flags[c.rank] + row * kMaxRanks + threadIdx.x;
+            const uint32_t* f = c.peer_flags[c.rank] + row * kMaxRanks + threadIdx.x;
             const uint64_t t0 = global_timer_ns();
             uint32_t spins = 0;
-            while (static_cast<int32_t>(*f - call) < 0) {
-                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+            while (static_cast<int32_t>(ld_acquire_sys(f) - call) < 0) {
+                if ((++spins & 0xffu) == 0 && global_timer_ns() - t0 > c.wait_limit_ns) {
                     atomicExch(&status[kStatusTimeout], 402);
                     s_ok = 0;
                     break;
@@ -201,6 +212,11 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
             }
         }
         __syncthreads();
+        // a partial never arrived: push nothing (the peers then run into their own limit, site 403)
+        if (!s_ok) {
+            if (threadIdx.x == 0) c.self_counter[row] = call;
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < kArVecPerThread; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
@@ -249,8 +265,9 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
                     y[i][0] = w0.x; y[i][1] = w0.z; y[i][2] = w1.x; y[i][3] = w1.z;
                     break;
                 }
-                if ((++spins & 0x3ffu) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+                if ((++spins & 0xffu) == 0 && global_timer_ns() - t0 > c.wait_limit_ns) {
                     atomicExch(&status[kStatusTimeout], 403);
+                    s_ok = 0;
                     y[i][0] = y[i][1] = y[i][2] = y[i][3] = 0u;
                     break;
                 }
@@ -258,6 +275,8 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
         }
     }
     if (threadIdx.x == 0) c.self_counter[row] = call;
+    __syncthreads();
+    if (!s_ok) return;  // the reduced row never arrived: leave `residual` and `out` as they are
 
     // every rank: the same add + norm on the same sum
     float vals[kArVecPerThread][8];
@@ -323,6 +342,8 @@ struct b200_comm {
     CommDevice dev = {};
     int64_t flags_bytes = 0, counters_bytes = 0;
     int two_shot_min_world = 8;   // B200_AR_TWO_SHOT_MIN_WORLD: groups of at least this size use the two-shot kernel
+    uint64_t wait_limit_ns = 2000000000ull;  // 2 s, as every other bounded wait of the library
+    bool loopback = false;        // every "peer" is this rank's own memory (time-out tests on one GPU)
 };
 
 namespace {
@@ -390,7 +411,51 @@ int b200_comm_connect(b200_comm* c, const void* all_handles) {
     c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
     c->dev.rank = c->rank;
     c->dev.world = c->world;
+    c->dev.wait_limit_ns = c->wait_limit_ns;
     c->connected = true;
+    return B200_OK;
+}
+
+int b200_comm_set_wait_limit_ns(b200_comm* c, uint64_t ns) {
+    B200_CHECK_ARG(c && ns > 0, "comm_set_wait_limit_ns: NULL communicator or zero limit");
+    c->wait_limit_ns = ns;
+    c->dev.wait_limit_ns = ns;
+    return B200_OK;
+}
+
+int b200_comm_connect_loopback(b200_comm* c) {
+    B200_CHECK_ARG(c, "comm_connect_loopback: NULL communicator");
+    B200_CHECK_ARG(!c->connected, "comm_connect_loopback: already connected");
+    for (int r = 0; r < c->world; ++r) c->peer_base[r] = c->local_base;
+    c->loopback = true;
+    // the same pointer set-up as b200_comm_connect, on the aliased bases
+    for (int r = 0; r < c->world; ++r) {
+        char* base = static_cast<char*>(c->peer_base[r]);
+        c->dev.peer_flags[r] = reinterpret_cast<uint32_t*>(base);
+        for (int p = 0; p < 2; ++p)
+            c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
+                                                                          p * c->buffer_bytes);
+        c->dev.peer_gather[r] = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
+    }
+    c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
+    c->dev.rank = c->rank;
+    c->dev.world = c->world;
+    c->dev.wait_limit_ns = c->wait_limit_ns;
+    c->connected = true;
+    return B200_OK;
+}
+
+int b200_comm_loopback_announce(b200_comm* c, uint32_t call_number, b200_stream_t stream) {
+    B200_CHECK_ARG(c && c->connected && c->loopback, "comm_loopback_announce: not a loop-back communicator");
+    // flag table [slots][kMaxRanks]: the word of source rank r in every slot
+    std::vector<uint32_t> row(static_cast<size_t>(kMaxCommBlocks) * kMaxRanks);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200_CHECK_CUDA(cudaStreamSynchronize(s));
+    B200_CHECK_CUDA(cudaMemcpy(row.data(), c->local_base, row.size() * 4, cudaMemcpyDeviceToHost));
+    for (int slot = 0; slot < kMaxCommBlocks; ++slot)
+        for (int r = 0; r < c->world; ++r)
+            if (r != c->rank) row[static_cast<size_t>(slot) * kMaxRanks + r] = call_number;
+    B200_CHECK_CUDA(cudaMemcpy(c->local_base, row.data(), row.size() * 4, cudaMemcpyHostToDevice));
     return B200_OK;
 }
 
@@ -403,7 +468,7 @@ int b200_comm_destroy(b200_comm* c) {
     if (!c) return B200_OK;
     cudaDeviceSynchronize();
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank && c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+        if (r != c->rank && c->peer_base[r] && !c->loopback) cudaIpcCloseMemHandle(c->peer_base[r]);
     if (c->local_base) cudaFree(c->local_base);
     delete c;
     return B200_OK;

@@ -572,14 +572,18 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
     p.kv_evict_first = kv_evict_first ? 1 : 0;
 
     const int smem = kStages * kStageBytes + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        B200_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
-    }
+    // The attribute belongs to (function, device): set it on every launch, as the other launchers do.
+    B200_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     B200_CHECK_CUDA(launch_kernel(attention_decode_kernel, dim3(grid), dim3(kThreads), smem, stream,
                                   dim3(1, 1, 1), tmap_k, tmap_v, p));
+    return B200_OK;
+}
+
+int reset_decode_workspace(void* workspace, cudaStream_t stream) {
+    // The per-request merge tickets at the head of the workspace: a step that was cut short (a
+    // bounded wait ran out) may leave them non-zero.
+    B200_CHECK_CUDA(cudaMemsetAsync(workspace, 0, kMaxBatch * sizeof(int), stream));
     return B200_OK;
 }
 
@@ -737,10 +741,10 @@ int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_tok
     unsigned char* base = static_cast<unsigned char*>(scratch);
     int* status = reinterpret_cast<int*>(base + usable);
     // The array keeps whatever the previous call left.  The per-request tickets must start at
-    // zero (a call that ended normally leaves them so, one that was cut short may not) and so must
-    // the status words; partial sums are always written before they are read.
+    // zero (a call that ended normally leaves them so, one that was cut short may not); partial
+    // sums are always written before they are read.  The status words in the array's tail are NOT
+    // cleared here: they keep the first report until b200_attention_decode_noalloc_status reads it.
     B200_CHECK_CUDA(cudaMemsetAsync(base, 0, kMaxBatch * sizeof(int), s));
-    B200_CHECK_CUDA(cudaMemsetAsync(status, 0, kNoAllocStatusBytes, s));
 
     CUtensorMap tk, tv;
     int err = make_kv_tmap(&tk, k_cache, num_slots, kv_heads, page_size);
@@ -750,6 +754,29 @@ int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_tok
     return launch_attention_decode(out, q, q_stride_token, q_stride_head, tk, tv, num_slots, page_table,
                                    page_table_stride, table_idx, seq_lens, batch, q_heads, kv_heads,
                                    page_size, sm_scale, base, usable, status, s);
+}
+
+int b200_attention_decode_noalloc_status(int32_t out[2], b200_stream_t stream) {
+    using namespace b200;
+    B200_CHECK_ARG(out != nullptr, "attention_decode_noalloc_status: out must not be NULL");
+    out[0] = out[1] = 0;
+    int dev = 0;
+    B200_CHECK_CUDA(cudaGetDevice(&dev));
+    B200_CHECK_ARG(dev >= 0 && dev < kNoAllocMaxDevices, "attention_decode_noalloc_status: device index out of range");
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        scratch = g_noalloc_ptr[dev];
+    }
+    if (!scratch) return B200_OK;  // no call was made on this device yet
+    int* status = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + kNoAllocScratchBytes - kNoAllocStatusBytes);
+    B200_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int host[2] = {0, 0};
+    B200_CHECK_CUDA(cudaMemcpy(host, status, sizeof(host), cudaMemcpyDeviceToHost));
+    out[0] = host[0];
+    out[1] = host[1];
+    if (host[0] != 0 || host[1] != 0) B200_CHECK_CUDA(cudaMemset(status, 0, sizeof(host)));
+    return B200_OK;
 }
 
 }  // extern "C"

@@ -51,6 +51,11 @@ void set_last_error(const char* fmt, ...);
 bool pdl_launches_enabled();
 void set_pdl_launches(bool on);
 
+// Kernels launched through launch_kernel by this thread so far (the step runner reports the
+// difference across a step).
+uint64_t kernel_launch_count();
+void note_kernel_launch();
+
 // One launch path for every kernel: cudaLaunchKernelEx, with the programmatic
 // stream serialization attribute when enabled (and an optional cluster shape).
 template <typename... KArgs, typename... Args>
@@ -77,6 +82,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n;
+    note_kernel_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

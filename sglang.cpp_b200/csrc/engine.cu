@@ -101,18 +101,6 @@ struct Tensor {
 
 using namespace b200;
 
-// Tuning builds only (-DB200_TUNE): B200_TUNE_SKIP is a bit mask of launches to leave out of the
-// step, to read each kernel family's cost inside the real launch chain.  Results are then garbage.
-#ifdef B200_TUNE
-static int tune_skip_mask() {
-    static const int v = getenv("B200_TUNE_SKIP") ? atoi(getenv("B200_TUNE_SKIP")) : 0;
-    return v;
-}
-#define B200_TUNE_SKIP(bit) ((tune_skip_mask() & (bit)) != 0)
-#else
-#define B200_TUNE_SKIP(bit) false
-#endif
-
 struct b200_comm;
 extern "C" {
 int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out);
@@ -245,6 +233,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     const b200_model_config& m = e->m;
     cudaStream_t s = e->stream;
     const int hidden = m.hidden_size, d = m.head_dim;
+    const uint64_t launches_before = kernel_launch_count();
     const int32_t* meta_table_idx = e->meta_dev;
     const int32_t* meta_qo = e->meta_dev + 2 * Bp;
 
@@ -308,7 +297,6 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             }
             return rc;
         }
-        if (B200_TUNE_SKIP(4)) return B200_OK;
         return launch_fused_add_rmsnorm(e->x, e->residual, w, T, hidden, m.rms_norm_eps, round_first, s);
     };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
@@ -316,13 +304,11 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     for (int l = 0; l < m.num_layers; ++l) {
         LayerWeights& L = e->layers[l];
         B200_TRY(add_norm(L.input_norm));
-        if (!B200_TUNE_SKIP(8))
-            B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+        B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
                                    B200_EPILOGUE_NONE, e->status, s));
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
         __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
-        if (!B200_TUNE_SKIP(2))
-            B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
+        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
                                               e->positions, e->out_loc, k_cache, v_cache, T, e->hq, e->hkv,
                                               d, m.max_position, e->num_slots, m.rms_norm_eps, 0, e->status, s));
         const bool timed = e->profile_attention && !e->capturing;
@@ -334,8 +320,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             }
             B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l], s));
         }
-        if (phase == B200_PHASE_DECODE && B200_TUNE_SKIP(1)) {
-        } else if (phase == B200_PHASE_DECODE) {
+        if (phase == B200_PHASE_DECODE) {
             B200_TRY(launch_attention_decode(e->attn_out, e->qkv, e->qkv_dim, d, L.tmap_k, L.tmap_v,
                                              e->num_slots, e->page_table, e->pt_cols, meta_table_idx,
                                              e->seq_lens, Bp, e->hq, e->hkv, e->c.page_size, e->sm_scale,
@@ -350,8 +335,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
             B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
             e->prof_pairs_recorded = l + 1;
         }
-        if (!B200_TUNE_SKIP(16))
-            B200_TRY(launch_linear(proj_out(), e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
+        B200_TRY(launch_linear(proj_out(), e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
                                    B200_EPILOGUE_NONE, e->status, s));
         B200_TRY(add_norm(L.post_norm));
         if (m.num_experts > 0) {
@@ -364,11 +348,9 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                         e->experts_local, e->moe_ws, e->status, s));
             continue;
         }
-        if (!B200_TUNE_SKIP(32))
-            B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
+        B200_TRY(launch_linear(e->h, e->x, L.gate_up, nullptr, T, 2 * e->inter, hidden, hidden, epi,
                                    e->status, s));
-        if (!B200_TUNE_SKIP(64))
-            B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
+        B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
                                    B200_EPILOGUE_NONE, e->status, s));
     }
     B200_TRY(add_norm(e->final_norm));
@@ -401,12 +383,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                       meta_table_idx, write_pos, static_cast<const int32_t*>(e->next_tokens),
                                       static_cast<int64_t>(B)));
     }
-    // Kernels launched above: prepare, embedding, per layer 8 (two norms, four GEMMs, the
-    // qk-norm/rope/store pass, attention), final norm, lm_head, argmax, token write-back, plus the
-    // row select in prefill.  A GEMM over more than 256 rows is one launch per 256-row slab.
-    const int slabs = div_ceil(T, 256);
-    e->launches_last_step = 2 + m.num_layers * (4 + 4 * slabs) + 1 + div_ceil(Bp, 256) + 1 +
-                            (B > 0 ? 1 : 0) + (phase == B200_PHASE_PREFILL ? 1 : 0);
+    e->launches_last_step = static_cast<int>(kernel_launch_count() - launches_before);
     return B200_OK;
 }
 
@@ -789,6 +766,9 @@ int b200_engine_synchronize(b200_engine* e) {
     B200_CHECK_CUDA(cudaMemcpy(host, e->status, sizeof(host), cudaMemcpyDeviceToHost));
     if (host[0] != 0) {
         cudaMemset(e->status, 0, sizeof(host));
+        // a step that was cut short can leave the decode kernel's merge tickets half counted
+        reset_decode_workspace(e->attn_ws, e->stream);
+        cudaStreamSynchronize(e->stream);
         set_last_error("a bounded wait inside a kernel ran out (site %d)", host[0]);
         return B200_ERR_TIMEOUT;
     }
@@ -820,6 +800,8 @@ int b200_engine_comm_connect(b200_engine* e, const void* all_handles) {
     B200_CHECK_ARG(e && e->comm, "engine_comm_connect: the engine was not created with tp_size > 1");
     return b200_comm_connect(e->comm, all_handles);
 }
+
+b200_comm* b200_engine_comm(b200_engine* e) { return e ? e->comm : nullptr; }
 
 int b200_engine_set_profiling(b200_engine* e, int on) {
     B200_CHECK_ARG(e, "engine_set_profiling: NULL engine");

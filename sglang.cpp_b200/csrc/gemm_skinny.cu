@@ -24,7 +24,6 @@
 #include "kernels.h"
 #include "tensormap.cuh"
 #include "tcgen05.cuh"
-#include <cstdio>
 
 namespace b200 {
 namespace {
@@ -88,20 +87,7 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
 }
 
-// Optional timeline capture for tuning (compiled out unless B200_GEMM_TRACE is defined): the
-// first thread of each role records %globaltimer at fixed points into p.trace[cta][point].
-#ifdef B200_GEMM_TRACE
-#define B200_TRACE(i)                                                                         \
-    do {                                                                                      \
-        if (p.trace && (threadIdx.x & 31) == 0)                                               \
-            p.trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = global_timer_ns();     \
-    } while (0)
-#else
-#define B200_TRACE(i) do { } while (0)
-#endif
-
 struct SkinnyParams {
-    unsigned long long* trace;  // NULL unless tracing
     __nv_bfloat16* y;          // [M, n_out]
     const __nv_bfloat16* bias; // [n_out] or NULL (plain epilogue only)
     int M;                     // rows of x / y
@@ -136,7 +122,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
     // Let the next kernel in the stream become resident right away: its set-up and weight loads
     // then overlap this kernel (it still waits for this grid to finish before touching its input).
-    B200_TRACE(0);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -203,7 +188,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    B200_TRACE(1);
 
     bool failed = false;
 
@@ -242,7 +226,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     break;
                 }
                 tc_fence_after();
-                if (i == 0) B200_TRACE(2);
                 const uint32_t a0 = smem_base + s * stage_bytes;
                 const uint32_t b0 = a0 + NUM_A * a_bytes;
 #pragma unroll
@@ -292,7 +275,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (is_epi) {
         if (!mbar_wait_bounded(smem_u32(&tmem_full_bar), 0, p.status, 103)) failed = true;
         tc_fence_after();
-        B200_TRACE(3);
     }
 
     for (int r = 0; r < nrounds; ++r) {
@@ -307,7 +289,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     tmem_ld_32x32b_x32(taddr, g);
                     if (NUM_A == 2) tmem_ld_32x32b_x32(taddr + nt, u);
                     tmem_ld_wait();
-                    B200_TRACE(4);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -350,9 +331,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         if (split == 1) continue;
 
-        B200_TRACE(5);
         cluster_sync_all();
-        B200_TRACE(6);
         if (is_epi) {
             // F / 4 is a power of two (split is 2, 4 or 8): shifts instead of divisions.
             const int f4_shift = 31 - __clz(F / 4);
@@ -401,7 +380,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
         }
     }
-    B200_TRACE(7);
 
     tc_fence_before();
     __syncthreads();
@@ -468,13 +446,6 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     // K split: up to one CTA per SM in total, at most 8 ranks (portable cluster size).
     int split = 1;
     int forced = env_int("B200_GEMM_SPLIT", 0);
-#ifdef B200_TUNE
-    {   // tuning builds: B200_SPLIT_N<N>=<split> overrides the split of GEMMs with that many W rows
-        char name[48];
-        snprintf(name, sizeof(name), "B200_SPLIT_N%d_K%d", N, K);
-        forced = env_int(name, forced);
-    }
-#endif
     if (forced > 0) {
         split = forced;
     } else {
@@ -513,10 +484,6 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     if (err != B200_OK) return err;
 
     SkinnyParams p;
-    p.trace = nullptr;
-#ifdef B200_GEMM_TRACE
-    p.trace = reinterpret_cast<unsigned long long*>(getenv("B200_GEMM_TRACE_PTR") ? strtoull(getenv("B200_GEMM_TRACE_PTR"), nullptr, 0) : 0ull);
-#endif
     p.y = static_cast<__nv_bfloat16*>(y);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.M = M;
@@ -581,7 +548,6 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
         if (err != B200_OK) return err;
     }
     SkinnyParams p;
-    p.trace = nullptr;
     p.y = static_cast<__nv_bfloat16*>(y);
     p.bias = nullptr;
     p.M = 0;

@@ -21,6 +21,11 @@ int g_sm_count[kMaxDevices] = {};
 namespace {
 thread_local bool g_pdl = false;
 }
+namespace {
+thread_local uint64_t g_launches = 0;
+}
+uint64_t kernel_launch_count() { return g_launches; }
+void note_kernel_launch() { ++g_launches; }
 bool pdl_launches_enabled() { return g_pdl; }
 void set_pdl_launches(bool on) { g_pdl = on; }
 

@@ -52,8 +52,8 @@ class ForwardOutput:
 
 class Engine:
     def __init__(self, model_config, config: EngineConfig):
-        """model_config: any object with the fields of oracle.token_loop_oracle.ModelConfig
-        (the forward-pass subset of include/sglang/models/config.h:15-42)."""
+        """model_config: any object with the forward-pass fields of the reference's ModelConfig
+        (include/sglang/models/config.h:15-42), named as b200_model_config names them."""
         self.model_config = model_config
         self.config = config
         m = ModelConfigStruct(
@@ -70,7 +70,11 @@ class Engine:
                                config.tp_size, int(config.expert_parallel))
         self._h = ctypes.c_void_p()
         call("b200_engine_create", ctypes.byref(m), ctypes.byref(c), ctypes.byref(self._h))
-        self._next_tokens_cpu = torch.empty(config.max_running_req + 1, dtype=torch.int32).pin_memory()
+        # A small ring of pinned token buffers, one per step in flight: a step enqueued before the
+        # previous step's tokens were read must not overwrite them (the reference allocates a
+        # pinned tensor per ForwardOutput, src/engine/engine.cc:526-531).
+        self._token_ring = [torch.empty(config.max_running_req + 1, dtype=torch.int32).pin_memory()
+                            for _ in range(4)]
         self.page_size = config.page_size
         self.dummy_table_idx = config.max_running_req
         self.pt_cols = (config.max_seq_len + 31) // 32 * 32   # page-table row length (src/engine/engine.cc:452-459)
@@ -99,9 +103,9 @@ class Engine:
              host.numel() * host.element_size())
 
     def load_weights(self, w: dict, tp_rank: int = 0, tp_size: int = 1) -> None:
-        """Upload weights given in the reference's packed layouts (full, unsharded tensors as
-        oracle.init_weights makes them), cut with the reference's TP shard rules for this rank
-        (sglang_cpp_b200.tp.shard_layer)."""
+        """Upload weights given in the reference's packed layouts (full, unsharded tensors: a dict
+        with "embed", "final_norm", optional "lm_head" and a list "layers" of per-layer dicts),
+        cut with the reference's TP shard rules for this rank (sglang_cpp_b200.tp.shard_layer)."""
         from .tp import shard_layer
 
         cfg = self.model_config
@@ -213,8 +217,14 @@ class Engine:
                         opt(top_k, np.int32), opt(top_p, np.float32), opt(seeds, np.uint64),
                         self._step_index)
         self._step_index += 1
-        call("b200_engine_step", self._h, ctypes.byref(st), self._next_tokens_cpu.data_ptr())
-        return ForwardOutput(self, self._next_tokens_cpu, b)
+        buf = self.next_token_buffer()
+        call("b200_engine_step", self._h, ctypes.byref(st), buf.data_ptr())
+        return ForwardOutput(self, buf, b)
+
+    def next_token_buffer(self) -> torch.Tensor:
+        """The pinned buffer the next step's tokens go to (call once per step)."""
+        self._ring_pos = (getattr(self, "_ring_pos", -1) + 1) % len(self._token_ring)
+        return self._token_ring[self._ring_pos]
 
     def synchronize(self) -> None:
         call("b200_engine_synchronize", self._h)

