@@ -408,6 +408,19 @@ class OracleModel:
         y = silu_and_mul(gu, st) if cfg.hidden_act == "silu" else gelu_and_mul(gu, st)
         return self._reduce(linear(y, L["down"], None, st))
 
+    def fused_layer(self, li: int, x, residual, batch: StepBatch, kv: KVState, page_table: np.ndarray):
+        """One decoder layer of the running-residual wiring (Qwen3DecoderLayer::forward,
+        src/models/qwen3.cc:21-35): returns (x, residual) as they leave the layer."""
+        cfg, st, L = self.cfg, self.store, self.w["layers"][li]
+        if residual is None:
+            residual = x
+            x = rmsnorm(x, L["input_norm"], cfg.rms_norm_eps, st)
+        else:
+            x, residual = fused_add_rmsnorm(x, residual, L["input_norm"], cfg.rms_norm_eps, st)
+        a = self._attn(L, li, x, batch, kv, page_table)
+        a, residual = fused_add_rmsnorm(a, residual, L["post_norm"], cfg.rms_norm_eps, st)
+        return self._mlp(L, a), residual
+
     def hidden_states(self, batch: StepBatch, kv: KVState, page_table: np.ndarray) -> torch.Tensor:
         cfg, st = self.cfg, self.store
         x = self.w["embed"][torch.from_numpy(batch.input_ids.astype(np.int64))].to(f32)
@@ -415,14 +428,7 @@ class OracleModel:
         for li, L in enumerate(self.w["layers"]):
             if cfg.fused_residual:
                 entering = (x, residual)
-                if residual is None:
-                    residual = x
-                    x = rmsnorm(x, L["input_norm"], cfg.rms_norm_eps, st)
-                else:
-                    x, residual = fused_add_rmsnorm(x, residual, L["input_norm"], cfg.rms_norm_eps, st)
-                a = self._attn(L, li, x, batch, kv, page_table)
-                a, residual = fused_add_rmsnorm(a, residual, L["post_norm"], cfg.rms_norm_eps, st)
-                x = self._mlp(L, a)
+                x, residual = self.fused_layer(li, x, residual, batch, kv, page_table)
                 if self.layer_trace is not None:
                     self.layer_trace.append({"x_in": entering[0], "res_in": entering[1], "x_out": x, "res_out": residual})
             else:

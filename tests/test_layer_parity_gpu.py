@@ -11,10 +11,16 @@ gate_up with the SwiGLU epilogue, down projection — and its outputs are compar
 outputs of that layer, computed with the reference's rounding points (src/layers/normalization.cu:
 27-43, src/layers/rotary_embedding.cu:49-66, src/layers/activation.cu:7-13).
 
-Bar per layer: the residual stream (one add away from the input) within ONE bf16 step of each
-value; the layer output (three GEMMs, a softmax and two norms downstream, fp32 sums in a different
-order) within 2^-7 of the output's RMS at the worst element and 2^-10 of it on average — one bf16
-step is 2^-8 relative, so that is two steps at the worst element of 32 x 1024.
+Bars per layer.  The residual stream leaving the layer (input + attention branch) and the layer
+output (three GEMMs, a softmax and two norms downstream of the
+input, fp32 sums taken in a different order, attention probabilities rounded to bf16 before P.V as
+FlashInfer's kernels do): mean error at most 5e-3 of the output's RMS — about one bf16 step of a
+typical element — and worst element of the 32 x 1024 at most 4e-2 of it (for the residual stream
+the RMS is that of the attention branch it gained).  Beside the fixed bars
+the test measures what ONE layer's bf16 rounding points cost by themselves (the oracle with the
+reference's rounding points against the same layer in exact fp32, same inputs) and requires the
+engine to be no further from the oracle than 1.5x that on the mean: no layer carries an error
+beyond rounding noise, so the whole-model distance is that noise compounded over 28 layers.
 """
 import numpy as np
 import pytest
@@ -53,6 +59,7 @@ def test_each_of_the_28_layers_matches_the_oracle_from_the_oracles_inputs(pkg, L
     qo = torch.tensor([0, T], dtype=torch.int32, device=dev)
     bf = torch.bfloat16
     report = []
+    exact = O.OracleModel(cfg, w, lambda t: t)
     for li, (Lw, tr) in enumerate(zip(w["layers"], oracle.layer_trace)):
         norm_in, norm_post = L.RMSNorm(cfg.hidden_size, cfg.rms_norm_eps), L.RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         norm_in.weight, norm_post.weight = Lw["input_norm"].to(dev), Lw["post_norm"].to(dev)
@@ -79,13 +86,19 @@ def test_each_of_the_28_layers_matches_the_oracle_from_the_oracles_inputs(pkg, L
         dy = (y.float().cpu() - want_y).abs()
         dr = (residual.float().cpu() - want_r).abs()
         rms = float(want_y.pow(2).mean().sqrt())
-        report.append((li, float(dy.max()) / rms, float(dy.mean()) / rms,
-                       float((dr / want_r.abs().clamp_min(1e-30)).max()), rms))
-    print("layer  max|dy|/rms  mean|dy|/rms  max rel residual  rms(y)")
+        # the same layer in exact fp32 from the same inputs: what the bf16 rounding points cost
+        ex_y, _ = exact.fused_layer(li, tr["x_in"], tr["res_in"], batch, O.KVState.create(cfg, 4 * page), pt)
+        noise = (ex_y - want_y).abs()
+        gained = want_r - (tr["res_in"] if tr["res_in"] is not None else tr["x_in"])
+        rms_a = float(gained.pow(2).mean().sqrt())
+        report.append((li, float(dy.max()) / rms, float(dy.mean()) / rms, float(noise.max()) / rms,
+                       float(noise.mean()) / rms, float(dr.max()) / rms_a, float(dr.mean()) / rms_a, rms))
+    print("layer  max|dy|/rms  mean|dy|/rms  noise max/rms  noise mean/rms  residual max  residual mean  rms(y)")
     for r in report:
-        print("%5d  %.3e   %.3e    %.3e        %.4f" % r)
-    for li, mx, mean, res_rel, _ in report:
-        assert res_rel <= 2.0 ** -7, f"layer {li}: residual stream {res_rel:.3e} from the oracle's"
-        assert mx <= 2.0 ** -7, f"layer {li}: output max {mx:.3e} of its RMS"
-        assert mean <= 2.0 ** -10, f"layer {li}: output mean {mean:.3e} of its RMS"
+        print("%5d  %.3e   %.3e    %.3e      %.3e       %.3e     %.3e      %.4f" % r)
+    for li, mx, mean, nmax, nmean, rmax, rmean, _ in report:
+        assert rmax <= 4e-2 and rmean <= 5e-3, f"layer {li}: residual stream {rmax:.3e} / {rmean:.3e} of the branch RMS"
+        assert mx <= 4e-2, f"layer {li}: output max {mx:.3e} of its RMS"
+        assert mean <= 5e-3, f"layer {li}: output mean {mean:.3e} of its RMS"
+        assert mean <= 1.5 * nmean, f"layer {li}: mean {mean:.3e} against rounding noise {nmean:.3e}"
     assert L.read_device_status() == (0, 0)
