@@ -169,6 +169,8 @@ struct b200_engine {
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
+    void* chain_scratch = nullptr;  // fp32 sums, partial sums of squares and barrier words of the decode layer chain
+    bool use_chain = true;  // B200_DECODE_CHAIN=0: decode steps run one kernel per operator, as prefill steps do
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
     bool kv_evict_first = true;  // B200_KV_EVICT_FIRST=0: K/V loads with the default L2 policy
     // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
@@ -301,7 +303,85 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
 
-    for (int l = 0; l < m.num_layers; ++l) {
+    // Decode batches of at most 64 tokens of a dense, unsharded model: everything between two attention
+    // launches is one persistent kernel (decode_chain.cu) instead of seven launches.
+    const bool chain = phase == B200_PHASE_DECODE && e->use_chain && !tp && m.num_experts == 0 &&
+                       decode_chain_supported(T, hidden, e->hq, e->hkv, d, e->inter, m.attention_bias != 0);
+    if (chain) {
+        auto caches = [&](int l, __nv_bfloat16** kc, __nv_bfloat16** vc) {
+            *kc = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
+            *vc = *kc + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
+        };
+        __nv_bfloat16 *kc = nullptr, *vc = nullptr;
+        caches(0, &kc, &vc);
+        LayerWeights& L0 = e->layers[0];
+        B200_TRY(add_norm(L0.input_norm));
+        B200_TRY(launch_linear(e->qkv, e->x, L0.qkv, nullptr, T, e->qkv_dim, hidden, hidden, B200_EPILOGUE_NONE,
+                               e->status, s));
+        B200_TRY(launch_qknorm_rope_store(e->qkv, L0.q_norm, L0.k_norm, e->rope_cos, e->rope_sin, e->positions,
+                                          e->out_loc, kc, vc, T, e->hq, e->hkv, d, m.max_position, e->num_slots,
+                                          m.rms_norm_eps, 0, e->status, s));
+        for (int l = 0; l < m.num_layers; ++l) {
+            LayerWeights& L = e->layers[l];
+            const bool timed = e->profile_attention && !e->capturing;
+            if (timed) {
+                while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
+                    cudaEvent_t ev = nullptr;
+                    B200_CHECK_CUDA(cudaEventCreate(&ev));
+                    e->prof_events.push_back(ev);
+                }
+                B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l], s));
+            }
+            B200_TRY(launch_attention_decode(e->attn_out, e->qkv, e->qkv_dim, d, L.tmap_k, L.tmap_v, e->num_slots,
+                                             e->page_table, e->pt_cols, meta_table_idx, e->seq_lens, Bp, e->hq,
+                                             e->hkv, e->c.page_size, e->sm_scale, e->attn_ws, e->attn_ws_bytes,
+                                             e->status, s, e->kv_evict_first));
+            if (timed) {
+                B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
+                e->prof_pairs_recorded = l + 1;
+            }
+            const bool last = l + 1 == m.num_layers;
+            DecodeChainArgs a = {};
+            a.tokens = T;
+            a.hidden = hidden;
+            a.inter = e->inter;
+            a.q_heads = e->hq;
+            a.kv_heads = e->hkv;
+            a.max_pos = m.max_position;
+            a.eps = m.rms_norm_eps;
+            a.round_first = round_first;
+            a.gelu = m.hidden_act == 1;
+            a.attn_out = e->attn_out;
+            a.residual = e->residual;
+            a.mlp_act = e->h;
+            a.x_out = e->x;
+            a.qkv_out = e->qkv;
+            a.w_o = L.o;
+            a.w_gate_up = L.gate_up;
+            a.w_down = L.down;
+            a.post_norm_w = L.post_norm;
+            if (!last) {
+                LayerWeights& N = e->layers[l + 1];
+                a.w_qkv_next = N.qkv;
+                a.next_input_norm_w = N.input_norm;
+                a.q_norm_w = N.q_norm;
+                a.k_norm_w = N.k_norm;
+                caches(l + 1, &kc, &vc);
+                a.k_cache_next = kc;
+                a.v_cache_next = vc;
+            }
+            a.cos_t = e->rope_cos;
+            a.sin_t = e->rope_sin;
+            a.positions = e->positions;
+            a.out_loc = e->out_loc;
+            a.num_slots = e->num_slots;
+            a.scratch = e->chain_scratch;
+            a.status = e->status;
+            B200_TRY(launch_decode_chain(a, s));
+        }
+    }
+
+    for (int l = 0; l < (chain ? 0 : m.num_layers); ++l) {
         LayerWeights& L = e->layers[l];
         B200_TRY(add_norm(L.input_norm));
         B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
@@ -490,6 +570,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     e->status = device_status_words(&err);
     if (err != B200_OK) { delete e; return err; }
     if (const char* v = getenv("B200_PDL")) e->use_pdl = atoi(v) != 0;
+    if (const char* v = getenv("B200_DECODE_CHAIN")) e->use_chain = atoi(v) != 0;
     if (const char* v = getenv("B200_KV_EVICT_FIRST")) e->kv_evict_first = atoi(v) != 0;
 
     auto fail = [&](int code) { b200_engine_destroy(e); return code; };
@@ -568,6 +649,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
                                             e->moe_inter),
                         false));
     }
+    E_TRY(dev_alloc(e, &e->chain_scratch, decode_chain_scratch_bytes(m.hidden_size), true));
     e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);
     E_TRY(dev_alloc(e, &e->attn_ws, e->attn_ws_bytes, true));
 

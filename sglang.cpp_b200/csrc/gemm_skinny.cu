@@ -438,7 +438,8 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
                        int K, int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
     const bool gated = epilogue != B200_EPILOGUE_NONE;
     const int n_out = gated ? N / 2 : N;
-    const int nt = div_ceil(M, 32) * 32;
+    // accumulator columns: 32, or a multiple of the 64-column exchange round (the epilogue walks whole rounds)
+    const int nt = M <= 32 ? 32 : div_ceil(M, kRoundCols) * kRoundCols;
     const int kb_total = K / kBlockK;
     const int n_tiles = div_ceil(n_out, kTileN);
     const int num_a = gated ? 2 : 1;

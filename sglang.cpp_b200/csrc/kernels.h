@@ -57,6 +57,33 @@ int launch_moe_forward(void* out, const void* hidden, const void* router_logits,
                        int activation, int expert_begin, int num_local_experts, void* workspace,
                        int* status, cudaStream_t stream);
 
+// Decode-step layer chain (decode_chain.cu): o_proj -> add + norm -> gate_up -> act -> down ->
+// add + norm -> the next layer's qkv -> QK-norm -> RoPE -> KV store, as one persistent kernel.
+struct DecodeChainArgs {
+    int tokens, hidden, inter, q_heads, kv_heads, max_pos;
+    float eps;
+    bool round_first, gelu;
+    const void* attn_out;        // [tokens, q_heads * 128] bf16, the attention output of this layer
+    void* residual;              // [tokens, hidden] bf16, updated in place
+    void* mlp_act;               // [tokens, inter] bf16 scratch (the activated gate_up output)
+    void* x_out;                 // last layer only: [tokens, hidden] down_proj output (no residual add)
+    void* qkv_out;               // [tokens, (q + 2 kv) * 128]: the q heads of the next layer are written
+    const void *w_o, *w_gate_up, *w_down;
+    const void* w_qkv_next;      // NULL for the last layer: the chain then ends after down_proj
+    const void *post_norm_w, *next_input_norm_w, *q_norm_w, *k_norm_w;   // q / k norm weights may be NULL
+    const float *cos_t, *sin_t;
+    const int32_t *positions, *out_loc;
+    void *k_cache_next, *v_cache_next;
+    int64_t num_slots;
+    void* scratch;               // decode_chain_scratch_bytes(hidden), zero-initialised once
+    int* status;
+};
+int decode_chain_max_grid();
+int64_t decode_chain_scratch_bytes(int hidden);
+bool decode_chain_supported(int tokens, int hidden, int q_heads, int kv_heads, int head_dim, int inter,
+                            bool has_bias);
+int launch_decode_chain(const DecodeChainArgs& args, cudaStream_t stream);
+
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
 int reset_decode_workspace(void* workspace, cudaStream_t stream);
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);

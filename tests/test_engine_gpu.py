@@ -21,6 +21,8 @@ def small_cfg(kind: str) -> O.ModelConfig:
         return O.ModelConfig(3, 256, 4, 2, 128, 512, 2048, 1e-6, 1e6, 512, True, True, True)
     if kind == "llama":
         return O.ModelConfig(2, 256, 4, 1, 128, 448, 1536, 1e-5, 5e5, 512, False, False, False)
+    if kind == "llama_chain":   # Llama wiring with sizes the decode layer chain takes (intermediate % 128 == 0)
+        return O.ModelConfig(3, 384, 4, 2, 128, 640, 1536, 1e-5, 5e5, 512, False, False, False)
     if kind == "qwen2":
         return O.ModelConfig(2, 256, 8, 8, 128, 512, 1024, 1e-6, 1e6, 512, True, False, False,
                              attention_bias=True)
@@ -47,6 +49,10 @@ class Pair:
         self.oracle = O.OracleModel(cfg, self.w, store)
         self.kv = O.KVState.create(cfg, (num_pages + 1) * page_size)
         self.max_running_req = max_running_req
+
+    def engine_status_clean(self):
+        self.engine.synchronize()   # raises on a recorded time-out or bad index
+        return True
 
     def oracle_batch(self, reqs, prefill, tokens_by_req=None):
         ids, pos, loc, qo = [], [], [], [0]
@@ -120,6 +126,58 @@ def test_prefill_then_decode_matches_oracle(pkg, kind, page_size):
         sure = (top2[:, 0] - top2[:, 1]) > 2 * MAX_ABS
         assert torch.equal(out.next_tokens_cpu.long()[sure], want_tok[sure])
     pr.engine.close()
+
+
+@pytest.mark.parametrize("kind,nreq", [("qwen3", 3), ("qwen3", 64), ("llama_chain", 5), ("llama_chain", 37)])
+def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_path(pkg, monkeypatch, kind, nreq):
+    """Decode steps of dense models run everything between two attention launches as one persistent
+    kernel.  The same requests through that path and through the one-kernel-per-operator path
+    (B200_DECODE_CHAIN=0, read when the engine is created): each against the oracle at the usual
+    bars, and against one another (they differ only in the order partial sums of squares are added
+    for the norms, so a few logits may sit one bf16 step apart)."""
+    cfg = small_cfg(kind)
+    rng = np.random.default_rng(17)
+    lens = rng.integers(3, 70, size=nreq)
+    prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).astype(np.int32) for n in lens]
+    outs = {}
+    for chain in ("0", "1"):
+        monkeypatch.setenv("B200_DECODE_CHAIN", chain)
+        pr = Pair(pkg, cfg, 16, num_pages=nreq * 6 + 8, max_running_req=max(nreq, 8))
+        reqs = [pr.hb.add_request(p, 6) for p in prompts]
+        pr.host_tokens = {r.table_idx: list(p) + [0] * 16 for r, p in zip(reqs, prompts)}
+        for i in range(0, nreq, 16):          # prefill in batches that fit the engine's extend budget
+            pr.hb.allocate(reqs[i:i + 16])
+            ob, pt = pr.oracle_batch(reqs[i:i + 16], True)
+            want = pr.oracle.forward(ob, pr.kv, pt)
+            out = pr.hb.prefill(reqs[i:i + 16])
+            out.synchronize()
+            tok = want.argmax(-1).tolist()
+            for r, t in zip(reqs[i:i + 16], tok):
+                pr.host_tokens[r.table_idx][r.cached_len] = t
+            pr.engine.write_token_pool([r.table_idx for r in reqs[i:i + 16]], [r.cached_len for r in reqs[i:i + 16]], tok)
+        steps = []
+        for step in range(3):
+            pr.hb.allocate(reqs)
+            ob, pt = pr.oracle_batch(reqs, False)
+            want = pr.oracle.forward(ob, pr.kv, pt)
+            out = pr.hb.decode(reqs, padded_size=min(nreq + (step % 2), 64))
+            out.synchronize()
+            got = pr.engine.logits(nreq)
+            check_logits(got, want, f"{kind} chain={chain} decode step {step}")
+            steps.append(got.clone())
+            tok = want.argmax(-1).tolist()
+            for r, t in zip(reqs, tok):
+                pr.host_tokens[r.table_idx][r.cached_len] = t
+            pr.engine.write_token_pool([r.table_idx for r in reqs], [r.cached_len for r in reqs], tok)
+        _, _, launches = pr.engine.read_profile()
+        outs[chain] = (torch.stack(steps), launches)
+        assert pr.engine_status_clean()
+        pr.engine.close()
+    assert outs["1"][1] < outs["0"][1], "the chain path must launch fewer kernels"
+    # prepare, embedding, layer 0's norm / qkv / rope, (attention + chain) per layer, final norm, lm_head, argmax, write-back
+    assert outs["1"][1] == 9 + 2 * cfg.num_layers, outs["1"][1]
+    d = (outs["1"][0].float() - outs["0"][0].float()).abs()
+    assert float(d.max()) <= MAX_ABS and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
 
 
 def test_engine_writes_its_own_tokens_back(pkg):

@@ -16,7 +16,8 @@ output (three GEMMs, a softmax and two norms downstream of the
 input, fp32 sums taken in a different order, attention probabilities rounded to bf16 before P.V as
 FlashInfer's kernels do): mean error at most 5e-3 of the output's RMS — about one bf16 step of a
 typical element — and worst element of the 32 x 1024 at most 4e-2 of it (for the residual stream
-the RMS is that of the attention branch it gained).  Beside the fixed bars
+the RMS is that of the attention branch it gained, and one bf16 step of the stored value is allowed on
+top: the stream is kept in bf16).  Beside the fixed bars
 the test measures what ONE layer's bf16 rounding points cost by themselves (the oracle with the
 reference's rounding points against the same layer in exact fp32, same inputs) and requires the
 engine to be no further from the oracle than 1.5x that on the mean: no layer carries an error
@@ -91,8 +92,11 @@ def test_each_of_the_28_layers_matches_the_oracle_from_the_oracles_inputs(pkg, L
         noise = (ex_y - want_y).abs()
         gained = want_r - (tr["res_in"] if tr["res_in"] is not None else tr["x_in"])
         rms_a = float(gained.pow(2).mean().sqrt())
+        # the residual stream is stored in bf16: an element may land on the neighbouring bf16 value when
+        # the branch it gained differs a little, so allow one step of the value beside the branch's own bar
+        excess = (dr - want_r.abs() * 2.0 ** -8).clamp_min(0.0)
         report.append((li, float(dy.max()) / rms, float(dy.mean()) / rms, float(noise.max()) / rms,
-                       float(noise.mean()) / rms, float(dr.max()) / rms_a, float(dr.mean()) / rms_a, rms))
+                       float(noise.mean()) / rms, float(excess.max()) / rms_a, float(dr.mean()) / rms_a, rms))
     print("layer  max|dy|/rms  mean|dy|/rms  noise max/rms  noise mean/rms  residual max  residual mean  rms(y)")
     for r in report:
         print("%5d  %.3e   %.3e    %.3e      %.3e       %.3e     %.3e      %.4f" % r)

@@ -24,6 +24,11 @@ RTOL = 2 ** -7
     (256, 128, 2048),     # Qwen3-MoE router
     (33, 1000, 192),      # N not a multiple of the 128-feature tile
     (300, 512, 256),      # more rows than one slab
+    (70, 384, 512),       # row counts between two multiples of the 64-column exchange round:
+    (96, 256, 128),       #   every row must be written (one round per 64 accumulator columns)
+    (150, 1024, 384),
+    (218, 1280, 384),
+    (224, 384, 640),
     (64, 151936, 1024),   # Qwen3-0.6B lm_head (tied embedding): 311 MB of weights
     (0, 512, 256),
 ])
@@ -47,7 +52,8 @@ def test_linear_bias_and_strided_input(L):
     assert_close_bf16(y, O.linear(x, w, b), 4e-3, RTOL, "linear + bias, strided rows")
 
 
-@pytest.mark.parametrize("M,I,K", [(64, 3072, 1024), (5, 768, 2048), (128, 14336 // 8, 4096), (256, 256, 128)])
+@pytest.mark.parametrize("M,I,K", [(64, 3072, 1024), (5, 768, 2048), (128, 14336 // 8, 4096), (256, 256, 128),
+                                   (90, 640, 384), (200, 256, 512)])
 def test_gate_up_swiglu_epilogue(L, pkg, M, I, K):
     gen = torch.Generator().manual_seed(I)
     x = randn_bf16(gen, M, K)
