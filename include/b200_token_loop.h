@@ -442,6 +442,15 @@ B200_API int b200_engine_comm_connect(b200_engine* engine, const void* all_handl
  * (NULL when the engine was created with tp_size 1). */
 B200_API b200_comm* b200_engine_comm(b200_engine* engine);
 
+/* No counterpart in the reference.  With B200_DECODE_CHAIN=1 in the environment when the engine is
+ * created, decode steps of at most 64 tokens of a dense, unsharded model run everything between two
+ * attention launches (o_proj, add + norm, gate_up, activation, down, add + norm, the next layer's
+ * qkv, QK-norm, RoPE, KV store) as one persistent kernel of 8-CTA clusters whose CTAs must all be
+ * resident at once, instead of one kernel per operator (the default, and the faster of the two on
+ * B200).  Returns the number of CTAs that kernel runs with on the current device, or 0 when the
+ * device cannot hold it. */
+B200_API int b200_decode_chain_grid(void);
+
 /* The stream the engine enqueues on (Engine::stream_), as a cudaStream_t. */
 B200_API b200_stream_t b200_engine_stream(b200_engine* engine);
 

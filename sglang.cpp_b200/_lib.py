@@ -80,6 +80,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_comm_connect_loopback": (_I, [_P]),
     "b200_comm_loopback_announce": (_I, [_P, ctypes.c_uint32, _P]),
     "b200_engine_comm": (c_void_p, [_P]),
+    "b200_decode_chain_grid": (_I, []),
     "b200_allreduce": (_I, [_P, _I, _P, _I, _I, _P]),
     "b200_allreduce_fused_add_rmsnorm": (_I, [_P, _I, _P, _P, _P, _I, _I, _F, _I, _P]),
     "b200_engine_comm_export": (_I, [_P, _P]),

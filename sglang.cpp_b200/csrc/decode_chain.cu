@@ -14,15 +14,17 @@
 //   * a producer warp streams the CTA's weight tiles with TMA through a ring of 16 KB slots in the
 //     order the phases will use them.  Weights depend on nothing, so the stream runs ahead across
 //     phase boundaries and the dependent chain only sees shared-memory latency;
-//   * the activation operand of a phase is built in shared memory by the CTA itself from what the
-//     previous phase left in global memory — for the projections that follow a norm, as
+//   * the activation operand of a phase comes from what the previous phase left in global memory:
+//     by TMA where that is bf16 already (attention output, activated gate_up output), and for the
+//     projections that follow a norm the CTA builds it in shared memory itself as
 //     bf16(sum * rstd * norm_weight) from the fp32 sums, which is exactly what the reference's
 //     fused add + RMSNorm stores (src/layers/normalization.cu:27-43), so no separate norm pass and
 //     no extra barrier is needed;
-//   * split-K partials go to the tile's owners through distributed shared memory (st.async with
-//     transaction counting on the owner's mbarrier): rank r of the cluster owns tokens 8r..8r+7 of
-//     the tile, reduces the eight partials in rank order and runs the phase's epilogue on whole
-//     128-feature rows: residual add (+ partial sums of squares), SwiGLU, or — a qkv tile being
+//   * split-K partials go to the tile's owners through distributed shared memory: the CTA lays
+//     its partial tile out per owner in its own shared memory and one thread sends each owner its
+//     4 KB with a bulk copy that counts bytes on the owner's mbarrier.  Rank r of the cluster owns
+//     tokens 8r..8r+7 of the tile, reduces the eight partials in rank order and runs the phase's
+//     epilogue on whole 128-feature rows: residual add (+ partial sums of squares), SwiGLU, or — a qkv tile being
 //     exactly one head — QK-norm, RoPE and the store into the paged KV pool;
 //   * phases are separated by a grid barrier (one atomic per CTA; bounded wait).
 // Every wait is bounded: when one runs out the kernel records the site in the status word, stops
@@ -41,15 +43,17 @@ constexpr int kTile = 128;      // features per unit (UMMA M)
 constexpr int kBK = 64;         // elements per k-block (one 128-byte swizzle row)
 constexpr int kNT = 64;         // token columns (UMMA N)
 constexpr int kTokPerRank = kNT / kCluster;  // 8 tokens owned by each rank
-constexpr int kWSlots = 6;
-constexpr int kBSlots = 6;
+constexpr int kWSlots = 5;
+constexpr int kBSlots = 4;
 constexpr int kThreads = 192;   // warp 0: weight TMA, warp 1: MMA + TMEM owner, warps 2-5: operand builders / epilogue
 constexpr uint32_t kWBytes = kTile * kBK * 2;   // 16 KB
 constexpr uint32_t kBBytes = kNT * kBK * 2;     // 8 KB
 constexpr uint32_t kXPart = kTile * kTokPerRank * 4;          // one (source rank, accumulator) block: 4 KB
 constexpr uint32_t kXchgBytes = kCluster * 2 * kXPart;        // 64 KB
+constexpr uint32_t kSendBytes = kCluster * kXPart;             // 32 KB: one accumulator's partial tile, owner-major
 constexpr uint32_t kStageBytes = 2 * kTokPerRank * kTile * 4; // 8 KB: reduced sums, token-major
-constexpr uint32_t kSmemBytes = kWSlots * kWBytes + kBSlots * kBBytes + kXchgBytes + kStageBytes + 1024;
+constexpr uint32_t kSmemBytes =
+    kWSlots * kWBytes + kBSlots * kBBytes + kXchgBytes + kSendBytes + kStageBytes + 1024;
 constexpr uint32_t kTmemCols = 256;  // two accumulator buffers of 2 x 64 columns
 
 enum PhaseKind : int {
@@ -112,16 +116,18 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
     return remote;
 }
-// 16 bytes into a peer's shared memory, counted on that peer's mbarrier when they land.
-__device__ __forceinline__ void st_async_v4(uint32_t remote_addr, float a, float b, float c, float d,
-                                            uint32_t remote_bar) {
+// `bytes` of this CTA's shared memory into a peer's, counted on the peer's mbarrier when they land.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t remote_dst, uint32_t local_src, uint32_t bytes,
+                                                  uint32_t remote_bar) {
     asm volatile(
-        "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
-            remote_addr),
-        "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)), "r"(__float_as_uint(d)),
-        "r"(remote_bar)
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(remote_dst),
+        "r"(local_src), "r"(bytes), "r"(remote_bar)
         : "memory");
 }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the bulk copies issued by this thread have finished READING their source
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
 }
@@ -176,6 +182,7 @@ template <int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
                     const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tm3,
+                    const __grid_constant__ CUtensorMap tmb0, const __grid_constant__ CUtensorMap tmb2,
                     const ChainParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t w_full[kWSlots], w_empty[kWSlots];
@@ -191,7 +198,8 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
     const uint32_t w_base = smem_base;
     const uint32_t b_base = w_base + kWSlots * kWBytes;
     const uint32_t x_base = b_base + kBSlots * kBBytes;
-    const uint32_t stage_base = x_base + kXchgBytes;
+    const uint32_t send_base = x_base + kXchgBytes;
+    const uint32_t stage_base = send_base + kSendBytes;
     uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
     const float* xbuf = reinterpret_cast<const float*>(smem_al + (x_base - smem_base));
     float* stage = reinterpret_cast<float*>(smem_al + (stage_base - smem_base));
@@ -200,6 +208,7 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
     const int cid = static_cast<int>(blockIdx.x) / kCluster;
     const int nclusters = static_cast<int>(gridDim.x) / kCluster;
     const CUtensorMap* tms[4] = {&tm0, &tm1, &tm2, &tm3};
+    const CUtensorMap* tmbs[4] = {&tmb0, nullptr, &tmb2, nullptr};   // bf16 activation operands (phases 0 and 2)
 
     // K range of this rank in a phase
     auto kb_range = [&](const ChainPhase& ph, int& kb0, int& nkb) {
@@ -217,7 +226,7 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
             mbar_init(smem_u32(&w_empty[s]), 1);
         }
         for (int s = 0; s < kBSlots; ++s) {
-            mbar_init(smem_u32(&b_full[s]), 128);
+            mbar_init(smem_u32(&b_full[s]), 1);
             mbar_init(smem_u32(&b_empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -228,7 +237,7 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
         mbar_init(smem_u32(&xchg_free), kCluster);
         s_failed = 0;
         fence_mbar_init();
-        // arm the exchange barrier for this cluster's first unit, before any peer can push
+        // arm the exchange barrier for this cluster's first unit, before any peer can send
         for (int q = 0; q < 4; ++q) {
             if (p.ph[q].kind != kPhaseNone && cid < p.ph[q].units) {
                 mbar_arrive_expect_tx(smem_u32(&xchg_full), xchg_tx(p.ph[q]));
@@ -236,6 +245,8 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
             }
         }
         for (int q = 0; q < 4; ++q) tma_prefetch_desc(tms[q]);
+        tma_prefetch_desc(&tmb0);
+        tma_prefetch_desc(&tmb2);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -372,45 +383,80 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
             }
 
             for (int u = cid; u < ph.units; u += nclusters, ++un) {
-                // ---- build this rank's slice of the activation operand: [64 tokens][64 k] per k-block ----
-                for (int i = 0; i < nkb; ++i, ++bit) {
-                    const uint32_t bs = bit % kBSlots;
-                    if (bit >= kBSlots) W.wait(smem_u32(&b_empty[bs]), ((bit / kBSlots) - 1) & 1u, 506);
-                    const int k0 = (kb0 + i) * kBK;
+                // ---- this rank's slice of the activation operand: [64 tokens][64 k] per k-block ----
+                if (!ph.b_norm) {
+                    // bf16 rows in global memory: TMA (rows past T read as zero).  What an earlier phase of
+                    // this launch wrote with ordinary stores is ordered before these reads by the grid
+                    // barrier plus a proxy fence on either side.
+                    if (et == 0) {
+                        fence_proxy_async_all();
+                        for (int i = 0; i < nkb; ++i) {
+                            const uint32_t bs = (bit + i) % kBSlots;
+                            if (bit + i >= kBSlots) W.wait(smem_u32(&b_empty[bs]), (((bit + i) / kBSlots) - 1) & 1u, 506);
+                            const uint32_t bar = smem_u32(&b_full[bs]);
+                            mbar_arrive_expect_tx(bar, kBBytes);
+                            tma_load_2d(b_base + bs * kBBytes, tmbs[q], (kb0 + i) * kBK, 0, bar);
+                        }
+                    }
+                    bit += nkb;
+                } else {
+                    // normalised operand, two k-blocks of loads in flight per thread
                     const int c = et & 7;
+                    for (int i0 = 0; i0 < nkb; i0 += 2) {
+                        const int ni = min(2, nkb - i0);
+                        float4 lo[2][4], hi[2][4];
+                        uint4 w4[2];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int t = (et >> 3) + 16 * j;
-                        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-                        if (t < p.T) {
-                            if (ph.b_norm) {
-                                const float4* sp = reinterpret_cast<const float4*>(p.sums + static_cast<int64_t>(t) * p.hidden + k0 + c * 8);
-                                const float4 lo = __ldcg(sp), hi = __ldcg(sp + 1);
-                                const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(ph.norm_w + k0 + c * 8));
-                                const float rs = s_rstd[t];
-                                packed.x = pack_bf16(lo.x * rs * bf16_lo(w4.x), lo.y * rs * bf16_hi(w4.x));
-                                packed.y = pack_bf16(lo.z * rs * bf16_lo(w4.y), lo.w * rs * bf16_hi(w4.y));
-                                packed.z = pack_bf16(hi.x * rs * bf16_lo(w4.z), hi.y * rs * bf16_hi(w4.z));
-                                packed.w = pack_bf16(hi.z * rs * bf16_lo(w4.w), hi.w * rs * bf16_hi(w4.w));
-                            } else {
-                                packed = __ldcg(reinterpret_cast<const uint4*>(ph.b_src + static_cast<int64_t>(t) * ph.ldb + k0 + c * 8));
+                        for (int ii = 0; ii < 2; ++ii) {
+                            if (ii >= ni) continue;
+                            const int k0 = (kb0 + i0 + ii) * kBK;
+                            w4[ii] = __ldg(reinterpret_cast<const uint4*>(ph.norm_w + k0 + c * 8));
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int t = (et >> 3) + 16 * j;
+                                if (t < p.T) {
+                                    const float4* sp = reinterpret_cast<const float4*>(p.sums + static_cast<int64_t>(t) * p.hidden + k0 + c * 8);
+                                    lo[ii][j] = __ldcg(sp);
+                                    hi[ii][j] = __ldcg(sp + 1);
+                                }
                             }
                         }
-                        const uint32_t dst = b_base + bs * kBBytes + static_cast<uint32_t>(t) * 128u +
-                                             (static_cast<uint32_t>(c ^ (t & 7)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed.x), "r"(packed.y),
-                                     "r"(packed.z), "r"(packed.w)
-                                     : "memory");
+#pragma unroll
+                        for (int ii = 0; ii < 2; ++ii) {
+                            if (ii >= ni) continue;
+                            const uint32_t bs = (bit + ii) % kBSlots;
+                            if (bit + ii >= kBSlots) W.wait(smem_u32(&b_empty[bs]), (((bit + ii) / kBSlots) - 1) & 1u, 506);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int t = (et >> 3) + 16 * j;
+                                uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+                                if (t < p.T) {
+                                    const float rs = s_rstd[t];
+                                    const float4 l = lo[ii][j], h = hi[ii][j];
+                                    packed.x = pack_bf16(l.x * rs * bf16_lo(w4[ii].x), l.y * rs * bf16_hi(w4[ii].x));
+                                    packed.y = pack_bf16(l.z * rs * bf16_lo(w4[ii].y), l.w * rs * bf16_hi(w4[ii].y));
+                                    packed.z = pack_bf16(h.x * rs * bf16_lo(w4[ii].z), h.y * rs * bf16_hi(w4[ii].z));
+                                    packed.w = pack_bf16(h.z * rs * bf16_lo(w4[ii].w), h.w * rs * bf16_hi(w4[ii].w));
+                                }
+                                const uint32_t dst = b_base + bs * kBBytes + static_cast<uint32_t>(t) * 128u +
+                                                     (static_cast<uint32_t>(c ^ (t & 7)) << 4);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed.x),
+                                             "r"(packed.y), "r"(packed.z), "r"(packed.w)
+                                             : "memory");
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        bar_epilogue();
+                        if (et == 0)
+                            for (int ii = 0; ii < ni; ++ii) mbar_arrive(smem_u32(&b_full[(bit + ii) % kBSlots]));
+                        bit += ni;
                     }
-                    fence_proxy_async_smem();
-                    mbar_arrive(smem_u32(&b_full[bs]));
                 }
 
-                // ---- partial sums: TMEM -> the owners' exchange buffers ----
+                // ---- partial sums: TMEM -> own shared memory, owner-major -> bulk copies to the owners ----
                 const uint32_t buf = un & 1u;
                 W.wait(smem_u32(&acc_full[buf]), (un >> 1) & 1u, 507);
                 tc_fence_after();
-                if (un >= 1) W.wait(xfree_addr, (un - 1) & 1u, 508, true);
                 for (int a = 0; a < na; ++a) {
                     uint32_t v0[32], v1[32];
                     if (nkb > 0) {
@@ -423,15 +469,30 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v0[j] = v1[j] = 0u;
                     }
-                    const uint32_t off = x_base + ((rank * 2u + static_cast<uint32_t>(a)) * kTile + static_cast<uint32_t>(feat)) * 32u;
+                    // the send buffer is free once the previous bulk copies have read it (thread 0 issued them)
+                    if (et == 0) bulk_wait_read();
+                    bar_epilogue();
 #pragma unroll
                     for (int o = 0; o < kCluster; ++o) {
-                        const uint32_t dst = map_to_rank(off, o), rbar = map_to_rank(xfull_addr, o);
+                        const uint32_t dst = send_base + (static_cast<uint32_t>(o) * kTile + static_cast<uint32_t>(feat)) * 32u;
                         const uint32_t* src = o < 4 ? &v0[8 * o] : &v1[8 * (o - 4)];
-                        st_async_v4(dst, __uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]),
-                                    __uint_as_float(src[3]), rbar);
-                        st_async_v4(dst + 16, __uint_as_float(src[4]), __uint_as_float(src[5]), __uint_as_float(src[6]),
-                                    __uint_as_float(src[7]), rbar);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(src[0]), "r"(src[1]),
+                                     "r"(src[2]), "r"(src[3])
+                                     : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16), "r"(src[4]), "r"(src[5]),
+                                     "r"(src[6]), "r"(src[7])
+                                     : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    bar_epilogue();
+                    if (et == 0) {
+                        // every owner's buffer must be free of the previous unit (each said so when it was done)
+                        if (a == 0 && un >= 1) W.wait(xfree_addr, (un - 1) & 1u, 508, true);
+                        const uint32_t off = x_base + (rank * 2u + static_cast<uint32_t>(a)) * kXPart;
+                        for (int o = 0; o < kCluster; ++o)
+                            bulk_copy_to_peer(map_to_rank(off, o), send_base + static_cast<uint32_t>(o) * kXPart, kXPart,
+                                              map_to_rank(xfull_addr, o));
+                        bulk_commit();
                     }
                 }
                 tc_fence_before();
@@ -585,11 +646,11 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
                     }
                 }
 
-                // ---- this CTA's exchange buffer is free again: arm it for the next unit, tell the cluster ----
+                // ---- this CTA's exchange buffer is free again: arm it for the next unit, then tell the cluster ----
                 bar_epilogue();
                 if (et == 0) {
-                    int nq = q, nu = u + nclusters;
-                    if (nu >= ph.units) {
+                    int nq = q;
+                    if (u + nclusters >= ph.units) {
                         for (nq = q + 1; nq < 4; ++nq)
                             if (p.ph[nq].kind != kPhaseNone && cid < p.ph[nq].units) break;
                     }
@@ -602,6 +663,7 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_consta
             bool more = false;
             for (int nq = q + 1; nq < 4; ++nq) more = more || p.ph[nq].kind != kPhaseNone;
             if (more) {
+                fence_proxy_async_all();   // this phase's global stores may be read by TMA in the next one
                 bar_epilogue();
                 if (et == 0) {
                     unsigned* cnt = p.grid_bar + 2 * q;
@@ -707,6 +769,13 @@ int launch_decode_chain(const DecodeChainArgs& a, cudaStream_t stream) {
     p.ph[0].kb_total = qd / kBK;
     p.ph[0].b_src = static_cast<const __nv_bfloat16*>(a.attn_out);
     p.ph[0].ldb = qd;
+    CUtensorMap tmb[2];
+    if ((err = cached_tmap(&tmb[0], a.attn_out, static_cast<uint64_t>(qd), static_cast<uint64_t>(a.tokens),
+                           static_cast<uint64_t>(qd) * 2, kBK, kNT)) != B200_OK)
+        return err;
+    if ((err = cached_tmap(&tmb[1], a.mlp_act, static_cast<uint64_t>(a.inter), static_cast<uint64_t>(a.tokens),
+                           static_cast<uint64_t>(a.inter) * 2, kBK, kNT)) != B200_OK)
+        return err;
     // phase 1: gate_up of normalised sums
     if ((err = wmap(1, a.w_gate_up, 2 * a.inter, a.hidden)) != B200_OK) return err;
     p.ph[1].kind = kPhaseGated;
@@ -763,8 +832,14 @@ int launch_decode_chain(const DecodeChainArgs& a, cudaStream_t stream) {
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kSmemBytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, dim3(kCluster, 1, 1), tm[0],
-                                  tm[1], tm[2], tm[3], p));
+                                  tm[1], tm[2], tm[3], tmb[0], tmb[1], p));
     return B200_OK;
 }
 
 }  // namespace b200
+
+extern "C" {
+
+int b200_decode_chain_grid(void) { return b200::decode_chain_max_grid(); }
+
+}  // extern "C"

@@ -170,7 +170,11 @@ struct b200_engine {
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
     void* chain_scratch = nullptr;  // fp32 sums, partial sums of squares and barrier words of the decode layer chain
-    bool use_chain = true;  // B200_DECODE_CHAIN=0: decode steps run one kernel per operator, as prefill steps do
+    // B200_DECODE_CHAIN=1: decode steps run everything between two attention launches as one
+    // persistent kernel (decode_chain.cu).  Off by default: measured on B200 it is the slower of the
+    // two paths (each of its phases pays several ~1 us round trips to L2 that separate launches hide
+    // behind one another under programmatic dependent launch).
+    bool use_chain = false;
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
     bool kv_evict_first = true;  // B200_KV_EVICT_FIRST=0: K/V loads with the default L2 policy
     // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
