@@ -291,6 +291,18 @@ B200_API int b200_sample(int32_t* out, const void* logits, int rows, int vocab, 
                          const uint64_t* seeds, uint64_t step_index, uint8_t* candidate_mask,
                          b200_stream_t stream);
 
+/* flashinfer_sample_from_probs / _top_k_ / _top_p_ / _top_k_top_p_sample_from_probs
+ * (include/sglang/engine/sampling.h:12-34; src/engine/sampling.cu:65-192): one token per row of
+ * fp32 probabilities [rows, vocab] (contiguous), drawn with the caller's uniform number
+ * uniform[row] in [0, 1) by inverse CDF over the tokens FlashInfer's rejection samplers accept:
+ * those among the top_k largest probabilities (ties included) whose strictly larger probabilities
+ * sum to less than top_p.  top_k / top_p: per-row device arrays, or NULL to use the scalar
+ * (top_k_value < 1 or >= vocab and top_p_value >= 1 switch the filter off).  Always succeeds (the
+ * reference's `success` flags are all true).  Reproducible: masses are summed in fixed point. */
+B200_API int b200_sample_from_probs(int32_t* out, const float* probs, int rows, int vocab,
+                                    const int32_t* top_k, int top_k_value, const float* top_p,
+                                    float top_p_value, const float* uniform, b200_stream_t stream);
+
 /* ---- tensor-parallel all-reduce (include/sglang/distributed/distributed.h:24) --- */
 
 /* One process per GPU.  A communicator owns this rank's two exchange buffers (call parity 0 / 1)

@@ -240,6 +240,36 @@ def sample_row_distribution(logits: torch.Tensor, temperature: float, top_k: int
     return torch.softmax(logits, -1)
 
 
+def sample_from_probs(probs: torch.Tensor, u: float, top_k: int = 0, top_p: float = 1.0):
+    """What flashinfer_*_sample_from_probs return in distribution (src/engine/sampling.cu:65-192 call
+    FlashInfer v0.2.0.post1's SamplingFromProb / TopK / TopP / TopKTopPSamplingFromProb, which is not
+    under the reference tree; this restates its published rejection rule): a token is accepted when
+    fewer than top_k probabilities are strictly larger than its own and those strictly larger
+    probabilities sum to less than top_p; the draw is by inverse CDF over the accepted tokens in
+    index order with the uniform number u.  Returns (token, accepted mask)."""
+    p = probs.to(torch.float64)
+    n = p.numel()
+    order = torch.argsort(p, descending=True, stable=True)
+    sp = p[order]
+    # for each sorted entry: how many and how much mass is strictly larger (ties share the first rank)
+    first_of_value = torch.searchsorted(-sp, -sp, right=False)
+    csum = torch.cat([torch.zeros(1, dtype=torch.float64), torch.cumsum(sp, 0)])
+    larger_count = first_of_value
+    larger_mass = csum[first_of_value]
+    ok = torch.ones(n, dtype=torch.bool)
+    if 0 < top_k < n:
+        ok &= larger_count < top_k
+    if top_p < 1.0:
+        ok &= larger_mass < top_p
+    accepted = torch.zeros(n, dtype=torch.bool)
+    accepted[order[ok]] = True
+    w = torch.where(accepted, p, torch.zeros_like(p))
+    c = torch.cumsum(w, 0)
+    target = u * c[-1]
+    token = int(torch.searchsorted(c, target, right=True).clamp(max=n - 1))
+    return token, accepted
+
+
 # --------------------------------------------------------------------------- model
 @dataclass
 class ModelConfig:

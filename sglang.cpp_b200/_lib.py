@@ -70,6 +70,7 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_attention_prefill": (_I, [_P, _P, _L, _L, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "b200_argmax": (_I, [_P, _P, _I, _I, _L, _P]),
     "b200_sample": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, ctypes.c_uint64, _P, _P]),
+    "b200_sample_from_probs": (_I, [_P, _P, _I, _I, _P, _I, _P, _F, _P, _P]),
     "b200_comm_create": (_I, [_I, _I, _L, POINTER(c_void_p)]),
     "b200_comm_handle_bytes": (_I, []),
     "b200_comm_export": (_I, [_P, _P]),

@@ -425,6 +425,21 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor, top_k: Optional[tor
     return (out, mask) if return_mask else out
 
 
+def sample_from_probs(probs: torch.Tensor, uniform: torch.Tensor, top_k: Optional[torch.Tensor] = None,
+                      top_p: Optional[torch.Tensor] = None, top_k_value: int = 0,
+                      top_p_value: float = 1.0) -> torch.Tensor:
+    """flashinfer_*_sample_from_probs (include/sglang/engine/sampling.h:12-34): fp32 probs
+    [rows, vocab], one uniform number per row, optional per-row top_k (int32) / top_p (fp32)."""
+    _check(probs.is_cuda and probs.dtype == torch.float32 and probs.dim() == 2 and probs.is_contiguous(),
+           "probs must be a contiguous CUDA float32 tensor [batch, vocab]")
+    _check(uniform.is_cuda and uniform.dtype == torch.float32 and uniform.numel() >= probs.size(0),
+           "uniform_samples must be CUDA float32 with one number per row")
+    out = torch.empty(probs.size(0), dtype=torch.int32, device=probs.device)
+    call("b200_sample_from_probs", out.data_ptr(), probs.data_ptr(), probs.size(0), probs.size(1), _ptr(top_k),
+         top_k_value, _ptr(top_p), top_p_value, uniform.data_ptr(), _stream())
+    return out
+
+
 def read_device_status() -> tuple[int, int]:
     import ctypes
     buf = (ctypes.c_int32 * 2)()

@@ -103,3 +103,55 @@ def test_greedy_rows_inside_a_sampled_batch(L):
     am = lg.float().argmax(-1)
     assert tok[0] == am[0] and tok[2] == am[2]
     assert mask[0].sum() == 1 and mask[2].sum() == 1
+
+
+# ---- sampling from probabilities (the reference's device path: flashinfer_*_sample_from_probs) -----
+def _probs(rows, vocab, seed, sharp=3.0):
+    gen = torch.Generator().manual_seed(seed)
+    return torch.softmax(torch.randn(rows, vocab, generator=gen) * sharp, -1).contiguous()
+
+
+def test_sample_from_probs_known_answers(L):
+    """tests/engine/test_sampler.cpp:92-109 (top_k = 1 samples the argmax whatever the uniform
+    number) and the no-filter form on a one-hot row."""
+    probs = _probs(5, 1000, 1)
+    u = torch.tensor([0.0, 0.3, 0.5, 0.9, 0.999], device="cuda")
+    k = torch.ones(5, dtype=torch.int32, device="cuda")
+    got = L.sample_from_probs(probs.cuda(), u, top_k=k)
+    assert got.cpu().tolist() == probs.argmax(-1).tolist()
+    one_hot = torch.zeros(2, 64)
+    one_hot[0, 17] = 1.0
+    one_hot[1, 63] = 1.0
+    got = L.sample_from_probs(one_hot.cuda(), torch.tensor([0.7, 0.2], device="cuda"))
+    assert got.cpu().tolist() == [17, 63]
+
+
+@pytest.mark.parametrize("vocab,k,p", [(1000, 0, 1.0), (1000, 50, 1.0), (1000, 0, 0.9), (1000, 20, 0.8),
+                                       (151936, 50, 0.9), (4099, 3, 0.5)])
+def test_sample_from_probs_matches_the_rejection_rule(L, vocab, k, p):
+    rows = 6
+    probs = _probs(rows, vocab, vocab + k)
+    us = torch.tensor([0.0, 0.11, 0.37, 0.5, 0.83, 0.9999], dtype=torch.float32)
+    tk = torch.full((rows,), k if k > 0 else vocab, dtype=torch.int32)
+    tp = torch.full((rows,), p, dtype=torch.float32)
+    got = L.sample_from_probs(probs.cuda(), us.cuda(), tk.cuda(), tp.cuda()).cpu().tolist()
+    for r in range(rows):
+        want, accepted = O.sample_from_probs(probs[r], float(us[r]), k, p)
+        assert bool(accepted[got[r]]), f"row {r}: token {got[r]} is outside the accepted set"
+        if got[r] != want:
+            # the inverse CDF lands within rounding of a boundary between two neighbouring accepted tokens
+            idx = accepted.nonzero().flatten().tolist()
+            assert abs(idx.index(got[r]) - idx.index(want)) <= 1, (r, got[r], want)
+    # scalar filter arguments give the same tokens as per-row arrays
+    again = L.sample_from_probs(probs.cuda(), us.cuda(), None, None, k, p).cpu().tolist()
+    assert again == got
+
+
+def test_sample_from_probs_follows_the_distribution(L):
+    probs = _probs(1, 32, 9, sharp=1.0)
+    n = 8192
+    gen = torch.Generator().manual_seed(0)
+    u = torch.rand(n, generator=gen)
+    got = L.sample_from_probs(probs.repeat(n, 1).contiguous().cuda(), u.cuda()).cpu()
+    freq = torch.bincount(got.long(), minlength=32).float() / n
+    assert float((freq - probs[0]).abs().max()) < 0.02
