@@ -432,8 +432,13 @@ B200_API int b200_engine_load(b200_engine* engine, const char* name, int layer, 
 B200_API int b200_engine_write_table(b200_engine* engine, int which, const int32_t* rows,
                                      const int32_t* positions, const int32_t* values, int64_t count);
 
-/* GraphRunner::capture_graphs (src/engine/engine.cc:670-730): captures one CUDA graph per padded
- * decode batch size; later decode steps whose num_padded_reqs matches replay it. */
+/* GraphRunner::capture_graphs (src/engine/engine.cc:670-730): captures CUDA graphs per padded decode
+ * batch size — one that ends in argmax and one that ends in the sampling kernel (the reference
+ * samples outside its graph, src/engine/engine.cc:504-523; here the sampling parameters and the
+ * step index live in device memory, so the sampled step replays too).  batch_sizes NULL or count 0:
+ * the reference's default list 1, 2, 4, 8, 16, ... and max_running_req (determine_batch_sizes,
+ * :592-616).  A later decode step runs at the smallest captured size >= its num_padded_reqs
+ * (GraphRunner::pad_batch, :628-645): the step runner adds dummy-request rows itself. */
 B200_API int b200_engine_capture_graphs(b200_engine* engine, const int32_t* batch_sizes, int count);
 
 /* Engine::forward_batch (src/engine/engine.cc:495-544) together with the device half of

@@ -157,8 +157,9 @@ struct b200_engine {
     bool meta_in_flight = false, scatter_in_flight = false;
     int* status = nullptr;
 
-    std::map<int, cudaGraphExec_t> graphs;  // padded decode batch size -> graph
-    std::map<int, int> graph_launches;      // kernels inside each captured graph
+    std::map<int, cudaGraphExec_t> graphs;          // padded decode batch size -> graph ending in argmax
+    std::map<int, cudaGraphExec_t> graphs_sampled;  // ... ending in the sampling kernel
+    std::map<int, int> graph_launches;              // kernels inside each captured graph
 
     // Optional per-kernel timing of the attention launches of eager steps.
     bool profile_attention = false;
@@ -177,8 +178,10 @@ struct b200_engine {
     bool use_chain = false;
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
     bool kv_evict_first = true;  // B200_KV_EVICT_FIRST=0: K/V loads with the default L2 policy
-    // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.
+    // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.  The 64-bit step
+    // index follows them, so a captured graph reads a fresh one on every replay.
     static int seed_offset(int Bp) { return (7 * Bp + 1 + 1) & ~1; }
+    static int step_index_offset(int Bp) { return seed_offset(Bp) + 2 * Bp; }
 };
 
 namespace {
@@ -454,7 +457,8 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                reinterpret_cast<const float*>(sp), sp + Bp,
                                reinterpret_cast<const float*>(sp + 2 * Bp),
                                reinterpret_cast<const uint64_t*>(e->meta_dev + e->seed_offset(Bp)), step_index,
-                               nullptr, s));
+                               nullptr, s,
+                               reinterpret_cast<const uint64_t*>(e->meta_dev + e->step_index_offset(Bp))));
     } else {
         B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s));
     }
@@ -471,23 +475,28 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     return B200_OK;
 }
 
-// Fills the pinned staging block for a step; returns T and the longest extend length.
-int stage_step(b200_engine* e, const b200_step* st, int* T_out, int* max_ext_out) {
-    const int Bp = st->num_padded_reqs, B = st->num_reqs;
+// Fills the pinned staging block for a step of Bp padded requests; returns T and the longest extend
+// length.  Rows past st->num_padded_reqs (the step runner padding a decode batch up to a captured
+// graph size, GraphRunner::pad_batch, src/engine/engine.cc:628-645) are the dummy request: its table
+// row, no cached tokens, one token, nothing written back.
+int stage_step(b200_engine* e, const b200_step* st, int Bp, int* T_out, int* max_ext_out) {
+    const int B = st->num_reqs, Bc = st->num_padded_reqs;
     int32_t* mh = e->meta_host;
     int T = 0, max_ext = 0;
     for (int i = 0; i < Bp; ++i) {
-        mh[i] = st->table_idx[i];
-        mh[Bp + i] = st->cached_lens[i];
+        const bool own = i < Bc;
+        const int ext = own ? st->extend_lens[i] : 1;
+        const int cached = own ? st->cached_lens[i] : 0;
+        mh[i] = own ? st->table_idx[i] : e->c.max_running_req;
+        mh[Bp + i] = cached;
         mh[2 * Bp + i] = T;
-        const int ext = st->extend_lens[i];
         if (ext < 0) {
             set_last_error("step: extend_lens[%d] is negative", i);
             return B200_ERR_INVALID_ARGUMENT;
         }
-        if (st->cached_lens[i] < 0 || st->cached_lens[i] + ext > e->pt_cols) {
-            set_last_error("step: request %d needs %d positions, the page table has %d columns", i,
-                           st->cached_lens[i] + ext, e->pt_cols);
+        if (cached < 0 || cached + ext > e->pt_cols) {
+            set_last_error("step: request %d needs %d positions, the page table has %d columns", i, cached + ext,
+                           e->pt_cols);
             return B200_ERR_INVALID_ARGUMENT;
         }
         T += ext;
@@ -510,6 +519,7 @@ int stage_step(b200_engine* e, const b200_step* st, int* T_out, int* max_ext_out
             tp[i] = pp < 1e-6f ? 1e-6f : (pp > 1.f ? 1.f : pp);
             sd[i] = (i < B && st->seeds) ? st->seeds[i] : static_cast<uint64_t>(i);
         }
+        *reinterpret_cast<uint64_t*>(mh + b200_engine::step_index_offset(Bp)) = st->step_index;
     }
     *T_out = T;
     *max_ext_out = max_ext;
@@ -683,6 +693,7 @@ int b200_engine_destroy(b200_engine* e) {
     if (!e) return B200_OK;
     if (e->stream) cudaStreamSynchronize(e->stream);
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& g : e->graphs_sampled) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
     for (cudaEvent_t ev : e->prof_events_ar) cudaEventDestroy(ev);
     if (e->comm) b200_comm_destroy(e->comm);
@@ -763,43 +774,55 @@ int b200_engine_write_table(b200_engine* e, int which, const int32_t* rows, cons
 }
 
 int b200_engine_capture_graphs(b200_engine* e, const int32_t* batch_sizes, int count) {
-    B200_CHECK_ARG(e && (count == 0 || batch_sizes), "engine_capture_graphs: NULL argument");
-    for (int i = 0; i < count; ++i) {
-        const int Bp = batch_sizes[i];
+    B200_CHECK_ARG(e && count >= 0, "engine_capture_graphs: NULL engine or negative count");
+    std::vector<int> sizes;
+    if (count == 0 || batch_sizes == nullptr) {
+        // GraphRunner::determine_batch_sizes (src/engine/engine.cc:592-616): 1, 2, 4, 8, ... and the maximum
+        const int mx = e->c.max_running_req;
+        for (int bs : {1, 2, 4}) if (bs <= mx) sizes.push_back(bs);
+        for (int bs = 8; bs <= mx; bs *= 2) sizes.push_back(bs);
+        if (sizes.empty() || sizes.back() != mx) sizes.push_back(mx);
+    } else {
+        sizes.assign(batch_sizes, batch_sizes + count);
+    }
+    for (int Bp : sizes) {
         B200_CHECK_ARG(Bp >= 1 && Bp <= e->max_batch, "engine_capture_graphs: batch size %d out of range", Bp);
-        if (e->graphs.count(Bp)) continue;
-        // Warm-up + capture run on the dummy request only (GraphRunner::capture_graphs does the
-        // same): every row is the dummy row, one key each, nothing is written back.
-        B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
-        int32_t* mh = e->meta_host;
-        for (int j = 0; j < Bp; ++j) {
-            mh[j] = e->c.max_running_req;
-            mh[Bp + j] = 0;
-            mh[2 * Bp + j] = j;
+        for (int variant = 0; variant < 2; ++variant) {   // 0: ends in argmax; 1: ends in the sampling kernel
+            auto& graphs = variant ? e->graphs_sampled : e->graphs;
+            if (graphs.count(Bp)) continue;
+            // Warm-up + capture run on the dummy request only (GraphRunner::capture_graphs does the
+            // same): every row is the dummy row, one key each, nothing is written back.
+            B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+            b200_step st = {};
+            st.phase = B200_PHASE_DECODE;
+            st.num_reqs = 0;
+            st.num_padded_reqs = 0;      // every row is padding
+            const float one = 1.0f;
+            st.temperatures = variant ? &one : nullptr;   // non-NULL only switches the staging of sampling fields on
+            int T = 0, max_ext = 0;
+            B200_TRY(stage_step(e, &st, Bp, &T, &max_ext));
+            const size_t bytes = (variant ? b200_engine::step_index_offset(Bp) + 2 : 4 * Bp + 1) * sizeof(int32_t);
+            B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, bytes, cudaMemcpyHostToDevice, e->stream));
+            B200_TRY(enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1, variant != 0));  // eager warm-up
+            B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+            cudaGraph_t graph = nullptr;
+            B200_CHECK_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+            e->capturing = true;
+            int err = enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1, variant != 0);
+            e->capturing = false;
+            cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+            if (err != B200_OK) {
+                if (graph) cudaGraphDestroy(graph);
+                return err;
+            }
+            B200_CHECK_CUDA(ce);
+            cudaGraphExec_t exec = nullptr;
+            ce = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            B200_CHECK_CUDA(ce);
+            graphs[Bp] = exec;
+            e->graph_launches[Bp] = e->launches_last_step;
         }
-        mh[3 * Bp] = Bp;
-        for (int j = 0; j < Bp; ++j) mh[3 * Bp + 1 + j] = -1;
-        B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, mh, (4 * Bp + 1) * sizeof(int32_t),
-                                        cudaMemcpyHostToDevice, e->stream));
-        B200_TRY(enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1));  // eager warm-up
-        B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
-        cudaGraph_t graph = nullptr;
-        B200_CHECK_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
-        e->capturing = true;
-        int err = enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1);
-        e->capturing = false;
-        cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
-        if (err != B200_OK) {
-            if (graph) cudaGraphDestroy(graph);
-            return err;
-        }
-        B200_CHECK_CUDA(ce);
-        cudaGraphExec_t exec = nullptr;
-        ce = cudaGraphInstantiate(&exec, graph, 0);
-        cudaGraphDestroy(graph);
-        B200_CHECK_CUDA(ce);
-        e->graphs[Bp] = exec;
-        e->graph_launches[Bp] = e->launches_last_step;
     }
     return B200_OK;
 }
@@ -816,27 +839,35 @@ int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_h
         B200_CHECK_CUDA(cudaEventSynchronize(e->ev_meta_done));
         e->meta_in_flight = false;
     }
+    // A decode batch runs at the next captured size (GraphRunner::pad_batch takes the lower bound of the
+    // captured sizes, src/engine/engine.cc:628-645): rows the caller did not pad are padded here.
+    auto& graphs = sampling ? e->graphs_sampled : e->graphs;
+    int Bg = Bp;
+    if (st->phase == B200_PHASE_DECODE && !e->profile_attention) {
+        auto it = graphs.lower_bound(Bp);
+        if (it != graphs.end()) Bg = it->first;
+    }
     int T = 0, max_ext = 0;
-    B200_TRY(stage_step(e, st, &T, &max_ext));
+    B200_TRY(stage_step(e, st, Bg, &T, &max_ext));
     B200_CHECK_ARG(T <= e->max_tokens, "engine_step: %d tokens exceed max_extend_tokens %d", T, e->max_tokens);
     if (st->phase == B200_PHASE_DECODE)
-        B200_CHECK_ARG(T == Bp, "engine_step: a decode step runs exactly one token per request");
+        B200_CHECK_ARG(T == Bg, "engine_step: a decode step runs exactly one token per request");
 
     cudaStream_t s = e->stream;
     B200_CHECK_CUDA(cudaEventRecord(e->ev_step_begin, s));
-    const size_t meta_bytes = (sampling ? b200_engine::seed_offset(Bp) + 2 * Bp : 4 * Bp + 1) * sizeof(int32_t);
+    const size_t meta_bytes =
+        (sampling ? b200_engine::step_index_offset(Bg) + 2 : 4 * Bg + 1) * sizeof(int32_t);
     B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, meta_bytes, cudaMemcpyHostToDevice, s));
     B200_CHECK_CUDA(cudaEventRecord(e->ev_meta_done, s));
     e->meta_in_flight = true;
-    // A captured graph covers all Bp rows; padded rows carry write_pos = -1 so nothing of
+    // A captured graph covers all Bg rows; padded rows carry write_pos = -1 so nothing of
     // theirs is written back, and only the first B tokens are copied out.
-    auto g = st->phase == B200_PHASE_DECODE ? e->graphs.find(Bp) : e->graphs.end();
-    // Sampled steps run the eager sequence: the captured graphs end in the argmax kernel.
-    if (g != e->graphs.end() && !e->profile_attention && !sampling) {
+    auto g = st->phase == B200_PHASE_DECODE ? graphs.find(Bg) : graphs.end();
+    if (g != graphs.end() && !e->profile_attention) {
         B200_CHECK_CUDA(cudaGraphLaunch(g->second, s));
-        e->launches_last_step = e->graph_launches[Bp];
+        e->launches_last_step = e->graph_launches[Bg];
     } else {
-        B200_TRY(enqueue_forward(e, st->phase, B, Bp, T, max_ext, sampling, st->step_index));
+        B200_TRY(enqueue_forward(e, st->phase, B, Bg, T, max_ext, sampling, st->step_index));
     }
     if (next_tokens_host && B > 0)
         B200_CHECK_CUDA(cudaMemcpyAsync(next_tokens_host, e->next_tokens, B * sizeof(int32_t),

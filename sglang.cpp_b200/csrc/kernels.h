@@ -23,9 +23,12 @@ int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weig
 int launch_act_and_mul(void* out, const void* in, int tokens, int d, bool gelu, cudaStream_t stream);
 int launch_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
                      int vocab, int* status, cudaStream_t stream);
+// step_index_dev (optional): the step index is read from device memory instead of the argument, so a
+// captured graph replays with a new value.
 int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   const float* temperatures, const int32_t* top_k, const float* top_p,
-                  const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream);
+                  const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream,
+                  const uint64_t* step_index_dev = nullptr);
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   cudaStream_t stream);
 

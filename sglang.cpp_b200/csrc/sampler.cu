@@ -1,5 +1,5 @@
-// Token selection from logits: greedy argmax and the single-pass
-// temperature / top-k / top-p sampler.
+// Token selection from logits: greedy argmax and the sort-free temperature / top-k / top-p sampler
+// (a full-resolution count histogram of the 16-bit keys in shared memory).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -119,21 +119,40 @@ int b200_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t l
 // ============================================================================
 // Temperature / top-k / top-p sampling without a sort.
 //
-// The logits are bf16, so their order-preserving 16-bit keys take at most 65536
-// values and equal keys are exact ties.  Top-k is "the k-th largest key" and
-// top-p is "the key below which the cumulative mass first exceeds p"; both are
-// found by a 16-step bitwise search whose probe is one pass over the row (which
-// stays in L2) with a fixed-order block reduction, so the result is exact and
-// deterministic.  The kept set always has the form
+// The logits are bf16, so their order-preserving 16-bit keys take at most 65536 values and equal
+// keys are exact ties: a histogram of COUNTS at full key resolution holds everything the filters
+// need, because the softmax weight is a function of the key alone,
+//     w(key) = exp2((value(key) - max) / T * log2 e)   in 40-bit fixed point,
+// so the mass at or above any key is sum(count[key'] * w(key')) and never depends on the order of
+// the atomic adds.  The kept set is therefore exact, reproducible and the same on every rank of a
+// tensor-parallel group.  It always has the form
 //     key > thr   or   (key == thr and it is among the first n_eq such by index),
-// which is how sample_row's sort-based definition reads when ties are ordered by
-// index.  One last pass in index order draws from the kept set with a Philox
-// uniform.  One CTA of 1024 threads per row.
+// which is how sample_row's sort-based definition (src/engine/engine.cc:126-158) reads when ties
+// are ordered by index.
+//
+// A cluster of two CTAs owns a row.  Both read the whole row once (the second read hits L2); the
+// first CTA counts the upper half of the key space (non-negative logits), the second the lower
+// half, each into a 32768-bin shared-memory histogram - the halves are disjoint, so nothing is
+// merged.  Counting at full resolution also spreads the adds: logits crowd into a handful of
+// exponents, but into hundreds of distinct bf16 values, so lanes of one warp rarely meet in a bin.
+// Every thread then owns 32 consecutive bins in descending key order; one block-wide scan of
+// (count, mass) plus the other half's totals tells each thread what lies above its bins, and the one
+// thread whose bins hold the k-th largest key (then the one whose bins cross p * Z) walks them and
+// posts the threshold to both CTAs.  A last pass in index order, each CTA over half of the row,
+// draws from the kept set with a Philox uniform.
 // ============================================================================
 namespace b200 {
 namespace {
 
 constexpr int kSampleThreads = 1024;
+constexpr int kSampleWarps = kSampleThreads / 32;
+constexpr int kSampleCluster = 2;
+constexpr int kHalfBins = 32768;                               // keys per half of the key space
+constexpr int kBinsPerThread = kHalfBins / kSampleThreads;     // 32
+constexpr int kHistWords = kHalfBins + kHalfBins / 32;         // one pad word per 32 bins: a thread's run of
+                                                               // 32 bins starts in a different bank than its neighbour's
+constexpr float kFixedOne = 1099511627776.0f;  // 2^40
+static_assert(kBinsPerThread == 32, "bin ownership assumes 32 bins per thread");
 
 __device__ __forceinline__ uint32_t order_key(uint32_t bits16) {
     return (bits16 & 0x8000u) ? (~bits16 & 0xffffu) : (bits16 | 0x8000u);
@@ -156,294 +175,400 @@ __device__ __forceinline__ uint4 philox4x32(uint4 ctr, uint2 key) {
     return ctr;
 }
 
-struct SampleSmem {
-    float f[32];
-    int i[32];
-    float bcast_f;
-    int bcast_i;
+typedef unsigned long long u64;
+
+// One per CTA; the peer writes its halves of the arrays, the deciding threads write the thresholds
+// into both copies, and every read after a cluster barrier is local.
+struct SampleMeet {
+    uint32_t cnt_total[kSampleCluster];   // keys counted by each half of the key space
+    u64 mass_total[kSampleCluster];
+    uint32_t thr_k;                       // top-k: threshold key, kept ties, mass of the kept set
+    int n_eq_k;
+    u64 z_k;
+    uint32_t thr_p;                       // after top-p
+    int n_eq_p;
+    int eqs[kSampleCluster];              // index halves: keys equal to thr, mass above thr
+    u64 gts[kSampleCluster];
 };
 
-__device__ __forceinline__ float block_sum_f(float v, SampleSmem& sm) {
-    v = warp_sum(v);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();
-    if (lane == 0) sm.f[warp] = v;
-    __syncthreads();
-    float t = sm.f[lane];
-    t = warp_sum(t);
-    return t;
+__device__ __forceinline__ uint32_t map_to_rank(const void* p, int r) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(r));
+    return a;
 }
-__device__ __forceinline__ int block_sum_i(int v, SampleSmem& sm) {
+__device__ __forceinline__ void post_u32(const void* p, uint32_t v) {   // into both CTAs' copies
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();
-    if (lane == 0) sm.i[warp] = v;
-    __syncthreads();
-    int t = sm.i[lane];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    return t;
+    for (int r = 0; r < kSampleCluster; ++r)
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_rank(p, r)), "r"(v) : "memory");
 }
-__device__ __forceinline__ int block_max_i(int v, SampleSmem& sm) {
+__device__ __forceinline__ void post_u64(const void* p, u64 v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();
-    if (lane == 0) sm.i[warp] = v;
-    __syncthreads();
-    int t = sm.i[lane];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t = max(t, __shfl_xor_sync(0xffffffffu, t, o));
-    return t;
+    for (int r = 0; r < kSampleCluster; ++r)
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(map_to_rank(p, r)), "l"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Exclusive prefix over the block in thread order; `total` gets the block sum.
-__device__ __forceinline__ float block_excl_scan_f(float v, float& total, SampleSmem& sm) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float incl = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
-    }
-    __syncthreads();
-    if (lane == 31) sm.f[warp] = incl;
-    __syncthreads();
-    float wsum = sm.f[lane], wincl = wsum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, wincl, o);
-        if (lane >= o) wincl += t;
-    }
-    total = __shfl_sync(0xffffffffu, wincl, 31);
-    const float warp_off = __shfl_sync(0xffffffffu, wincl - wsum, warp);
-    return warp_off + incl - v;
-}
-__device__ __forceinline__ int block_excl_scan_i(int v, int& total, SampleSmem& sm) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int incl = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
-    }
-    __syncthreads();
-    if (lane == 31) sm.i[warp] = incl;
-    __syncthreads();
-    int wsum = sm.i[lane], wincl = wsum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, wincl, o);
-        if (lane >= o) wincl += t;
-    }
-    total = __shfl_sync(0xffffffffu, wincl, 31);
-    const int warp_off = __shfl_sync(0xffffffffu, wincl - wsum, warp);
-    return warp_off + incl - v;
-}
-
-__device__ __forceinline__ void unpack_keys(const uint4& a, uint32_t (&k)[8]) {
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        k[2 * j] = order_key(w[j] & 0xffffu);
-        k[2 * j + 1] = order_key(w[j] >> 16);
-    }
-}
-
-__global__ void __launch_bounds__(kSampleThreads)
+__global__ void __launch_bounds__(kSampleThreads, 1)
 sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logits, int vocab,
               int64_t ld, const float* __restrict__ temps, const int32_t* __restrict__ top_k,
               const float* __restrict__ top_p, const uint64_t* __restrict__ seeds,
-              uint64_t step_index, uint8_t* __restrict__ mask) {
-    __shared__ SampleSmem sm;
-    __shared__ int s_chosen;
+              const uint64_t* __restrict__ step_index_ptr, uint64_t step_index_arg,
+              uint8_t* __restrict__ mask) {
+    extern __shared__ __align__(16) uint32_t s_hist[];   // kHistWords counters; bin b lives at b + b / 32
+    __shared__ SampleMeet meet;
+    __shared__ u64 s_wm[kSampleWarps];
+    __shared__ uint32_t s_wc[kSampleWarps];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x / kSampleCluster, rank = blockIdx.x % kSampleCluster;
+    const uint32_t own_half = rank == 0 ? 1u : 0u;       // the first CTA counts keys >= 0x8000
+    for (int i = tid; i < kHistWords / 4; i += kSampleThreads)
+        reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0u, 0u, 0u, 0u);
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int row = blockIdx.x;
-    const uint4* rv = reinterpret_cast<const uint4*>(logits + static_cast<int64_t>(row) * ld);
-    const int nvec = vocab >> 3;
+    const __nv_bfloat16* rowp = logits + static_cast<int64_t>(row) * ld;
     uint8_t* mrow = mask ? mask + static_cast<int64_t>(row) * vocab : nullptr;
-
-    auto count_ge = [&](uint32_t c) {
-        int n = 0;
-        for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
-            uint32_t k[8];
-            unpack_keys(rv[v], k);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) n += k[e] >= c ? 1 : 0;
-        }
-        return block_sum_i(n, sm);
-    };
-    auto count_eq = [&](uint32_t c) {
-        int n = 0;
-        for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
-            uint32_t k[8];
-            unpack_keys(rv[v], k);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) n += k[e] == c ? 1 : 0;
-        }
-        return block_sum_i(n, sm);
-    };
-
-    // ---- row maximum ----
-    int kmax_local = 0;
-    for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
-        uint32_t k[8];
-        unpack_keys(rv[v], k);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kmax_local = max(kmax_local, static_cast<int>(k[e]));
-    }
-    const uint32_t kmax = static_cast<uint32_t>(block_max_i(kmax_local, sm));
-    const float lmax = key_to_float(kmax);
-
     const float T = temps[row];
-    if (threadIdx.x == 0) s_chosen = -1;
-    __syncthreads();
-    if (T <= 1.0000001e-6f) {
-        // Greedy request inside a sampled batch (Sampler::prepare clamps its temperature to
-        // 1e-6): the distribution is one-hot on the first maximum.
-        int best = -0x7fffffff;
-        for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
-            uint32_t k[8];
-            unpack_keys(rv[v], k);
+    const bool greedy = T <= 1.0000001e-6f;
+    const int nvec = vocab >> 3;                          // the row is whole 16-byte vectors
+    const uint4* rv = reinterpret_cast<const uint4*>(rowp);
+
+    // Exclusive scan over the block, in thread order, of a (count, mass) pair; totals on every thread.
+    auto block_scan = [&](uint32_t c, u64 m, uint32_t& c_excl, u64& m_excl, uint32_t& c_tot, u64& m_tot) {
+        uint32_t ic = c;
+        u64 im = m;
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (k[e] == kmax) best = max(best, -(v * 8 + e));
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t tc = __shfl_up_sync(0xffffffffu, ic, o);
+            const u64 tm = __shfl_up_sync(0xffffffffu, im, o);
+            if (lane >= o) {
+                ic += tc;
+                im += tm;
+            }
         }
-        const int idx = -block_max_i(best, sm);
-        if (threadIdx.x == 0) out[row] = idx;
+        __syncthreads();   // the arrays may still be read from an earlier scan
+        if (lane == 31) {
+            s_wc[warp] = ic;
+            s_wm[warp] = im;
+        }
+        __syncthreads();
+        const uint32_t wc = s_wc[lane];
+        const u64 wm = s_wm[lane];
+        uint32_t pc = wc;
+        u64 pm = wm;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t tc = __shfl_up_sync(0xffffffffu, pc, o);
+            const u64 tm = __shfl_up_sync(0xffffffffu, pm, o);
+            if (lane >= o) {
+                pc += tc;
+                pm += tm;
+            }
+        }
+        c_tot = __shfl_sync(0xffffffffu, pc, 31);
+        m_tot = __shfl_sync(0xffffffffu, pm, 31);
+        c_excl = __shfl_sync(0xffffffffu, pc - wc, warp) + ic - c;
+        m_excl = __shfl_sync(0xffffffffu, pm - wm, warp) + im - m;
+    };
+
+    if (greedy) {
+        // Greedy request inside a sampled batch (Sampler::prepare clamps its temperature to 1e-6): the
+        // distribution is one-hot on the first maximum.  The first CTA does it alone.
+        if (rank != 0) return;
+        uint32_t bk = 0;
+        int bi = 0x7fffffff;
+        for (int v = tid; v < nvec; v += kSampleThreads) {
+            const uint4 a = __ldg(rv + v);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t k = order_key((w[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+                if (k > bk) {          // indices grow along a thread's walk: ">" keeps the first maximum
+                    bk = k;
+                    bi = v * 8 + j;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const uint32_t ok = __shfl_xor_sync(0xffffffffu, bk, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ok > bk || (ok == bk && oi < bi)) {
+                bk = ok;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            s_wc[warp] = bk;
+            s_wm[warp] = static_cast<u64>(bi);
+        }
+        __syncthreads();
+        uint32_t k = s_wc[0];
+        int idx = static_cast<int>(s_wm[0]);
+        for (int w = 1; w < kSampleWarps; ++w) {
+            const uint32_t ok = s_wc[w];
+            const int oi = static_cast<int>(s_wm[w]);
+            if (ok > k || (ok == k && oi < idx)) {
+                k = ok;
+                idx = oi;
+            }
+        }
+        if (idx == 0x7fffffff) idx = 0;
+        if (tid == 0) out[row] = idx;
         if (mrow)
-            for (int i = threadIdx.x; i < vocab; i += kSampleThreads) mrow[i] = i == idx ? 1 : 0;
+            for (int i = tid; i < vocab; i += kSampleThreads) mrow[i] = i == idx ? 1 : 0;
         return;
     }
-    const float scale = 1.4426950408889634f / T;
-    auto weight = [&](uint32_t key) { return exp2f((key_to_float(key) - lmax) * scale); };
-    // Mass of n tied entries (n may be 0, and then the key may be one no entry has).
-    auto tie_mass = [&](int n, uint32_t key) { return n > 0 ? static_cast<float>(n) * weight(key) : 0.f; };
-    auto mass_ge = [&](uint32_t c) {
-        float s = 0.f;
-        for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
-            uint32_t k[8];
-            unpack_keys(rv[v], k);
+    __syncthreads();   // the histogram is cleared
+
+    // ---- the whole row once: count this CTA's half of the key space, take the row maximum ----
+    uint32_t kmax = 0;
+    for (int v0 = tid; v0 < nvec; v0 += 4 * kSampleThreads) {
+        uint4 a[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s += k[e] >= c ? weight(k[e]) : 0.f;
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * kSampleThreads;
+            a[u] = v < nvec ? __ldg(rv + v) : make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);   // key 0
         }
-        return block_sum_f(s, sm);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t w[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t k = order_key((w[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+                kmax = max(kmax, k);
+                // key 0 is the bf16 pattern 0xFFFF (a NaN), never a logit: it is neither counted nor kept
+                if ((k >> 15) == own_half && k != 0u) {
+                    const uint32_t b = k & 0x7fffu;
+                    atomicAdd(&s_hist[b + (b >> 5)], 1u);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    if (lane == 0) s_wc[warp] = kmax;
+    __syncthreads();   // the histogram is complete
+    kmax = s_wc[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    const float lmax = key_to_float(kmax);
+    const float scale = 1.4426950408889634f / T;
+    auto fixed_w = [&](uint32_t key) -> u64 {
+        return static_cast<u64>(exp2f((key_to_float(key) - lmax) * scale) * kFixedOne);
     };
 
-    // ---- top-k: thr = k-th largest key, n_eq = how many of the keys equal to it are kept ----
+    // ---- every thread owns 32 bins in descending key order: thread 0 the largest keys of the half ----
+    const uint32_t key_top = (own_half << 15) | static_cast<uint32_t>(kHalfBins - 1 - kBinsPerThread * tid);
+    const uint32_t* my_bins = s_hist + 33 * (kSampleThreads - 1 - tid) + 31;   // my_bins[-i]: count of key_top - i
+    uint32_t my_cnt = 0;
+    u64 my_mass = 0;
+#pragma unroll 8
+    for (int i = 0; i < kBinsPerThread; ++i) {
+        const uint32_t c = *(my_bins - i);
+        if (c) {
+            my_cnt += c;
+            my_mass += static_cast<u64>(c) * fixed_w(key_top - i);
+        }
+    }
+    uint32_t cnt_excl, cnt_tot;
+    u64 mass_excl, mass_tot;
+    block_scan(my_cnt, my_mass, cnt_excl, mass_excl, cnt_tot, mass_tot);
+    if (tid == 0) {
+        post_u32(&meet.cnt_total[rank], cnt_tot);
+        post_u64(&meet.mass_total[rank], mass_tot);
+    }
+    cluster_barrier();   // (1) both halves' totals are in both CTAs
+    const uint32_t all_cnt = meet.cnt_total[0] + meet.cnt_total[1];
+    const u64 all_mass = meet.mass_total[0] + meet.mass_total[1];
+    // what lies above this thread's bins: the upper half comes first
+    const uint32_t cnt_above = (rank == 0 ? 0u : meet.cnt_total[0]) + cnt_excl;
+    const u64 mass_above = (rank == 0 ? 0ull : meet.mass_total[0]) + mass_excl;
+
+    // ---- top-k: the thread whose bins hold the K-th largest key walks them ----
     int K = top_k ? top_k[row] : vocab;
     if (K < 1 || K > vocab) K = vocab;
-    uint32_t thr = 0;
-    int n_eq;
-    if (K < vocab) {
-        uint32_t v = 0;
-        for (int bit = 15; bit >= 0; --bit) {
-            const uint32_t cand = v | (1u << bit);
-            if (cand <= kmax && count_ge(cand) >= K) v = cand;
+    const float P = top_p ? top_p[row] : 1.0f;
+    const bool want_k = static_cast<uint32_t>(K) < all_cnt;
+    uint32_t thr = 0;        // no filter: every counted key is above 0
+    int n_eq = 0;
+    u64 Z = all_mass;
+    if (want_k) {
+        if (cnt_above < static_cast<uint32_t>(K) && static_cast<uint32_t>(K) <= cnt_above + my_cnt) {
+            uint32_t run_c = cnt_above;
+            u64 run_m = mass_above;
+            for (int i = 0; i < kBinsPerThread; ++i) {
+                const uint32_t c = *(my_bins - i);
+                if (!c) continue;
+                const uint32_t key = key_top - i;
+                const u64 w = fixed_w(key);
+                if (run_c + c >= static_cast<uint32_t>(K)) {
+                    const uint32_t keep = static_cast<uint32_t>(K) - run_c;
+                    post_u32(&meet.thr_k, key);
+                    post_u32(&meet.n_eq_k, keep);
+                    post_u64(&meet.z_k, run_m + static_cast<u64>(keep) * w);
+                    break;
+                }
+                run_c += c;
+                run_m += static_cast<u64>(c) * w;
+            }
         }
-        thr = v;
-        n_eq = min(K - count_ge(thr + 1), count_eq(thr));
-    } else {
-        n_eq = count_eq(0);
+        cluster_barrier();   // (2)
+        thr = meet.thr_k;
+        n_eq = meet.n_eq_k;
+        Z = meet.z_k;
     }
-    // ---- top-p over the top-k set ----
-    float P = top_p ? top_p[row] : 1.0f;
+
+    // ---- top-p inside the top-k set: the largest key t whose "t and above" mass exceeds P * Z; of the
+    //      keys equal to t, as many as still fit under the budget (at least one entry is always kept) ----
     if (P < 1.0f) {
-        const float Z = mass_ge(thr + 1) + tie_mass(n_eq, thr);
-        const float budget = P * Z;
-        uint32_t t = 0;  // largest key whose "this key and above" mass exceeds the budget
-        for (int bit = 15; bit >= 0; --bit) {
-            const uint32_t cand = t | (1u << bit);
-            if (cand > kmax) continue;
-            const float m = cand <= thr ? Z : mass_ge(cand);
-            if (m > budget) t = cand;
+        const u64 budget = static_cast<u64>(static_cast<double>(P) * static_cast<double>(Z));
+        // this thread's mass inside the top-k set; the bins above it are untouched by the top-k cut
+        const uint32_t key_bottom = key_top - (kBinsPerThread - 1);
+        u64 in_set = my_mass;
+        if (want_k) {
+            if (key_top < thr) {
+                in_set = 0;
+            } else if (key_bottom <= thr) {
+                in_set = 0;
+                for (int i = 0; i < kBinsPerThread; ++i) {
+                    const uint32_t c = *(my_bins - i), key = key_top - i;
+                    if (!c || key < thr) continue;
+                    in_set += static_cast<u64>(key == thr ? static_cast<uint32_t>(n_eq) : c) * fixed_w(key);
+                }
+            }
         }
-        if (t < thr) t = thr;
-        const float m_full = t + 1 > kmax ? 0.f : mass_ge(t + 1);
-        const int c_t = t == thr ? n_eq : count_eq(t);
-        int j = c_t > 0 ? static_cast<int>(floorf((budget - m_full) / weight(t))) : 0;
-        j = max(0, min(j, c_t));
-        if (m_full == 0.f && j == 0) j = 1;  // the first sorted entry is never dropped
-        thr = t;
-        n_eq = j;
+        if (in_set > 0 && mass_above <= budget && budget < mass_above + in_set) {
+            u64 run = mass_above;
+            for (int i = 0; i < kBinsPerThread; ++i) {
+                const uint32_t c = *(my_bins - i), key = key_top - i;
+                if (!c || key < thr) continue;
+                const uint32_t c_t = (want_k && key == thr) ? static_cast<uint32_t>(n_eq) : c;
+                const u64 w_t = fixed_w(key);
+                if (run + static_cast<u64>(c_t) * w_t > budget) {
+                    u64 j = w_t > 0 ? (budget - run) / w_t : 0ull;
+                    if (j > c_t) j = c_t;
+                    if (run == 0ull && j == 0ull) j = 1;   // the first sorted entry is never dropped
+                    post_u32(&meet.thr_p, key);
+                    post_u32(&meet.n_eq_p, static_cast<uint32_t>(j));
+                    break;
+                }
+                run += static_cast<u64>(c_t) * w_t;
+            }
+        }
+        cluster_barrier();   // (3)
+        thr = meet.thr_p;
+        n_eq = meet.n_eq_p;
     }
-    const float Zf = mass_ge(thr + 1) + tie_mass(n_eq, thr);
+
+    // ---- one pass in index order, each CTA over half of the row: every thread owns a contiguous run of
+    //      whole 8-key vectors and takes, of its run, the mass above thr and the number of keys equal
+    //      to thr.  Ties are kept in index order, so with the tie counts of everything before it a
+    //      thread knows its kept mass without a second look: gt + w(thr) * clamp(n_eq - ties before, 0, own ties) ----
+    const u64 w_thr = fixed_w(thr);
+    const int vper = (nvec + kSampleCluster - 1) / kSampleCluster;
+    const int s_begin = min(rank * vper, nvec), s_end = min(s_begin + vper, nvec);   // this CTA's vectors
+    const int per_thread = (s_end - s_begin + kSampleThreads - 1) / kSampleThreads;
+    const int v_begin = min(s_begin + tid * per_thread, s_end), v_end = min(v_begin + per_thread, s_end);
+    uint32_t my_eq = 0;
+    u64 my_gt = 0;
+#pragma unroll 4
+    for (int v = v_begin; v < v_end; ++v) {
+        const uint4 a = __ldg(rv + v);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t k = order_key((w[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+            my_eq += k == thr ? 1u : 0u;
+            if (k > thr) my_gt += fixed_w(k);
+        }
+    }
+    uint32_t eq_in_cta, eq_total;
+    u64 gt_in_cta, gt_total;
+    block_scan(my_eq, my_gt, eq_in_cta, gt_in_cta, eq_total, gt_total);
+    if (tid == 0) {
+        post_u32(&meet.eqs[rank], eq_total);
+        post_u64(&meet.gts[rank], gt_total);
+    }
+    cluster_barrier();   // (4) both index halves' totals are in both CTAs; nothing remote is touched after this
+    int eq_before = 0;
+    u64 mass_before = 0, Zf = 0;
+    {
+        int eq_run = 0;
+#pragma unroll
+        for (int r = 0; r < kSampleCluster; ++r) {
+            const int e = meet.eqs[r];
+            const int kept_ties = max(0, min(n_eq - eq_run, e));
+            const u64 m = meet.gts[r] + static_cast<u64>(kept_ties) * w_thr;
+            if (r < rank) {
+                mass_before += m;
+                eq_before += e;
+            }
+            Zf += m;
+            eq_run += e;
+        }
+    }
+    const int eq_rank = eq_before + static_cast<int>(eq_in_cta);                                  // ties before my run
+    const int ties_before_in_cta = max(0, min(n_eq - eq_before, static_cast<int>(eq_in_cta)));   // kept ones of this CTA
+    const int my_kept_ties = max(0, min(n_eq - eq_rank, static_cast<int>(my_eq)));
+    const u64 my_kept = my_gt + static_cast<u64>(my_kept_ties) * w_thr;
+    const u64 lo = mass_before + gt_in_cta + static_cast<u64>(ties_before_in_cta) * w_thr;
 
     // ---- draw ----
     const uint64_t seed = seeds ? seeds[row] : static_cast<uint64_t>(row);
+    const uint64_t step_index = step_index_ptr ? *step_index_ptr : step_index_arg;
     const uint4 rnd = philox4x32(make_uint4(static_cast<uint32_t>(step_index), static_cast<uint32_t>(step_index >> 32), 0u, 0u),
                                  make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32)));
-    const float u01 = static_cast<float>(rnd.x >> 8) * (1.0f / 16777216.0f);  // [0, 1)
-    const float target = u01 * Zf;
-
-    // ---- one pass in index order: membership, optional mask, and the draw ----
-    int run_eq = 0, last_kept = -1;
-    float run_w = 0.f;
-    for (int base = 0; base < nvec; base += kSampleThreads) {
-        const int v = base + threadIdx.x;
-        uint32_t k[8];
-        if (v < nvec) {
-            unpack_keys(rv[v], k);
-        } else {
+    const double u01 = static_cast<double>(rnd.x >> 8) * (1.0 / 16777216.0);  // [0, 1)
+    const u64 target = static_cast<u64>(u01 * static_cast<double>(Zf));       // < Zf: u01 <= 1 - 2^-24
+    if (Zf == 0ull && rank == 0 && tid == 0) out[row] = 0;                    // a row of NaNs: nothing to draw from
+    if (my_kept > 0 && target >= lo && target < lo + my_kept) {
+        // this thread's run holds the target: walk it
+        u64 c = lo;
+        int er = eq_rank, pick = -1;
+        for (int v = v_begin; v < v_end && pick < 0; ++v) {
+            const uint4 a = __ldg(rv + v);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) k[e] = 0xffffffffu;  // matches nothing
-        }
-        int eq_local = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) eq_local += (k[e] == thr) ? 1 : 0;
-        int eq_total;
-        int eq_rank = run_eq + block_excl_scan_i(eq_local, eq_total, sm);
-        float w[8], w_local = 0.f;
-        int my_last = -1;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            bool kept = false;
-            if (v < nvec) {
-                if (k[e] > thr && k[e] != 0xffffffffu) kept = true;
-                else if (k[e] == thr) kept = eq_rank++ < n_eq;
-            }
-            w[e] = kept ? weight(k[e]) : 0.f;
-            w_local += w[e];
-            if (kept) my_last = v * 8 + e;
-            if (mrow && v < nvec) mrow[v * 8 + e] = kept ? 1 : 0;
-        }
-        float w_total;
-        const float w_before = run_w + block_excl_scan_f(w_local, w_total, sm);
-        if (my_last >= 0 && target >= w_before && target < w_before + w_local) {
-            float c = w_before;
-            int pick = my_last;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                if (w[e] > 0.f) {
-                    c += w[e];
-                    if (target < c) {
-                        pick = v * 8 + e;
-                        break;
-                    }
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t k = order_key((w[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+                bool kept = k > thr;
+                if (k == thr) kept = er++ < n_eq;
+                if (kept && pick < 0) {
+                    c += fixed_w(k);
+                    if (target < c) pick = v * 8 + j;
                 }
             }
-            atomicMax(&s_chosen, pick);  // intervals are disjoint: at most one thread gets here
         }
-        last_kept = max(last_kept, my_last);
-        run_eq += eq_total;
-        run_w += w_total;
+        if (pick >= 0) out[row] = pick;
     }
-    const int last_all = block_max_i(last_kept, sm);
-    __syncthreads();
-    if (threadIdx.x == 0) out[row] = s_chosen >= 0 ? s_chosen : max(last_all, 0);
+    if (mrow) {   // candidate mask (tests): membership of every key of the run
+        int er = eq_rank;
+        for (int i = v_begin * 8; i < v_end * 8; ++i) {
+            const uint32_t k = order_key(__bfloat16_as_ushort(rowp[i]));
+            bool kept = k > thr;
+            if (k == thr) kept = er++ < n_eq;
+            mrow[i] = kept ? 1 : 0;
+        }
+    }
 }
 
 }  // namespace
 
 int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   const float* temperatures, const int32_t* top_k, const float* top_p,
-                  const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream) {
+                  const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream,
+                  const uint64_t* step_index_dev) {
     if (rows == 0) return B200_OK;
-    B200_CHECK_CUDA(launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, dim3(1, 1, 1),
-                                  out, static_cast<const __nv_bfloat16*>(logits), vocab, ld, temperatures,
-                                  top_k, top_p, seeds, step_index, mask));
+    const size_t smem = kHistWords * sizeof(uint32_t);
+    B200_CHECK_CUDA(cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+    B200_CHECK_CUDA(launch_kernel(sample_kernel, dim3(rows * kSampleCluster), dim3(kSampleThreads), smem, stream,
+                                  dim3(kSampleCluster, 1, 1), out, static_cast<const __nv_bfloat16*>(logits), vocab,
+                                  ld, temperatures, top_k, top_p, seeds, step_index_dev, step_index, mask));
     return B200_OK;
 }
 
@@ -461,7 +586,7 @@ int b200_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t l
     if (rows == 0) return B200_OK;
     B200_CHECK_ARG(out && logits && temperatures, "sample: NULL tensor");
     return b200::launch_sample(out, logits, rows, vocab, ld, temperatures, top_k, top_p, seeds,
-                               step_index, candidate_mask, static_cast<cudaStream_t>(stream));
+                               step_index, candidate_mask, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 }  // extern "C"

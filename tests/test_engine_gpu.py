@@ -200,27 +200,35 @@ def test_engine_writes_its_own_tokens_back(pkg):
     pr.engine.close()
 
 
-def test_decode_graph_replay_equals_eager(pkg):
-    """A captured decode graph gives bit-identical logits to the eager launch sequence, also when
-    the batch is padded with the dummy request (src/engine/engine.cc:628-645,732-743)."""
+@pytest.mark.parametrize("sampled", [False, True])
+@pytest.mark.parametrize("caller_pads", [True, False])
+def test_decode_graph_replay_equals_eager(pkg, sampled, caller_pads):
+    """A captured decode graph gives bit-identical logits and tokens to the eager launch sequence, also
+    when the batch is padded with the dummy request (src/engine/engine.cc:628-645,732-743) — by the
+    caller, or by the step runner itself, which takes the next captured size as GraphRunner::pad_batch
+    does — and also for sampled steps (temperature / top-k / top-p with per-request seeds): their graph
+    ends in the sampling kernel, which reads its parameters and the step index from device memory."""
     cfg = small_cfg("qwen3")
+    sampling = dict(temperatures=[0.7, 1.0, 0.9], top_k=[50, -1, 5], top_p=[0.9, 1.0, 0.8], seeds=[11, 12, 13]) if sampled else None
     results = []
     for use_graph in (False, True):
         pr = Pair(pkg, cfg, 16)
         rng = np.random.default_rng(5)
         reqs = [pr.hb.add_request(rng.integers(0, cfg.vocab_size, size=n).astype(np.int32), 8) for n in (12, 40, 7)]
         if use_graph:
-            pr.engine.capture_graphs([4])
+            pr.engine.capture_graphs([4] if caller_pads else [])   # [] = the reference's default list: 1, 2, 4, 8
         pr.hb.prefill(reqs).synchronize()
         toks = []
         for _ in range(4):
-            out = pr.hb.decode(reqs, padded_size=4)
+            out = pr.hb.decode(reqs, padded_size=4 if caller_pads or not use_graph else None, sampling=sampling)
             out.synchronize()
             toks.append(out.next_tokens_cpu.clone())
-        results.append((torch.stack(toks), pr.engine.logits(3).clone()))
+        _, _, launches = pr.engine.read_profile()
+        results.append((torch.stack(toks), pr.engine.logits(3).clone(), launches))
         pr.engine.close()
     assert torch.equal(results[0][0], results[1][0])
     assert torch.equal(results[0][1], results[1][1])
+    assert results[0][2] == results[1][2] > 0      # the replay launches what the eager step launches
 
 
 def test_prefix_cache_hit_reuses_pages_and_gives_same_logits(pkg):
