@@ -22,7 +22,9 @@ all N ranks, the fused all-reduce kernels on the data path) and attach it as the
 the part of the path that shards, and the replicas of the headline cannot show it.
 
 Other workloads (not the headline metric): --context N gives every prompt N tokens (the
-"batch 64 / 2048-token context" point); --workload c4 is Llama-3-8B under tensor parallelism and
+"batch 64 / 2048-token context" point); --workload c3 is the prefill-heavy mixed case (8 prompts
+of 4096 tokens prefilled in chunks, alternating with sampled decode steps of 56 running requests:
+prefill tokens/s, decode ms/step, fraction of the tensor-pipe rate); --workload c4 is Llama-3-8B under tensor parallelism and
 --workload c5 Qwen3-30B-A3B under expert parallelism + attention TP over the N ranks (strong
 scaling, weights drawn on the device); --eager / --profile-region / --profile-prefill shape a run
 for a profiler's launch list.
@@ -392,6 +394,190 @@ def run_gpu(args):
         print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------- mixed workload
+def run_gpu_c3(args):
+    """Workload "c3": Qwen3-0.6B, 8 new prompts of 4096 tokens prefilled in chunks while 56 requests
+    at contexts U[128, 8192] (seed 3) keep decoding, everything sampled (temperature 0.7, top-k 50,
+    top-p 0.9, one fixed seed per request).  A batch is prefill or decode, never both
+    (src/scheduler/scheduler.cc:366-388), so a step here is one prefill batch of 8192 tokens (four
+    prompts advancing by one 2048-token chunk: the second chunk attends to the first through the
+    page table) followed by one decode step of the 56 running requests.  After four steps the eight
+    prompts are complete and are wound back to position 0 (they keep their pages), so every timed
+    step does the same amount of work.  Prefill and decode are timed separately with CUDA events on
+    the engine's stream; prefill FLOPs (every linear layer, causal attention) are set against the
+    sustained bf16 rate of a large cuBLAS GEMM on this pool."""
+    import __graft_entry__ as entry
+    from oracle import token_loop_oracle as O
+
+    torch.cuda.set_device(0)
+    pkg = entry.load_package()
+    pkg.load_library()
+    from sglang_cpp_b200.engine import Engine, EngineConfig
+    from sglang_cpp_b200.host_batch import HostBatcher
+
+    cfg = O.qwen3_0_6b()
+    K, W = args.steps, max(args.warmup, 4)
+    n_new, new_len, n_run, chunk, per_step = 8, 4096, 56, args.chunk_tokens, 4
+    chunks_per_prompt = -(-new_len // chunk)
+    cycle = (n_new // per_step) * chunks_per_prompt
+    rng = np.random.default_rng(3)
+    ctx = rng.integers(128, 8192 + 1, size=n_run)
+    total_new = 64 * (K + W) + 64    # every repeat of the timed region continues decoding
+    run_prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).astype(np.int32) for n in ctx]
+    new_prompts = [rng.integers(0, cfg.vocab_size, size=new_len).astype(np.int32) for _ in range(n_new)]
+    max_len = 8192 + total_new + 2
+    num_pages = (sum(math.ceil((len(p) + total_new + 1) / PAGE_SIZE) for p in run_prompts)
+                 + n_new * math.ceil((new_len + 2) / PAGE_SIZE) + 8)
+    engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, n_run + n_new, max_len, MAX_EXTEND_TOKENS))
+    engine.load_weights(O.init_weights(cfg, seed=0, std=0.02))
+    hb = HostBatcher(engine, num_pages, PAGE_SIZE, n_run + n_new, enable_prefix_cache=False)
+
+    def sampling(reqs):
+        return dict(temperatures=[0.7] * len(reqs), top_k=[50] * len(reqs), top_p=[0.9] * len(reqs),
+                    seeds=[1000 + r.table_idx for r in reqs])
+
+    # the 56 running requests reach their contexts by ordinary prefill batches
+    running, batch, tokens = [], [], 0
+    for p in run_prompts:
+        if tokens + len(p) > MAX_EXTEND_TOKENS and batch:
+            hb.prefill(batch, None, sampling(batch)).synchronize()
+            batch, tokens = [], 0
+        r = hb.add_request(p, total_new)
+        running.append(r)
+        batch.append(r)
+        tokens += len(p)
+    if batch:
+        hb.prefill(batch, None, sampling(batch)).synchronize()
+    fresh = [hb.add_request(p, 1) for p in new_prompts]
+    engine.capture_graphs([64])
+
+    stream = torch.cuda.ExternalStream(pkg.load_library().b200_engine_stream(engine._h))
+    state = {"i": 0, "prefill_wall_ms": 0.0, "launches": [0, 0]}
+
+    def one_step(ev=None, wait=False):
+        """Prefill chunk + decode step; `ev` = three events recorded before, between and after."""
+        i = state["i"] % cycle
+        state["i"] += 1
+        group = fresh[(i // chunks_per_prompt) * per_step:(i // chunks_per_prompt + 1) * per_step]
+        if i % chunks_per_prompt == 0:
+            for r in group:                      # wound back: the pages stay
+                r.cached_len, r.device_len, r.is_chunked_prefill = 0, len(r.input_ids), False
+        if ev:
+            ev[0].record(stream)
+        t0 = time.perf_counter()
+        out = hb.prefill(group, chunk, sampling(group))
+        if wait:
+            out.synchronize()
+            _ = out.next_tokens_cpu[0].item()
+            state["prefill_wall_ms"] += (time.perf_counter() - t0) * 1e3
+            state["launches"][0] = engine.read_profile()[2]
+        if ev:
+            ev[1].record(stream)
+        out = hb.decode(running, sampling=sampling(running))
+        if wait:
+            out.synchronize()
+            _ = out.next_tokens_cpu[0].item()
+            state["launches"][1] = engine.read_profile()[2]
+        if ev:
+            ev[2].record(stream)
+
+    def sync():
+        engine.synchronize()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    pre_ms, dec_ms, tot_ms, ctx_sum = [], [], [], []
+    while True:
+        state["i"] = 0
+        for _ in range(W):
+            one_step()
+        sync()
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record(stream)
+        for k in range(K):
+            ctx_sum.append(sum(r.device_len for r in running))
+            one_step(evs[k])
+        last.record(stream)
+        sync()
+        pre_ms += [e[0].elapsed_time(e[1]) for e in evs]
+        dec_ms += [e[1].elapsed_time(e[2]) for e in evs]
+        tot_ms.append(first.elapsed_time(last))
+        if sum(tot_ms) >= args.min_timed_ms or len(tot_ms) >= 16:
+            break
+    # end to end: the host waits for every batch's tokens
+    e2e_ms, e2e_prefill_ms = [], []
+    while True:
+        state["i"] = 0
+        for _ in range(W):
+            one_step(wait=True)
+        sync()
+        state["prefill_wall_ms"] = 0.0
+        t0 = time.perf_counter()
+        for _ in range(K):
+            one_step(wait=True)
+        sync()
+        e2e_ms.append((time.perf_counter() - t0) * 1e3)
+        e2e_prefill_ms.append(state["prefill_wall_ms"])
+        if sum(e2e_ms) >= args.min_timed_ms or len(e2e_ms) >= 16:
+            break
+    clocks = sampler.stop()
+
+    d, L, Hq, Hkv = cfg.head_dim, cfg.num_layers, cfg.num_qo_heads, cfg.num_kv_heads
+    per_layer = (Hq + 2 * Hkv) * d * cfg.hidden_size + cfg.hidden_size * Hq * d + 3 * cfg.intermediate_size * cfg.hidden_size
+    step_tokens = per_step * chunk
+    linear_flops = 2.0 * per_layer * L * step_tokens
+    # causal attention of a chunk at positions [c, c + n): each query meets c + (its offset + 1) keys
+    attn_flops = 0.0
+    for j in range(chunks_per_prompt):
+        c, n = j * chunk, min(chunk, new_len - j * chunk)
+        attn_flops += 4.0 * Hq * d * (n * c + n * (n + 1) / 2) * L * per_step
+    attn_flops /= chunks_per_prompt                              # mean over the steps of a cycle
+    pre = statistics.median(pre_ms)
+    dec = statistics.median(dec_ms)
+    tflops = (linear_flops + attn_flops) / (pre * 1e-3) / 1e12
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tensor_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    hbm_peak, peak_kind = measured_peaks()
+    kv_tok = 2 * Hkv * d * L * 2
+    dec_bytes = 2 * (L * per_layer + cfg.vocab_size * cfg.hidden_size) + statistics.mean(ctx_sum) * kv_tok \
+        + n_run * (kv_tok + cfg.vocab_size * 2)
+    total = statistics.median(tot_ms)
+    line = {
+        "metric": "prefill tokens/s and sampled-decode ms/step, interleaved (Qwen3-0.6B, 8 x 4096 new + 56 running)",
+        "value": round(step_tokens / (pre * 1e-3), 1), "unit": "prefill tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(total / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c3: Qwen3-0.6B, 8 new prompts of 4096 tokens prefilled in %d-token chunks (4 prompts = %d tokens per "
+                               "batch) alternating with decode steps of 56 requests at contexts U[128,8192] seed 3, page size 16, "
+                               "temperature 0.7 / top-k 50 / top-p 0.9 with a fixed seed per request" % (chunk, step_tokens),
+                   "l2": "inputs larger than L2: a decode step streams about %.0f GB of K/V" % (statistics.mean(ctx_sum) * kv_tok / 1e9),
+                   "parallelism": "single GPU"},
+        "prefill": {"ms_per_batch": round(pre, 4), "tokens_per_batch": step_tokens,
+                    "tokens_per_s": round(step_tokens / (pre * 1e-3), 1), "tflops": round(tflops, 1),
+                    "linear_share_of_flops": round(linear_flops / (linear_flops + attn_flops), 3)},
+        "decode": {"ms_per_step": round(dec, 4), "requests": n_run, "mean_context": round(statistics.mean(ctx_sum) / n_run, 1),
+                   "tokens_per_s": round(n_run / (dec * 1e-3), 1), "replayed_graph": "64-row sampled graph (8 dummy rows)",
+                   "achieved_gbs": round(dec_bytes / (dec * 1e-3) / 1e9, 1),
+                   "frac_of_measured_hbm": round(dec_bytes / (dec * 1e-3) / 1e9 / hbm_peak, 4)},
+        # the same loop with the host waiting for every batch's tokens; the prefill share by wall clock
+        "e2e": {"value": round(step_tokens * K / (statistics.median(e2e_prefill_ms) * 1e-3), 1), "unit": "prefill tokens/s",
+                "ms_per_step": round(statistics.median(e2e_ms) / K, 4),
+                "decode_ms_per_step": round((statistics.median(e2e_ms) - statistics.median(e2e_prefill_ms)) / K, 4),
+                "h2d_bytes_per_step": (4 * per_step + 1) * 4 + 16 * per_step + (4 * 64 + 1) * 4 + 16 * 64,
+                "d2h_bytes_per_step": (per_step + n_run) * 4},
+        "gpu_launches": int(sum(state["launches"])) * K,
+        "roofline": {"bound": "tensor", "kernel": "prefill batch (tile GEMMs + prefill attention)", "achieved": round(tflops, 1),
+                     "peak": tensor_peak, "unit": "TFLOP/s", "frac": round(tflops / tensor_peak, 4),
+                     "peak_kind": "measured (sustained cuBLAS bf16)" if peaks else "fallback", "traffic": None},
+        "timed_repeats": len(tot_ms),
+        "clocks": clocks,
+    }
+    engine.close()
+    print(json.dumps(line), flush=True)
+
+
 # ------------------------------------------------------------------------------- TP workload
 def run_gpu_tp(args, dist_ready=False, as_record=False):
     """Workload "c4": Llama-3-8B architecture, bf16, random-init weights drawn on the device,
@@ -514,7 +700,8 @@ def run_gpu_tp(args, dist_ready=False, as_record=False):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": ("c5: Qwen3-30B-A3B decode, batch 256, prompts of 512 random tokens, page size 16, greedy"
                                 if moe else
-                                "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy"),
+                                "c3: Qwen3-0.6B chunked prefill alternating with sampled decode, one GPU; "
+                         "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy"),
                    "parallelism": (f"ep{world}+tp{world}" if moe else f"tp{world}"), "mean_context": mean_ctx,
                    "ranks_in_lockstep": lockstep},
         "step_roofline": {"algorithmic_bytes_per_step_per_gpu": int(bytes_gpu),
@@ -633,8 +820,10 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"],
+    ap.add_argument("--chunk-tokens", type=int, default=2048, help="c3: tokens a prompt advances per prefill batch")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"],
                     help="c2 (default, the headline metric): Qwen3-0.6B decode, replicas when N > 1; "
+                         "c3: Qwen3-0.6B chunked prefill alternating with sampled decode, one GPU; "
                          "c4: Llama-3-8B decode, tensor parallel over the N ranks; "
                          "c5: Qwen3-30B-A3B decode, experts and attention heads split over the N ranks")
     ap.add_argument("--context", type=int, default=0,
@@ -658,6 +847,10 @@ def main():
         run_reference(args)
     elif args.workload in ("c4", "c5"):
         run_gpu_tp(args)
+    elif args.workload == "c3":
+        if args.gpus != 1:
+            raise SystemExit("workload c3 runs on one GPU")
+        run_gpu_c3(args)
     else:
         run_gpu(args)
 
