@@ -288,8 +288,9 @@ def run_gpu(args):
 
     # ---- phase B: end to end, the host waits for every step's tokens ----
     # Driven the way the scheduler's decode loop drives the engine: per step the host arrays cross
-    # the C ABI, the metadata goes host-to-device from pinned memory, the tokens come back and are
-    # waited for.  (DecodeSession keeps the per-step host bookkeeping in vector form.)
+    # the C ABI, the metadata goes host-to-device from pinned memory, the tokens, finish flags and
+    # status words land in the engine's pinned result ring and the host waits on that step's event.
+    # (DecodeSession keeps the per-step host bookkeeping in vector form.)
     from sglang_cpp_b200.host_batch import DecodeSession
     e2e_ms_all, step_ms = [], []
     while True:
@@ -297,13 +298,12 @@ def run_gpu(args):
         for _ in range(W):
             hb.decode(reqs).synchronize()
         barrier()
-        session = DecodeSession(hb, reqs)
+        session = DecodeSession(hb, reqs, ring=True)
         t0 = time.perf_counter()
         for _ in range(K):
             ts = time.perf_counter()
-            toks = session.step()
-            engine.synchronize()
-            _ = toks[0].item()
+            toks, finished = session.wait(session.step())   # this step's event only; tokens and flags in pinned memory
+            _ = int(toks[0]) + int(finished[0])
             step_ms.append((time.perf_counter() - ts) * 1e3)
         barrier()
         ms = (time.perf_counter() - t0) * 1e3
@@ -355,7 +355,7 @@ def run_gpu(args):
                            "repeat_ms_min_max": [round(min(dev_ms_all), 3), round(max(dev_ms_all), 3)]},
         "p50_tpot_ms": round(statistics.median(step_ms), 4),
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": (4 * BATCH + 1) * 4, "d2h_bytes_per_step": BATCH * 4,
+                "h2d_bytes_per_step": (4 * BATCH + 1) * 4, "d2h_bytes_per_step": BATCH * 5 + 16,
                 "ms_per_step": round(e2e_ms / K, 4), "timed_repeats": len(e2e_ms_all)},
         "gpu_launches": int(launches_per_step) * K,
         "roofline": {"bound": "hbm", "kernel": "attention_decode_kernel",

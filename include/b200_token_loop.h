@@ -448,6 +448,26 @@ B200_API int b200_engine_capture_graphs(b200_engine* engine, const int32_t* batc
 B200_API int b200_engine_step(b200_engine* engine, const b200_step* step, int32_t* next_tokens_host);
 B200_API int b200_engine_synchronize(b200_engine* engine);
 
+/* The same step reporting through the engine's result ring instead of a device-to-host copy and a
+ * stream synchronisation: what ForwardOutput's pinned tensor + event (src/engine/engine.cc:526-531)
+ * and the scheduler's per-request finish test (src/scheduler/scheduler.cc:449-455) are in the
+ * reference.  The step's last kernel writes, into pinned host memory, the sampled tokens, one finish
+ * flag per request (1 when write_pos[i] < 0, i.e. the request cannot decode further, or when the
+ * token equals the end-of-sequence id and ignore_eos[i] is 0; a chunked prefill request also has
+ * write_pos < 0 and its flag, like its token, means nothing), and the device status words.
+ * b200_engine_wait blocks on that step's own event only - steps enqueued behind it keep running -
+ * and returns pointers into the slot, valid until b200_engine_result_slots() further steps have
+ * been enqueued; a ticket older than that is refused.  Its return code is the step's:
+ * B200_ERR_TIMEOUT / B200_ERR_INVALID_ARGUMENT as b200_engine_synchronize reports them.
+ * ignore_eos: [num_reqs] or NULL (nobody ignores).  b200_engine_set_eos_token: Engine::eos_token_id
+ * (include/sglang/engine/engine.h:71); negative (the default) = the model has none. */
+B200_API int b200_engine_set_eos_token(b200_engine* engine, int32_t eos_token_id);
+B200_API int b200_engine_result_slots(void);
+B200_API int b200_engine_step_async(b200_engine* engine, const b200_step* step, const uint8_t* ignore_eos,
+                                    int64_t* ticket);
+B200_API int b200_engine_wait(b200_engine* engine, int64_t ticket, const int32_t** tokens,
+                              const uint8_t** finished);
+
 /* Copies the bf16 logits [rows, vocab] of the last step to host memory (synchronous). */
 B200_API int b200_engine_read_logits(b200_engine* engine, void* host, int rows);
 

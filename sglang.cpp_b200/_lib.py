@@ -94,6 +94,10 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_engine_capture_graphs": (_I, [_P, _P, _I]),
     "b200_engine_step": (_I, [_P, _P, _P]),
     "b200_engine_synchronize": (_I, [_P]),
+    "b200_engine_set_eos_token": (_I, [_P, c_int32]),
+    "b200_engine_result_slots": (_I, []),
+    "b200_engine_step_async": (_I, [_P, _P, _P, POINTER(c_int64)]),
+    "b200_engine_wait": (_I, [_P, c_int64, POINTER(c_void_p), POINTER(c_void_p)]),
     "b200_engine_read_logits": (_I, [_P, _P, _I]),
     "b200_engine_stream": (c_void_p, [_P]),
     "b200_engine_last_step_ms": (_I, [_P, POINTER(c_float)]),

@@ -79,6 +79,32 @@ __global__ void scatter_int32_kernel(int32_t* __restrict__ table, int64_t rows, 
     table[rr * stride + pp] = v[i];
 }
 
+// Last kernel of a step that reports through the result ring: the sampled tokens, one finish flag per
+// request (what Scheduler::process_forward_output derives on the host, src/scheduler/scheduler.cc:449-455:
+// the request cannot decode further - the host passed no write position - or the token is the
+// end-of-sequence id and the request does not ignore it), the two device status words and, last, the
+// step's ticket, all written into pinned host memory.
+__global__ void publish_step_kernel(int32_t* __restrict__ tokens_out, uint8_t* __restrict__ finished_out,
+                                    const uint8_t* __restrict__ ignore_eos, int32_t* __restrict__ status_out,
+                                    const int32_t* __restrict__ next_tokens, const int32_t* __restrict__ write_pos,
+                                    const int* __restrict__ status, int B, int eos, unsigned long long ticket) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        const int32_t tok = next_tokens[i];
+        tokens_out[i] = tok;
+        finished_out[i] = (write_pos[i] < 0 || (eos >= 0 && !ignore_eos[i] && tok == eos)) ? 1 : 0;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        status_out[0] = status[0];
+        status_out[1] = status[1];
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned long long*>(status_out + 2) = ticket;
+    }
+}
+
 __global__ void fill_int32_kernel(int32_t* p, int32_t v, int64_t n) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
@@ -170,6 +196,23 @@ struct b200_engine {
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
+
+    // Results of the steps in flight: a ring of pinned, device-mapped slots the last kernel of a step
+    // writes straight into (tokens, finish flags, the device status words, the ticket), one event each.
+    struct ResultSlot {
+        int32_t* tokens = nullptr;         // [max_batch]
+        uint8_t* finished = nullptr;       // [max_batch]
+        uint8_t* ignore_eos = nullptr;     // [max_batch], written by the host before the launch
+        int32_t* status = nullptr;         // [2] + 64-bit ticket behind them
+        cudaEvent_t done = nullptr;
+        int64_t ticket = -1;
+        int num_reqs = 0;
+    };
+    static constexpr int kResultSlots = 4;
+    ResultSlot ring[kResultSlots];
+    uint8_t* ring_host = nullptr;
+    int64_t next_ticket = 0;
+    int32_t eos_token_id = -1;
     void* chain_scratch = nullptr;  // fp32 sums, partial sums of squares and barrier words of the decode layer chain
     // B200_DECODE_CHAIN=1: decode steps run everything between two attention launches as one
     // persistent kernel (decode_chain.cu).  Off by default: measured on B200 it is the slower of the
@@ -673,6 +716,28 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
         return fail(B200_ERR_CUDA);
     }
     E_TRY(named_alloc(e, &e->meta_dev, "step_meta", e->meta_ints, true));
+    {
+        const size_t rows = (static_cast<size_t>(e->max_batch) + 15) & ~size_t(15);
+        const size_t slot_bytes = rows * 4 + rows + rows + 16;
+        if (cudaHostAlloc(reinterpret_cast<void**>(&e->ring_host), slot_bytes * b200_engine::kResultSlots,
+                          cudaHostAllocMapped) != cudaSuccess) {
+            set_last_error("engine_create: pinned result ring allocation failed");
+            return fail(B200_ERR_CUDA);
+        }
+        memset(e->ring_host, 0, slot_bytes * b200_engine::kResultSlots);
+        for (int i = 0; i < b200_engine::kResultSlots; ++i) {
+            uint8_t* base = e->ring_host + slot_bytes * i;
+            auto& slot = e->ring[i];
+            slot.tokens = reinterpret_cast<int32_t*>(base);
+            slot.finished = base + rows * 4;
+            slot.ignore_eos = base + rows * 5;
+            slot.status = reinterpret_cast<int32_t*>(base + rows * 6);
+            if (cudaEventCreateWithFlags(&slot.done, cudaEventDisableTiming) != cudaSuccess) {
+                set_last_error("engine_create: event creation failed");
+                return fail(B200_ERR_CUDA);
+            }
+        }
+    }
     if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&e->ev_meta_done, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&e->ev_scatter_done, cudaEventDisableTiming) != cudaSuccess ||
@@ -700,6 +765,9 @@ int b200_engine_destroy(b200_engine* e) {
     for (void* p : e->allocs) cudaFree(p);
     if (e->meta_host) cudaFreeHost(e->meta_host);
     if (e->scatter_host) cudaFreeHost(e->scatter_host);
+    for (auto& slot : e->ring)
+        if (slot.done) cudaEventDestroy(slot.done);
+    if (e->ring_host) cudaFreeHost(e->ring_host);
     if (e->ev_meta_done) cudaEventDestroy(e->ev_meta_done);
     if (e->ev_scatter_done) cudaEventDestroy(e->ev_scatter_done);
     if (e->ev_step_begin) cudaEventDestroy(e->ev_step_begin);
@@ -827,7 +895,8 @@ int b200_engine_capture_graphs(b200_engine* e, const int32_t* batch_sizes, int c
     return B200_OK;
 }
 
-int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_host) {
+// One step; the tokens go to `next_tokens_host` by a copy, or (slot != NULL) through the result ring.
+static int run_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_host, b200_engine::ResultSlot* slot) {
     B200_CHECK_ARG(e && st, "engine_step: NULL argument");
     B200_CHECK_ARG(st->phase == B200_PHASE_PREFILL || st->phase == B200_PHASE_DECODE, "engine_step: bad phase");
     const int B = st->num_reqs, Bp = st->num_padded_reqs;
@@ -872,7 +941,75 @@ int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_h
     if (next_tokens_host && B > 0)
         B200_CHECK_CUDA(cudaMemcpyAsync(next_tokens_host, e->next_tokens, B * sizeof(int32_t),
                                         cudaMemcpyDeviceToHost, s));
+    if (slot) {
+        B200_CHECK_CUDA(launch_kernel(publish_step_kernel, dim3(1), dim3(256), 0, s, dim3(1, 1, 1), slot->tokens,
+                                      slot->finished, static_cast<const uint8_t*>(slot->ignore_eos), slot->status,
+                                      static_cast<const int32_t*>(e->next_tokens),
+                                      static_cast<const int32_t*>(e->meta_dev + 3 * Bg + 1),
+                                      static_cast<const int*>(e->status), B, static_cast<int>(e->eos_token_id),
+                                      static_cast<unsigned long long>(slot->ticket)));
+        e->launches_last_step += 1;
+        B200_CHECK_CUDA(cudaEventRecord(slot->done, s));
+    }
     B200_CHECK_CUDA(cudaEventRecord(e->ev_step_end, s));
+    return B200_OK;
+}
+
+int b200_engine_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_host) {
+    return run_step(e, st, next_tokens_host, nullptr);
+}
+
+int b200_engine_set_eos_token(b200_engine* e, int32_t eos_token_id) {
+    B200_CHECK_ARG(e, "engine_set_eos_token: NULL engine");
+    e->eos_token_id = eos_token_id;
+    return B200_OK;
+}
+
+int b200_engine_result_slots(void) { return b200_engine::kResultSlots; }
+
+int b200_engine_step_async(b200_engine* e, const b200_step* st, const uint8_t* ignore_eos, int64_t* ticket) {
+    B200_CHECK_ARG(e && st && ticket, "engine_step_async: NULL argument");
+    B200_CHECK_ARG(st->num_reqs >= 0 && st->num_reqs <= e->max_batch, "engine_step_async: batch size out of range");
+    auto& slot = e->ring[e->next_ticket % b200_engine::kResultSlots];
+    // The slot's previous step (kResultSlots tickets ago) has long finished in a loop that waits for
+    // its tickets; if nobody waited, its result is overwritten and its ticket becomes stale.
+    if (slot.ticket >= 0) B200_CHECK_CUDA(cudaEventSynchronize(slot.done));
+    for (int i = 0; i < st->num_reqs; ++i) slot.ignore_eos[i] = ignore_eos ? ignore_eos[i] : 0;
+    slot.ticket = e->next_ticket;
+    slot.num_reqs = st->num_reqs;
+    int err = run_step(e, st, nullptr, &slot);
+    if (err != B200_OK) {
+        slot.ticket = -1;
+        return err;
+    }
+    *ticket = e->next_ticket++;
+    return B200_OK;
+}
+
+int b200_engine_wait(b200_engine* e, int64_t ticket, const int32_t** tokens, const uint8_t** finished) {
+    B200_CHECK_ARG(e, "engine_wait: NULL engine");
+    B200_CHECK_ARG(ticket >= 0 && ticket < e->next_ticket, "engine_wait: ticket %lld was never issued",
+                   static_cast<long long>(ticket));
+    auto& slot = e->ring[ticket % b200_engine::kResultSlots];
+    B200_CHECK_ARG(slot.ticket == ticket, "engine_wait: ticket %lld has left the ring (%d steps are kept)",
+                   static_cast<long long>(ticket), b200_engine::kResultSlots);
+    B200_CHECK_CUDA(cudaEventSynchronize(slot.done));
+    if (tokens) *tokens = slot.tokens;
+    if (finished) *finished = slot.finished;
+    const int timeout_site = slot.status[0], bad_index = slot.status[1];
+    if (timeout_site != 0 || bad_index != 0) {
+        // rare: put the device words and the decode kernel's merge tickets back in order
+        cudaStreamSynchronize(e->stream);
+        cudaMemset(e->status, 0, 2 * sizeof(int));
+        if (timeout_site != 0) {
+            reset_decode_workspace(e->attn_ws, e->stream);
+            cudaStreamSynchronize(e->stream);
+            set_last_error("a bounded wait inside a kernel ran out (site %d)", timeout_site);
+            return B200_ERR_TIMEOUT;
+        }
+        set_last_error("a kernel saw an out-of-range index (%d)", bad_index - 1);
+        return B200_ERR_INVALID_ARGUMENT;
+    }
     return B200_OK;
 }
 

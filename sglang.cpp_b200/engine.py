@@ -50,6 +50,16 @@ class ForwardOutput:
         self._engine.synchronize()
 
 
+class StepTicket:
+    """A step in flight in the engine's result ring (b200_engine_step_async / b200_engine_wait)."""
+
+    def __init__(self, engine: "Engine", ticket: int, num_reqs: int):
+        self._engine, self.ticket, self.num_reqs = engine, ticket, num_reqs
+
+    def wait(self):
+        return self._engine.wait(self.ticket, self.num_reqs)
+
+
 class Engine:
     def __init__(self, model_config, config: EngineConfig):
         """model_config: any object with the forward-pass fields of the reference's ModelConfig
@@ -220,6 +230,47 @@ class Engine:
         buf = self.next_token_buffer()
         call("b200_engine_step", self._h, ctypes.byref(st), buf.data_ptr())
         return ForwardOutput(self, buf, b)
+
+    def set_eos_token(self, eos_token_id: int) -> None:
+        """Engine::eos_token_id (include/sglang/engine/engine.h:71) for the device-side finish flags."""
+        call("b200_engine_set_eos_token", self._h, int(eos_token_id))
+
+    def forward_batch_async(self, phase: int, table_idx, cached_lens, extend_lens, write_pos=None,
+                            num_reqs: Optional[int] = None, temperatures=None, top_k=None, top_p=None,
+                            seeds=None, ignore_eos=None) -> "StepTicket":
+        """forward_batch reporting through the engine's pinned result ring: ``StepTicket.wait()``
+        blocks on this step's own event and returns (tokens, finished flags) as numpy views of the
+        ring slot (valid until ``b200_engine_result_slots()`` further steps have been enqueued)."""
+        t, c, e = _i32(table_idx), _i32(cached_lens), _i32(extend_lens)
+        bp = len(t)
+        b = bp if num_reqs is None else num_reqs
+        wp = _i32(write_pos) if write_pos is not None else None
+        keep = []
+
+        def opt(a, dtype):
+            if a is None:
+                return None
+            arr = np.ascontiguousarray(np.asarray(a, dtype=dtype))
+            keep.append(arr)
+            return arr.ctypes.data
+
+        st = StepStruct(phase, b, bp, t.ctypes.data, c.ctypes.data, e.ctypes.data,
+                        wp.ctypes.data if wp is not None else None, opt(temperatures, np.float32),
+                        opt(top_k, np.int32), opt(top_p, np.float32), opt(seeds, np.uint64),
+                        self._step_index)
+        self._step_index += 1
+        ticket = ctypes.c_int64()
+        call("b200_engine_step_async", self._h, ctypes.byref(st), opt(ignore_eos, np.uint8), ctypes.byref(ticket))
+        return StepTicket(self, int(ticket.value), b)
+
+    def wait(self, ticket: int, num_reqs: int):
+        tok, fin = ctypes.c_void_p(), ctypes.c_void_p()
+        call("b200_engine_wait", self._h, ticket, ctypes.byref(tok), ctypes.byref(fin))
+        if num_reqs == 0:
+            return np.zeros(0, np.int32), np.zeros(0, np.uint8)
+        tokens = np.ctypeslib.as_array(ctypes.cast(tok, ctypes.POINTER(ctypes.c_int32)), shape=(num_reqs,))
+        finished = np.ctypeslib.as_array(ctypes.cast(fin, ctypes.POINTER(ctypes.c_uint8)), shape=(num_reqs,))
+        return tokens, finished
 
     def next_token_buffer(self) -> torch.Tensor:
         """The pinned buffer the next step's tokens go to (call once per step)."""

@@ -633,8 +633,12 @@ class DecodeSession:
     vector operations, as the reference's C++ loop keeps it.  The request lengths live in numpy
     arrays between ``step()`` calls; ``sync_back()`` writes them to the ``Req`` objects again."""
 
-    def __init__(self, batcher: HostBatcher, reqs, padded_size: Optional[int] = None):
+    def __init__(self, batcher: HostBatcher, reqs, padded_size: Optional[int] = None, ring: bool = False):
         import ctypes
+
+        self.ring = ring          # steps report through the engine's pinned result ring; step() returns a ticket
+        self._ticket = ctypes.c_int64()
+        self._ticket_ref = ctypes.byref(self._ticket)
 
         from ._lib import StepStruct
 
@@ -656,7 +660,8 @@ class DecodeSession:
         self._st_ref = ctypes.byref(self._st)
 
     def step(self):
-        """One decode step of every request (asynchronous, like Engine.forward_batch)."""
+        """One decode step of every request (asynchronous, like Engine.forward_batch): returns the
+        pinned token buffer, valid after ``engine.synchronize()`` (or the ticket for ``wait``)."""
         from ._lib import call
 
         hb, P = self.hb, self.hb.page_size
@@ -675,12 +680,21 @@ class DecodeSession:
         eng = self.engine
         self._st.step_index = eng._step_index
         eng._step_index += 1
-        buf = eng.next_token_buffer()
-        call("b200_engine_step", eng._h, self._st_ref, buf.data_ptr())
+        if self.ring:
+            call("b200_engine_step_async", eng._h, self._st_ref, None, self._ticket_ref)
+            out = self._ticket.value
+        else:
+            buf = eng.next_token_buffer()
+            call("b200_engine_step", eng._h, self._st_ref, buf.data_ptr())
+            out = buf[:self.n]
         # Req::complete_one for every request
         self.cached[:self.n] = self.device_len
         self.device_len += can
-        return buf[:self.n]
+        return out
+
+    def wait(self, ticket: int):
+        """(tokens, finish flags) of a step enqueued with ``ring=True``: blocks on that step only."""
+        return self.engine.wait(ticket, self.n)
 
     def sync_back(self) -> None:
         for i, r in enumerate(self.reqs):

@@ -480,3 +480,63 @@ def test_decode_session_equals_step_by_step_batcher(pkg):
     assert torch.equal(runs[0][0], runs[1][0])
     assert runs[0][1] == runs[1][1]
     assert runs[0][2] == runs[1][2]
+
+
+def test_result_ring_tokens_and_finish_flags(pkg):
+    """Steps reporting through the pinned result ring (b200_engine_step_async / b200_engine_wait):
+    (a) the tokens equal those of b200_engine_step + synchronize on the same state, also when several
+    steps are enqueued before the first wait; (b) the device-side finish flag equals the host rule of
+    Scheduler::process_forward_output (src/scheduler/scheduler.cc:449-455): the request cannot decode
+    further, or its token is the end-of-sequence id and it does not ignore it; (c) a ticket that has
+    left the ring is refused."""
+    from sglang_cpp_b200._lib import B200Error, load
+
+    cfg = small_cfg("qwen3")
+    slots = load().b200_engine_result_slots()
+    assert slots >= 2
+
+    def prepare():
+        pr = Pair(pkg, cfg, 16)
+        rng = np.random.default_rng(5)
+        # the second request may only produce 3 tokens: it runs out of length during the test
+        reqs = [pr.hb.add_request(rng.integers(0, cfg.vocab_size, size=n).astype(np.int32), new)
+                for n, new in ((19, 12), (33, 3), (8, 12))]
+        pr.hb.prefill(reqs).synchronize()
+        return pr, reqs
+
+    # reference run: plain steps
+    pr, reqs = prepare()
+    plain = []
+    for _ in range(6):
+        out = pr.hb.decode(reqs)
+        out.synchronize()
+        plain.append(out.next_tokens_cpu.tolist())
+    pr.engine.close()
+    eos = plain[2][0]           # request 0 produces this token at step 2
+
+    pr, reqs = prepare()
+    pr.engine.set_eos_token(eos)
+    ignore = [0, 0, 1]
+    tickets, expect_fin = [], []
+    for step in range(6):
+        pr.hb.allocate(reqs)
+        wp = [r.write_pos() for r in reqs]
+        t = pr.engine.forward_batch_async(1, [r.table_idx for r in reqs], [r.cached_len for r in reqs],
+                                          [1] * len(reqs), write_pos=wp, ignore_eos=ignore)
+        for r in reqs:
+            r.complete_one()
+        tickets.append(t)
+        expect_fin.append([int(w < 0 or (not ig and tok == eos)) for w, ig, tok in zip(wp, ignore, plain[step])])
+        if step % slots == slots - 1:          # wait only once the ring is full: steps stay in flight
+            for k in range(step - slots + 1, step + 1):
+                toks, fin = tickets[k].wait()
+                assert toks.tolist() == plain[k], f"step {k}"
+                assert fin.tolist() == expect_fin[k], f"step {k}"
+    for k in range(6 - 6 % slots, 6):
+        toks, fin = tickets[k].wait()
+        assert toks.tolist() == plain[k] and fin.tolist() == expect_fin[k]
+    assert expect_fin[2][0] == 1 and any(f[1] for f in expect_fin), "the test must see both finish causes"
+    with pytest.raises(B200Error):
+        tickets[0].wait()                      # overwritten long ago
+    pr.engine.synchronize()
+    pr.engine.close()
