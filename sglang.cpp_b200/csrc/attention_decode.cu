@@ -20,8 +20,9 @@
 //     runs, one per CTA (computed on the device from seq_lens alone: no host plan, graph-replay
 //     safe), so every CTA streams the same number of bytes; a run is split into items at
 //     request boundaries and the stage ring runs across item boundaries.
-//   * every warp writes an (m, l, O) partial; the CTA that delivers a request's last partial
-//     (threadfence + atomic ticket, looked at after the CTA's last stage) merges and writes bf16.
+//   * every warp writes an (m, l, O) partial (or, for a request that is a single partial, bf16
+//     outputs at once); a second, tiny kernel merges the partials of every request, one warp per
+//     (request, query head), so the streaming kernel ends with its last stage.
 #include <mutex>
 
 #include "common.cuh"
@@ -42,8 +43,7 @@ constexpr int kStages = 3;
 constexpr int kMaxBatch = 1024;
 constexpr int kSlotTab = 1024;
 constexpr int kMinStagesPerCta = 2;   // do not split below two stages (128 KB) per CTA
-constexpr int kMergeTab = 2048;   // (head, partial) softmax weights staged for the merge
-constexpr int kMergeHeads = 128;
+constexpr int kMergeWarps = 4;    // merge kernel: one warp per (request, query head)
 
 struct DecodeParams {
     __nv_bfloat16* out;
@@ -60,7 +60,6 @@ struct DecodeParams {
     float scale_log2;
     float* ws_o;        // [max_items * KG, q_heads, 128]
     float* ws_ml;       // [max_items * KG, q_heads, 2]
-    int* counters;      // [kMaxBatch], zero between calls
     int max_items;
     int* status;
     int kv_evict_first;   // stream K/V through L2 with the evict-first policy (read once per step)
@@ -83,9 +82,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __shared__ int s_prefix[kMaxBatch + 1];  // exclusive scan of items per request
     __shared__ int s_len[kMaxBatch];         // seq_lens, read once
     __shared__ int s_slot_tab[kSlotTab];
-    __shared__ int s_pend[2][4];             // cross-CTA items of this CTA: b, ticket, nchunks, first_slot
-    __shared__ float s_mw[kMergeTab];
-    __shared__ float s_minv[kMergeHeads];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -254,71 +250,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
     };
     const int Hq = p.q_heads;
 
-    // Merge of all partials of request b (every consumer thread takes part).
-    auto merge_request = [&](int b, int nparts, int first_slot) {
-        const int64_t part0 = static_cast<int64_t>(first_slot) * KG;
-        consumer_bar();  // the staging arrays may still be read by a previous merge
-        if (Hq * nparts <= kMergeTab && Hq <= kMergeHeads) {
-            // Phase 1: one warp per head computes the softmax weight of every partial.
-            for (int head = warp; head < Hq; head += kConsumerWarps) {
-                float mloc = -INFINITY;
-                for (int pp = lane; pp < nparts; pp += 32)
-                    mloc = fmaxf(mloc, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                const float M = warp_max(mloc);
-                float lsum = 0.f;
-                for (int pp = lane; pp < nparts; pp += 32) {
-                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(
-                        p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                    const float wgt = exp2f(ml.x - M);
-                    s_mw[head * nparts + pp] = wgt;
-                    lsum += ml.y * wgt;
-                }
-                const float Lt = warp_sum(lsum);
-                if (lane == 0) s_minv[head] = Lt > 0.f ? 1.f / Lt : 0.f;
-            }
-            consumer_bar();
-            // Phase 2: independent, unrolled loads of the partial outputs.
-            for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
-                const int head = idx / (kD / 2), dp = idx % (kD / 2);
-                const float* wrow = s_mw + head * nparts;
-                const float* src = p.ws_o + (part0 * Hq + head) * kD + dp * 2;
-                const int64_t pstride = static_cast<int64_t>(Hq) * kD;
-                float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-                for (int pp = 0; pp < nparts; ++pp) {
-                    const float2 ov = __ldcg(reinterpret_cast<const float2*>(src + pp * pstride));
-                    a0 += ov.x * wrow[pp];
-                    a1 += ov.y * wrow[pp];
-                }
-                const float inv = s_minv[head];
-                *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(b) * Hq + head) * kD + dp * 2) =
-                    pack_bf16(a0 * inv, a1 * inv);
-            }
-        } else {
-            for (int idx = threadIdx.x; idx < Hq * (kD / 2); idx += kConsumerThreads) {
-                const int head = idx / (kD / 2), dp = idx % (kD / 2);
-                float M = -INFINITY;
-                for (int pp = 0; pp < nparts; ++pp)
-                    M = fmaxf(M, __ldcg(p.ws_ml + ((part0 + pp) * Hq + head) * 2));
-                float L = 0.f, a0 = 0.f, a1 = 0.f;
-                for (int pp = 0; pp < nparts; ++pp) {
-                    const int64_t ph = (part0 + pp) * Hq + head;
-                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ph * 2));
-                    const float wgt = exp2f(ml.x - M);
-                    const float2 ov = __ldcg(reinterpret_cast<const float2*>(p.ws_o + ph * kD + dp * 2));
-                    L += ml.y * wgt;
-                    a0 += ov.x * wgt;
-                    a1 += ov.y * wgt;
-                }
-                const float inv = L > 0.f ? 1.f / L : 0.f;
-                *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(b) * Hq + head) * kD + dp * 2) =
-                    pack_bf16(a0 * inv, a1 * inv);
-            }
-        }
-    };
-
     pdl_wait_prior();  // q comes from the kernel before this one
-    int npend = 0;  // cross-CTA items whose merge is decided after this CTA's last stage
     int gpos = g_begin;
     bool have = gpos < g_end;
     ItemInfo it = {};
@@ -478,43 +410,111 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                             make_float2(rr ? m1 : m0, rr ? l1 : l0);
                 }
             }
-            if (it.nchunks == 1) {
-                // All partials of the request are this CTA's own (several key groups per stage).
-                __threadfence();
-                merge_request(it.b, nparts, it.first_slot);
-            } else {
-                // The request is shared with other CTAs.  Release: the barrier orders every
-                // thread's partial stores before thread 0's fence, the fence orders them before
-                // the ticket (fences are cumulative).  Nobody waits for the ticket here: whether
-                // this CTA has to merge is looked at after its last stage, so the stage pipeline
-                // keeps running.  At most two items of a contiguous run cross CTAs.
-                consumer_bar();
-                if (threadIdx.x == 0 && npend < 2) {
-                    __threadfence();
-                    s_pend[npend][0] = it.b;
-                    s_pend[npend][1] = atomicAdd(&p.counters[it.b], 1);
-                    s_pend[npend][2] = it.nchunks;
-                    s_pend[npend][3] = it.first_slot;
-                }
-                ++npend;
-            }
         }
         have = has_next;
         it = nx;
     }
+}
 
-    // ---- deferred merges: requests for which this CTA delivered the last partial ----
-    if (npend > 0) {
-        consumer_bar();
-        for (int k = 0; k < min(npend, 2); ++k) {
-            const int b = s_pend[k][0], ticket = s_pend[k][1], nchunks = s_pend[k][2];
-            if (ticket == nchunks - 1) {
-                __threadfence();  // the other CTAs' partials are visible once the last ticket is
-                merge_request(b, nchunks * KG, s_pend[k][3]);
-                if (threadIdx.x == 0) p.counters[b] = 0;
+// Second kernel of a decode attention call: the partial results of every request that was cut over
+// several CTAs (or several key groups of a stage) are combined and written as bf16.  One warp per
+// (request, query head): it repeats the split arithmetic of the kernel above for its request, reads the
+// (max, sum) pairs and the fp32 partial rows in one round trip to L2 and writes 128 outputs.  Kept out
+// of the streaming kernel on purpose: there the CTA that happened to deliver a request's last partial
+// merged it behind its own last stage, a chain of fences, a ticket and three dependent trips to L2 that
+// left the other 147 SMs and HBM idle for about 12 us per launch.
+__global__ void __launch_bounds__(kMergeWarps * 32)
+attention_decode_merge_kernel(const DecodeParams p, int attn_grid) {
+    __shared__ int s_first, s_stages, s_total;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_per_cta = kMergeWarps;
+    const int ctas_per_req = (p.q_heads + heads_per_cta - 1) / heads_per_cta;
+    const int b = static_cast<int>(blockIdx.x) / ctas_per_req;
+    const int head = (static_cast<int>(blockIdx.x) % ctas_per_req) * heads_per_cta + warp;
+    const int SK = p.stage_keys;
+    pdl_launch_dependents();
+    // seq_lens were complete before the attention kernel started: the split runs ahead of the wait
+    if (warp == 0) {
+        int carry = 0, first = 0, mine = 0;
+        for (int base = 0; base < p.batch; base += 32) {
+            const int r = base + lane;
+            const int n = r < p.batch ? (max(p.seq_lens[r], 0) + SK - 1) / SK : 0;
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
             }
+            if (b >= base && b < base + 32) {
+                first = carry + __shfl_sync(0xffffffffu, incl - n, b - base);
+                mine = __shfl_sync(0xffffffffu, n, b - base);
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            s_first = first;
+            s_stages = mine;
+            s_total = carry;
         }
     }
+    __syncthreads();
+    const int first = s_first, st = s_stages;
+    const int per = max((s_total + attn_grid - 1) / attn_grid, kMinStagesPerCta);
+    const int KG = kConsumerWarps / p.kv_heads;
+    const int c0 = first / per;
+    const int nparts = st > 0 ? ((first + st - 1) / per - c0 + 1) * KG : 0;
+    pdl_wait_prior();
+    if (nparts <= 1 || head >= p.q_heads) return;   // a single partial was written as bf16 by the kernel above
+    const int Hq = p.q_heads;
+    const int64_t part0 = static_cast<int64_t>(b + c0) * KG;
+    const float* ml = p.ws_ml + (part0 * Hq + head) * 2;
+    const float* po = p.ws_o + (part0 * Hq + head) * kD + lane * 4;
+    const int64_t ml_stride = static_cast<int64_t>(Hq) * 2, o_stride = static_cast<int64_t>(Hq) * kD;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float M = -INFINITY, Lsum = 0.f;
+    for (int base = 0; base < nparts; base += 32) {
+        const int n = min(32, nparts - base);
+        // this chunk's (max, sum) pairs, one per lane, and its rows: all loads are independent
+        float2 mine = make_float2(-INFINITY, 0.f);
+        if (lane < n) mine = __ldcg(reinterpret_cast<const float2*>(ml + (base + lane) * ml_stride));
+        float4 rows[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            rows[j] = j < n ? __ldcg(reinterpret_cast<const float4*>(po + (base + j) * o_stride))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float Mc = fmaxf(M, warp_max(mine.x));   // finite: a request's first partial holds key 0
+        const float rescale = exp2f(M - Mc);           // 0 on the first chunk (M = -inf)
+        acc.x *= rescale;
+        acc.y *= rescale;
+        acc.z *= rescale;
+        acc.w *= rescale;
+        const float w_mine = exp2f(mine.x - Mc);
+        Lsum = Lsum * rescale + warp_sum(mine.y * w_mine);
+        M = Mc;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j < n) {   // n is the same on every lane
+                const float w = __shfl_sync(0xffffffffu, w_mine, j);
+                acc.x += rows[j].x * w;
+                acc.y += rows[j].y * w;
+                acc.z += rows[j].z * w;
+                acc.w += rows[j].w * w;
+            }
+        }
+        for (int j = 8; j < n; ++j) {
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            const float4 r = __ldcg(reinterpret_cast<const float4*>(po + (base + j) * o_stride));
+            acc.x += r.x * w;
+            acc.y += r.y * w;
+            acc.z += r.z * w;
+            acc.w += r.w * w;
+        }
+    }
+    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.out + (static_cast<int64_t>(b) * Hq + head) * kD + lane * 4) = packed;
 }
 
 }  // namespace
@@ -523,7 +523,7 @@ int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads) {
     const int kg = kConsumerWarps / kv_heads;
     const int64_t items = static_cast<int64_t>(sm_count()) + max_batch;
     const int64_t parts = items * kg;
-    return kMaxBatch * 4 + parts * q_heads * (kD + 2) * 4 + 256;
+    return parts * q_heads * (kD + 2) * 4 + 256;
 }
 
 int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,
@@ -534,8 +534,8 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                             int* status, cudaStream_t stream, bool kv_evict_first) {
     const int kg = kConsumerWarps / kv_heads;
     const int grid = sm_count();
-    // Workspace layout: counters | ws_ml | ws_o
-    const int64_t avail = workspace_bytes - kMaxBatch * 4 - 256;
+    // Workspace layout: ws_ml | ws_o
+    const int64_t avail = workspace_bytes - 256;
     const int64_t per_item = static_cast<int64_t>(kg) * q_heads * (kD + 2) * 4;
     const int64_t max_items = avail / per_item;
     if (max_items < static_cast<int64_t>(grid) + batch) {
@@ -562,8 +562,7 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
     p.num_slots = num_slots;
     p.scale_log2 = sm_scale * 1.4426950408889634f;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    p.counters = reinterpret_cast<int*>(ws);
-    uint8_t* f = ws + kMaxBatch * 4;
+    uint8_t* f = ws;
     f = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(f) + 255) & ~uintptr_t(255));
     p.ws_ml = reinterpret_cast<float*>(f);
     p.ws_o = p.ws_ml + max_items * kg * q_heads * 2;
@@ -577,13 +576,9 @@ int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     B200_CHECK_CUDA(launch_kernel(attention_decode_kernel, dim3(grid), dim3(kThreads), smem, stream,
                                   dim3(1, 1, 1), tmap_k, tmap_v, p));
-    return B200_OK;
-}
-
-int reset_decode_workspace(void* workspace, cudaStream_t stream) {
-    // The per-request merge tickets at the head of the workspace: a step that was cut short (a
-    // bounded wait ran out) may leave them non-zero.
-    B200_CHECK_CUDA(cudaMemsetAsync(workspace, 0, kMaxBatch * sizeof(int), stream));
+    const int merge_ctas = batch * ((q_heads + kMergeWarps - 1) / kMergeWarps);
+    B200_CHECK_CUDA(launch_kernel(attention_decode_merge_kernel, dim3(merge_ctas), dim3(kMergeWarps * 32), 0, stream,
+                                  dim3(1, 1, 1), p, grid));
     return B200_OK;
 }
 
@@ -740,11 +735,9 @@ int b200_attention_decode_noalloc(void* out, const void* q, int64_t q_stride_tok
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     unsigned char* base = static_cast<unsigned char*>(scratch);
     int* status = reinterpret_cast<int*>(base + usable);
-    // The array keeps whatever the previous call left.  The per-request tickets must start at
-    // zero (a call that ended normally leaves them so, one that was cut short may not); partial
-    // sums are always written before they are read.  The status words in the array's tail are NOT
-    // cleared here: they keep the first report until b200_attention_decode_noalloc_status reads it.
-    B200_CHECK_CUDA(cudaMemsetAsync(base, 0, kMaxBatch * sizeof(int), s));
+    // The array keeps whatever the previous call left: partial sums are always written before they
+    // are read.  The status words in the array's tail are NOT cleared here: they keep the first
+    // report until b200_attention_decode_noalloc_status reads it.
 
     CUtensorMap tk, tv;
     int err = make_kv_tmap(&tk, k_cache, num_slots, kv_heads, page_size);

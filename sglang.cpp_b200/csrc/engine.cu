@@ -998,12 +998,10 @@ int b200_engine_wait(b200_engine* e, int64_t ticket, const int32_t** tokens, con
     if (finished) *finished = slot.finished;
     const int timeout_site = slot.status[0], bad_index = slot.status[1];
     if (timeout_site != 0 || bad_index != 0) {
-        // rare: put the device words and the decode kernel's merge tickets back in order
+        // rare: clear the device words for the steps that follow
         cudaStreamSynchronize(e->stream);
         cudaMemset(e->status, 0, 2 * sizeof(int));
         if (timeout_site != 0) {
-            reset_decode_workspace(e->attn_ws, e->stream);
-            cudaStreamSynchronize(e->stream);
             set_last_error("a bounded wait inside a kernel ran out (site %d)", timeout_site);
             return B200_ERR_TIMEOUT;
         }
@@ -1020,9 +1018,6 @@ int b200_engine_synchronize(b200_engine* e) {
     B200_CHECK_CUDA(cudaMemcpy(host, e->status, sizeof(host), cudaMemcpyDeviceToHost));
     if (host[0] != 0) {
         cudaMemset(e->status, 0, sizeof(host));
-        // a step that was cut short can leave the decode kernel's merge tickets half counted
-        reset_decode_workspace(e->attn_ws, e->stream);
-        cudaStreamSynchronize(e->stream);
         set_last_error("a bounded wait inside a kernel ran out (site %d)", host[0]);
         return B200_ERR_TIMEOUT;
     }

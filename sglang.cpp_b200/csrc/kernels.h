@@ -88,7 +88,6 @@ bool decode_chain_supported(int tokens, int hidden, int q_heads, int kv_heads, i
 int launch_decode_chain(const DecodeChainArgs& args, cudaStream_t stream);
 
 int64_t decode_workspace_bytes(int max_batch, int q_heads, int kv_heads);
-int reset_decode_workspace(void* workspace, cudaStream_t stream);
 int make_kv_tmap(CUtensorMap* out, const void* cache, int64_t num_slots, int kv_heads, int page_size);
 int launch_attention_decode(void* out, const void* q, int64_t q_st, int64_t q_sh,
                             const CUtensorMap& tmap_k, const CUtensorMap& tmap_v, int64_t num_slots,

@@ -174,8 +174,8 @@ def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_p
         assert pr.engine_status_clean()
         pr.engine.close()
     assert outs["1"][1] < outs["0"][1], "the chain path must launch fewer kernels"
-    # prepare, embedding, layer 0's norm / qkv / rope, (attention + chain) per layer, final norm, lm_head, argmax, write-back
-    assert outs["1"][1] == 9 + 2 * cfg.num_layers, outs["1"][1]
+    # prepare, embedding, layer 0's norm / qkv / rope, (attention + merge + chain) per layer, final norm, lm_head, argmax, write-back
+    assert outs["1"][1] == 9 + 3 * cfg.num_layers, outs["1"][1]
     d = (outs["1"][0].float() - outs["0"][0].float()).abs()
     assert float(d.max()) <= MAX_ABS and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
 
