@@ -62,8 +62,8 @@ FlashInferBackend::FlashInferBackend(std::shared_ptr<BaseKVCachePool> kv_cache, 
                                      int head_dim)
     : kv_cache_(kv_cache), num_qo_heads_(num_qo_heads), num_kv_heads_(num_kv_heads), head_dim_(head_dim) {
     TORCH_CHECK(head_dim == 128, "the sm_100a attention kernels take head_dim 128");
-    // split-KV scratch of the decode kernel for up to 1024 requests, zero-initialised once (the
-    // calls leave it zeroed where it must be)
+    // split-KV scratch of the decode kernel for up to 1024 requests (partials are written before
+    // they are read, so it needs no initialisation)
     const int64_t bytes = b200_attention_decode_workspace_bytes(1024, num_qo_heads, num_kv_heads, head_dim);
     TORCH_CHECK(bytes > 0, "unsupported head configuration for decode attention: ", num_qo_heads, " / ", num_kv_heads);
     float_workspace_ = torch::zeros({bytes}, torch::TensorOptions().dtype(torch::kByte).device(kv_cache_->device()));

@@ -155,3 +155,28 @@ def test_sample_from_probs_follows_the_distribution(L):
     got = L.sample_from_probs(probs.repeat(n, 1).contiguous().cuda(), u.cuda()).cpu()
     freq = torch.bincount(got.long(), minlength=32).float() / n
     assert float((freq - probs[0]).abs().max()) < 0.02
+
+
+def test_sampler_time_per_call(L):
+    """64 rows of a 151 936-word vocabulary (the decode batch of the benchmark): device time per call,
+    printed with -s.  The bound only catches a regression to the multi-pass form (0.3 ms)."""
+    rows, vocab = 64, 151936
+    gen = torch.Generator().manual_seed(0)
+    logits = (torch.randn(rows, vocab, generator=gen) * 0.64).to(torch.bfloat16).cuda()
+    seeds = torch.arange(rows, dtype=torch.int64).cuda()
+    for t, k, p in ((0.7, 50, 0.9), (1.0, -1, 1.0)):
+        temps = torch.full((rows,), t).cuda()
+        tk = torch.full((rows,), k, dtype=torch.int32).cuda()
+        tp = torch.full((rows,), p).cuda()
+        for _ in range(3):
+            L.sample(logits, temps, tk, tp, seeds=seeds, step_index=3)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            L.sample(logits, temps, tk, tp, seeds=seeds, step_index=3)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1000 / 20
+        print(f"sample_kernel, {rows} x {vocab}, temperature {t} top_k {k} top_p {p}: {us:.1f} us per call")
+        assert us < 150.0
