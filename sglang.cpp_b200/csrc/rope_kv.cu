@@ -102,11 +102,36 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
         lane / LPR;
 
     pdl_launch_dependents();
+    // What the first row needs besides the row itself - its token's position and slot, the rotation
+    // entries of that position, the norm weights - does not come from the kernel before this one
+    // (positions and out_loc are complete before any kernel of the layer stack starts): fetch it
+    // ahead of the wait, so that only the row is loaded behind it.
+    int pre_pos = 0, pre_slot = 0;
+    float pre_c[EPL], pre_s[EPL];
+    Vec pre_wa, pre_wb;
+    if (row0 < total_rows) {
+        const int64_t t = row0 / rows_per_token;
+        const int r = static_cast<int>(row0 - t * rows_per_token);
+        pre_pos = positions[t];
+        pre_slot = out_loc[t];
+        const int pc = min(max(pre_pos, 0), max_pos - 1);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            pre_c[e] = cos_t[static_cast<int64_t>(pc) * (D / 2) + sub * EPL + e];
+            pre_s[e] = sin_t[static_cast<int64_t>(pc) * (D / 2) + sub * EPL + e];
+        }
+        const __nv_bfloat16* w = r < q_heads ? qw : kw;
+        if (w != nullptr && r < q_heads + kv_heads) {
+            pre_wa = *reinterpret_cast<const Vec*>(w + sub * EPL);
+            pre_wb = *reinterpret_cast<const Vec*>(w + D / 2 + sub * EPL);
+        }
+    }
     pdl_wait_prior();
     if (row0 >= total_rows) return;
 
     // One row: a, b are its two halves, already loaded.
     auto process = [&](int64_t row, Vec a, Vec b) {
+    const bool first = row == row0;
     const int64_t t = row / rows_per_token;
     const int r = static_cast<int>(row - t * rows_per_token);
     __nv_bfloat16* src = qkv + (t * rows_per_token + r) * D;
@@ -117,7 +142,7 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
 
     int64_t slot = 0;
     if (!is_q) {
-        slot = out_loc[t];
+        slot = first ? pre_slot : out_loc[t];
         if (slot < 0 || slot >= num_slots) {
             if (sub == 0) atomicExch(&status[kStatusBadIndex], static_cast<int>(slot) + 1);
             slot = -1;
@@ -148,8 +173,8 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
         const float scale = rsqrtf(ss / static_cast<float>(D) + eps);
-        Vec wa = *reinterpret_cast<const Vec*>(w + sub * EPL);
-        Vec wb = *reinterpret_cast<const Vec*>(w + D / 2 + sub * EPL);
+        Vec wa = first ? pre_wa : *reinterpret_cast<const Vec*>(w + sub * EPL);
+        Vec wb = first ? pre_wb : *reinterpret_cast<const Vec*>(w + D / 2 + sub * EPL);
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
             // bf16 rounding here is where the unfused norm kernel stores its result.
@@ -158,7 +183,7 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
         }
     }
 
-    int pos = positions[t];
+    int pos = first ? pre_pos : positions[t];
     if (pos < 0 || pos >= max_pos) {
         if (sub == 0) atomicExch(&status[kStatusBadIndex], pos + 1);
         pos = min(max(pos, 0), max_pos - 1);
@@ -168,7 +193,7 @@ qknorm_rope_store_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ q
     Vec oa, ob;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
-        const float cs = c[e], sn = s[e];
+        const float cs = first ? pre_c[e] : c[e], sn = first ? pre_s[e] : s[e];
         oa.v[e] = __float2bfloat16_rn(x1[e] * cs - x2[e] * sn);
         ob.v[e] = __float2bfloat16_rn(x2[e] * cs + x1[e] * sn);
     }
