@@ -700,7 +700,6 @@ def run_gpu_tp(args, dist_ready=False, as_record=False):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": ("c5: Qwen3-30B-A3B decode, batch 256, prompts of 512 random tokens, page size 16, greedy"
                                 if moe else
-                                "c3: Qwen3-0.6B chunked prefill alternating with sampled decode, one GPU; "
                          "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy"),
                    "parallelism": (f"ep{world}+tp{world}" if moe else f"tp{world}"), "mean_context": mean_ctx,
                    "ranks_in_lockstep": lockstep},
