@@ -540,3 +540,51 @@ def test_result_ring_tokens_and_finish_flags(pkg):
         tickets[0].wait()                      # overwritten long ago
     pr.engine.synchronize()
     pr.engine.close()
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3moe"])
+def test_engine_runs_a_checkpoint_read_from_safetensors_shards(pkg, tmp_path, kind):
+    """Checkpoint on disk (two safetensors shards with Hugging Face names, one with the prefix the
+    reference strips, src/models/weight_loader.cc:27-43) -> load_checkpoint -> Engine.load_weights:
+    prefill and decode logits equal the oracle's on the same tensors."""
+    from sglang_cpp_b200 import weights as W
+    from sglang_cpp_b200.engine import Engine, EngineConfig
+    from sglang_cpp_b200.host_batch import HostBatcher
+
+    cfg = small_cfg(kind)
+    w = O.init_weights(cfg, seed=9, std=0.02)
+    w["final_norm"] = (torch.randn(cfg.hidden_size, generator=torch.Generator().manual_seed(1)) * 0.1 + 1).to(torch.bfloat16)
+    flat = W.unpack_checkpoint(cfg, w)
+    names = sorted(flat)
+    W.write_safetensors(tmp_path / "model-00001-of-00002.safetensors", {n: flat[n] for n in names[::2]})
+    W.write_safetensors(tmp_path / "model-00002-of-00002.safetensors",
+                        {"language_model." + n: flat[n] for n in names[1::2]})
+    loaded = W.load_checkpoint(cfg, tmp_path)
+
+    pr = Pair(pkg, cfg, 16)
+    pr.engine.close()
+    pr.w = loaded
+    pr.engine = Engine(cfg, EngineConfig(16, 64, 8, 512, 1024))
+    pr.engine.load_weights(loaded)
+    pr.hb = HostBatcher(pr.engine, 64, 16, 8)
+    pr.oracle = O.OracleModel(cfg, w, O.store_bf16)     # the tensors that were written, not the ones read back
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.int32) for n in (23, 40)]
+    reqs = [pr.hb.add_request(p, 4) for p in prompts]
+    pr.host_tokens = {r.table_idx: list(p) + [0] * 8 for r, p in zip(reqs, prompts)}
+    pr.hb.allocate(reqs)
+    ob, pt = pr.oracle_batch(reqs, True)
+    want = pr.oracle.forward(ob, pr.kv, pt)
+    pr.hb.prefill(reqs).synchronize()
+    check_logits(pr.engine.logits(2), want, f"{kind} checkpoint prefill")
+    tok = want.argmax(-1).tolist()
+    for r, t in zip(reqs, tok):
+        pr.host_tokens[r.table_idx][r.cached_len] = t
+    pr.engine.write_token_pool([r.table_idx for r in reqs], [r.cached_len for r in reqs], tok)
+    pr.hb.allocate(reqs)
+    ob, pt = pr.oracle_batch(reqs, False)
+    want = pr.oracle.forward(ob, pr.kv, pt)
+    pr.hb.decode(reqs).synchronize()
+    check_logits(pr.engine.logits(2), want, f"{kind} checkpoint decode")
+    assert pr.engine_status_clean()
+    pr.engine.close()
