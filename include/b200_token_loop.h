@@ -315,6 +315,17 @@ B200_API int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_co
 B200_API int b200_comm_handle_bytes(void);
 B200_API int b200_comm_export(b200_comm* comm, void* handle_out);
 B200_API int b200_comm_connect(b200_comm* comm, const void* all_handles);
+/* The same communicator over memory the host obtained elsewhere (a symmetric allocation): region =
+ * this rank's block of b200_comm_region_bytes(buffer_bytes) zeroed bytes, 256-byte aligned;
+ * peer_regions[world] = every rank's block as this process addresses it; multicast_region = the
+ * NVLink multicast address of the blocks, or NULL.  With a multicast address the all-reduce is
+ * summed inside the switch (multimem.ld_reduce) and delivered with one store (multimem.st); the
+ * order of the additions is then the switch's, not rank order.  The memory stays the caller's. */
+B200_API int64_t b200_comm_region_bytes(int64_t buffer_bytes);
+B200_API int b200_comm_create_on(int rank, int world, int64_t buffer_bytes, void* region, b200_comm** out);
+B200_API int b200_comm_connect_pointers(b200_comm* comm, const void* const* peer_regions,
+                                        const void* multicast_region);
+B200_API int b200_comm_uses_multicast(b200_comm* comm);
 /* Device address of this rank's exchange buffer for the given parity: the producer of the
  * partial sum (the row-parallel GEMM) writes there. */
 B200_API void* b200_comm_buffer(b200_comm* comm, int parity);
@@ -475,6 +486,19 @@ B200_API int b200_engine_read_logits(b200_engine* engine, void* host, int rows);
  * (b200_comm_handle_bytes bytes) and connect to all ranks' handles before the first step. */
 B200_API int b200_engine_comm_export(b200_engine* engine, void* handle_out);
 B200_API int b200_engine_comm_connect(b200_engine* engine, const void* all_handles);
+/* The same over memory the host obtained elsewhere - a symmetric allocation whose peer addresses,
+ * and the NVLink multicast address of the whole group where the fabric has one, the host already
+ * knows (torch.distributed's symmetric memory in the tests; no counterpart in the reference, whose
+ * all-reduce is NCCL's).  region: this rank's block of b200_engine_comm_region_bytes() zeroed bytes,
+ * 256-byte aligned; peer_regions[tp_size]: every rank's block as this process addresses it;
+ * multicast_region: the multicast address of the blocks or NULL.  With a multicast address the
+ * all-reduce is reduced inside the switch (multimem.ld_reduce) and its result delivered to every
+ * rank with one store (multimem.st); the sum's order of additions is then the switch's, not rank
+ * order.  Replaces the communicator created with the engine; call before capturing graphs.  The
+ * memory stays the caller's and must outlive the engine. */
+B200_API int64_t b200_engine_comm_region_bytes(b200_engine* engine);
+B200_API int b200_engine_comm_attach(b200_engine* engine, void* region, const void* const* peer_regions,
+                                     const void* multicast_region);
 /* The engine's communicator, for b200_comm_set_wait_limit_ns and the loop-back test hooks
  * (NULL when the engine was created with tp_size 1). */
 B200_API b200_comm* b200_engine_comm(b200_engine* engine);

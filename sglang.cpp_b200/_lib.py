@@ -84,6 +84,12 @@ PROTOTYPES: dict[str, tuple] = {
     "b200_decode_chain_grid": (_I, []),
     "b200_allreduce": (_I, [_P, _I, _P, _I, _I, _P]),
     "b200_allreduce_fused_add_rmsnorm": (_I, [_P, _I, _P, _P, _P, _I, _I, _F, _I, _P]),
+    "b200_comm_region_bytes": (c_int64, [c_int64]),
+    "b200_comm_create_on": (_I, [_I, _I, c_int64, _P, POINTER(c_void_p)]),
+    "b200_comm_connect_pointers": (_I, [_P, _P, _P]),
+    "b200_comm_uses_multicast": (_I, [_P]),
+    "b200_engine_comm_region_bytes": (c_int64, [_P]),
+    "b200_engine_comm_attach": (_I, [_P, _P, _P, _P]),
     "b200_engine_comm_export": (_I, [_P, _P]),
     "b200_engine_comm_connect": (_I, [_P, _P]),
     "b200_engine_create": (_I, [_P, _P, POINTER(c_void_p)]),

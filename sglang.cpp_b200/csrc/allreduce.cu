@@ -35,6 +35,10 @@ struct CommDevice {
     uint32_t* self_counter;                       // [blocks] calls this CTA slot has completed
     void* peer_gather[kMaxRanks];                 // [rank] -> that rank's buffer of reduced rows (two-shot):
                                                   // 8-byte words of two bf16 values + the call number
+    // NVLink multicast (NVLS) addresses of the same memory on every rank, or NULL: a load-reduce through
+    // them is summed inside the switch, a store through them lands on every rank.
+    const uint8_t* mc_buf[2];
+    uint8_t* mc_gather;
     int rank, world;
     uint64_t wait_limit_ns;                       // longest a CTA waits for its peers before it gives up
 };
@@ -221,6 +225,24 @@ allreduce_twoshot_kernel(const CommDevice c, int parity, __nv_bfloat16* out, __n
         for (int i = 0; i < kArVecPerThread; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
             if (v >= nvec) continue;
+            if (c.mc_gather != nullptr) {
+                // In-switch reduction: one load returns the sum of this vector over every rank (fp32
+                // accumulation, bf16 result; the order of the additions is the switch's), one store per
+                // 16 bytes delivers the sum and the call number to every rank.
+                const uint8_t* src = c.mc_buf[parity] + (base + v) * 16;
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(y[i][0]), "=r"(y[i][1]), "=r"(y[i][2]), "=r"(y[i][3]) : "l"(src) : "memory");
+                uint8_t* dst = c.mc_gather + (base + v) * 32;
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst),
+                             "f"(__uint_as_float(y[i][0])), "f"(__uint_as_float(call)), "f"(__uint_as_float(y[i][1])),
+                             "f"(__uint_as_float(call))
+                             : "memory");
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 16),
+                             "f"(__uint_as_float(y[i][2])), "f"(__uint_as_float(call)), "f"(__uint_as_float(y[i][3])),
+                             "f"(__uint_as_float(call))
+                             : "memory");
+                continue;
+            }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int r = 0; r < c.world; ++r) {  // rank order
                 const uint4 a = __ldcv(reinterpret_cast<const uint4*>(c.peer_buf[parity][r]) + base + v);
@@ -344,6 +366,8 @@ struct b200_comm {
     int two_shot_min_world = 8;   // B200_AR_TWO_SHOT_MIN_WORLD: groups of at least this size use the two-shot kernel
     uint64_t wait_limit_ns = 2000000000ull;  // 2 s, as every other bounded wait of the library
     bool loopback = false;        // every "peer" is this rank's own memory (time-out tests on one GPU)
+    bool owns_memory = true;      // local_base came from cudaMalloc here (false: the caller's symmetric allocation)
+    bool mapped_ipc = false;      // peer bases were opened from CUDA IPC handles
 };
 
 namespace {
@@ -380,6 +404,66 @@ int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out)
     return B200_OK;
 }
 
+int64_t b200_comm_region_bytes(int64_t buffer_bytes) {
+    if (buffer_bytes <= 0) return -1;
+    return align_up(static_cast<int64_t>(kMaxCommBlocks) * kMaxRanks * 4, 256) +
+           align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256) + 4 * align_up(buffer_bytes, 256);
+}
+
+int b200_comm_create_on(int rank, int world, int64_t buffer_bytes, void* region, b200_comm** out) {
+    B200_CHECK_ARG(out && region, "comm_create_on: NULL argument");
+    B200_CHECK_ARG(world >= 1 && world <= kMaxRanks, "comm_create_on: world size must be in [1, 8]");
+    B200_CHECK_ARG(rank >= 0 && rank < world, "comm_create_on: rank out of range");
+    B200_CHECK_ARG(buffer_bytes > 0, "comm_create_on: buffer_bytes must be positive");
+    B200_CHECK_ARG((reinterpret_cast<uintptr_t>(region) & 255u) == 0, "comm_create_on: the region must be 256-byte aligned");
+    b200_comm* c = new b200_comm();
+    c->rank = rank;
+    c->world = world;
+    B200_CHECK_CUDA(cudaGetDevice(&c->device));
+    c->buffer_bytes = align_up(buffer_bytes, 256);
+    c->flags_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * kMaxRanks * 4, 256);
+    c->counters_bytes = align_up(static_cast<int64_t>(kMaxCommBlocks) * 4, 256);
+    if (const char* v = getenv("B200_AR_TWO_SHOT_MIN_WORLD")) c->two_shot_min_world = atoi(v);
+    c->local_base = region;
+    c->owns_memory = false;
+    c->peer_base[rank] = region;
+    *out = c;
+    return B200_OK;
+}
+
+static void comm_set_pointers(b200_comm* c, const void* multicast_base) {
+    for (int r = 0; r < c->world; ++r) {
+        char* base = static_cast<char*>(c->peer_base[r]);
+        c->dev.peer_flags[r] = reinterpret_cast<uint32_t*>(base);
+        for (int p = 0; p < 2; ++p)
+            c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
+                                                                          p * c->buffer_bytes);
+        c->dev.peer_gather[r] = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
+    }
+    const uint8_t* mc = static_cast<const uint8_t*>(multicast_base);
+    for (int p = 0; p < 2; ++p)
+        c->dev.mc_buf[p] = mc ? mc + c->flags_bytes + c->counters_bytes + p * c->buffer_bytes : nullptr;
+    c->dev.mc_gather = mc ? const_cast<uint8_t*>(mc) + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes : nullptr;
+    c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
+    c->dev.rank = c->rank;
+    c->dev.world = c->world;
+    c->dev.wait_limit_ns = c->wait_limit_ns;
+    c->connected = true;
+}
+
+int b200_comm_connect_pointers(b200_comm* c, const void* const* peer_regions, const void* multicast_region) {
+    B200_CHECK_ARG(c && peer_regions, "comm_connect_pointers: NULL argument");
+    B200_CHECK_ARG(!c->connected, "comm_connect_pointers: already connected");
+    for (int r = 0; r < c->world; ++r) {
+        B200_CHECK_ARG(peer_regions[r] != nullptr, "comm_connect_pointers: rank %d has no region", r);
+        if (r != c->rank) c->peer_base[r] = const_cast<void*>(peer_regions[r]);
+    }
+    comm_set_pointers(c, multicast_region);
+    return B200_OK;
+}
+
+int b200_comm_uses_multicast(b200_comm* c) { return c && c->dev.mc_gather != nullptr ? 1 : 0; }
+
 int b200_comm_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
 
 int b200_comm_export(b200_comm* c, void* handle_out) {
@@ -400,19 +484,8 @@ int b200_comm_connect(b200_comm* c, const void* all_handles) {
         memcpy(&h, hs + static_cast<size_t>(r) * sizeof(h), sizeof(h));
         B200_CHECK_CUDA(cudaIpcOpenMemHandle(&c->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
     }
-    for (int r = 0; r < c->world; ++r) {
-        char* base = static_cast<char*>(c->peer_base[r]);
-        c->dev.peer_flags[r] = reinterpret_cast<uint32_t*>(base);
-        for (int p = 0; p < 2; ++p)
-            c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
-                                                                          p * c->buffer_bytes);
-        c->dev.peer_gather[r] = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
-    }
-    c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
-    c->dev.rank = c->rank;
-    c->dev.world = c->world;
-    c->dev.wait_limit_ns = c->wait_limit_ns;
-    c->connected = true;
+    c->mapped_ipc = true;
+    comm_set_pointers(c, nullptr);
     return B200_OK;
 }
 
@@ -428,20 +501,7 @@ int b200_comm_connect_loopback(b200_comm* c) {
     B200_CHECK_ARG(!c->connected, "comm_connect_loopback: already connected");
     for (int r = 0; r < c->world; ++r) c->peer_base[r] = c->local_base;
     c->loopback = true;
-    // the same pointer set-up as b200_comm_connect, on the aliased bases
-    for (int r = 0; r < c->world; ++r) {
-        char* base = static_cast<char*>(c->peer_base[r]);
-        c->dev.peer_flags[r] = reinterpret_cast<uint32_t*>(base);
-        for (int p = 0; p < 2; ++p)
-            c->dev.peer_buf[p][r] = reinterpret_cast<const __nv_bfloat16*>(base + c->flags_bytes + c->counters_bytes +
-                                                                          p * c->buffer_bytes);
-        c->dev.peer_gather[r] = base + c->flags_bytes + c->counters_bytes + 2 * c->buffer_bytes;
-    }
-    c->dev.self_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(c->local_base) + c->flags_bytes);
-    c->dev.rank = c->rank;
-    c->dev.world = c->world;
-    c->dev.wait_limit_ns = c->wait_limit_ns;
-    c->connected = true;
+    comm_set_pointers(c, nullptr);
     return B200_OK;
 }
 
@@ -468,8 +528,8 @@ int b200_comm_destroy(b200_comm* c) {
     if (!c) return B200_OK;
     cudaDeviceSynchronize();
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank && c->peer_base[r] && !c->loopback) cudaIpcCloseMemHandle(c->peer_base[r]);
-    if (c->local_base) cudaFree(c->local_base);
+        if (r != c->rank && c->peer_base[r] && c->mapped_ipc) cudaIpcCloseMemHandle(c->peer_base[r]);
+    if (c->local_base && c->owns_memory) cudaFree(c->local_base);
     delete c;
     return B200_OK;
 }
@@ -493,7 +553,7 @@ int launch_allreduce(b200_comm* c, int parity, int mode, void* out, void* residu
         return B200_ERR_INVALID_ARGUMENT;
     }
     if (rows == 0) return B200_OK;
-    if (c->world >= c->two_shot_min_world && rows <= kMaxCommBlocks) {
+    if ((c->world >= c->two_shot_min_world || c->dev.mc_gather != nullptr) && rows <= kMaxCommBlocks) {
         auto k2 = mode == 0 ? allreduce_twoshot_kernel<0, false>
                             : (round_first ? allreduce_twoshot_kernel<1, true> : allreduce_twoshot_kernel<1, false>);
         B200_CHECK_CUDA(launch_kernel(k2, dim3(rows), dim3(256), 0, stream, dim3(1, 1, 1), c->dev, parity,

@@ -130,6 +130,9 @@ using namespace b200;
 struct b200_comm;
 extern "C" {
 int b200_comm_create(int rank, int world, int64_t buffer_bytes, b200_comm** out);
+int64_t b200_comm_region_bytes(int64_t buffer_bytes);
+int b200_comm_create_on(int rank, int world, int64_t buffer_bytes, void* region, b200_comm** out);
+int b200_comm_connect_pointers(b200_comm* c, const void* const* peer_regions, const void* multicast_region);
 int b200_comm_export(b200_comm* c, void* handle_out);
 int b200_comm_connect(b200_comm* c, const void* all_handles);
 void* b200_comm_buffer(b200_comm* c, int parity);
@@ -196,6 +199,7 @@ struct b200_engine {
     int prof_pairs_recorded = 0;
     int launches_last_step = 0;
     b200_comm* comm = nullptr;  // tensor parallelism: exchange buffers for the fused all-reduce
+    int64_t comm_buffer_bytes = 0;
 
     // Results of the steps in flight: a ring of pinned, device-mapped slots the last kernel of a step
     // writes straight into (tokens, finish flags, the device status words, the ticket), one event each.
@@ -698,7 +702,8 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     E_TRY(named_alloc(e, &e->input_ids, "input_ids", Tm));
     E_TRY(named_alloc(e, &e->seq_lens, "seq_lens", e->max_batch));
     E_TRY(named_alloc(e, &e->next_tokens, "next_tokens", e->max_batch, true));
-    if (c.tp_size > 1) E_TRY(b200_comm_create(c.tp_rank, c.tp_size, Tm * H * 2, &e->comm));
+    e->comm_buffer_bytes = Tm * H * 2;
+    if (c.tp_size > 1) E_TRY(b200_comm_create(c.tp_rank, c.tp_size, e->comm_buffer_bytes, &e->comm));
     if (m.num_experts > 0) {
         E_TRY(named_alloc(e, &e->router_logits, "router_logits", Tm * m.num_experts));
         E_TRY(dev_alloc(e, &e->moe_ws,
@@ -1051,6 +1056,31 @@ int b200_engine_comm_connect(b200_engine* e, const void* all_handles) {
 }
 
 b200_comm* b200_engine_comm(b200_engine* e) { return e ? e->comm : nullptr; }
+
+int64_t b200_engine_comm_region_bytes(b200_engine* e) {
+    if (!e || !e->comm) return -1;
+    return b200_comm_region_bytes(e->comm_buffer_bytes);
+}
+
+int b200_engine_comm_attach(b200_engine* e, void* region, const void* const* peer_regions,
+                            const void* multicast_region) {
+    B200_CHECK_ARG(e && e->comm, "engine_comm_attach: the engine was not created with tp_size > 1");
+    B200_CHECK_ARG(region && peer_regions, "engine_comm_attach: NULL region");
+    B200_CHECK_ARG(e->graphs.empty() && e->graphs_sampled.empty(),
+                   "engine_comm_attach: attach before capturing graphs (they hold the exchange buffers' addresses)");
+    B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    b200_comm* fresh = nullptr;
+    int err = b200_comm_create_on(e->c.tp_rank, e->c.tp_size, e->comm_buffer_bytes, region, &fresh);
+    if (err != B200_OK) return err;
+    err = b200_comm_connect_pointers(fresh, peer_regions, multicast_region);
+    if (err != B200_OK) {
+        b200_comm_destroy(fresh);
+        return err;
+    }
+    b200_comm_destroy(e->comm);
+    e->comm = fresh;
+    return B200_OK;
+}
 
 int b200_engine_set_profiling(b200_engine* e, int on) {
     B200_CHECK_ARG(e, "engine_set_profiling: NULL engine");

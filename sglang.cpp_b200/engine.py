@@ -127,10 +127,36 @@ class Engine:
             for name, t in shard_layer(cfg, L, tp_rank, tp_size, self.config.expert_parallel).items():
                 self.load(name, l, t)
 
-    def connect_tp(self, group=None) -> None:
-        """Exchange the CUDA IPC handles of the all-reduce buffers over torch.distributed and map
-        the peers (what the reference's NCCL unique-id rendezvous does,
-        src/distributed/distributed.cc:142-173)."""
+    def connect_tp(self, group=None, symmetric: Optional[bool] = None) -> None:
+        """Connect the all-reduce buffers of the ranks (what the reference's NCCL unique-id
+        rendezvous does, src/distributed/distributed.cc:142-173).
+
+        Default: CUDA IPC handles of the engine's own buffers travel over torch.distributed.  With
+        ``symmetric`` (or B200_TP_SYMMETRIC=1 in the environment) the buffers are a
+        torch.distributed symmetric-memory allocation instead, whose peer addresses and NVLink
+        multicast address come from torch's rendezvous: the all-reduce is then summed inside the
+        switch.  Needs a CUDA-capable process group (NCCL) as ``group``."""
+        import os
+
+        if symmetric is None:
+            symmetric = os.environ.get("B200_TP_SYMMETRIC", "0") == "1"
+        if symmetric:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+
+            nbytes = int(_lib.load().b200_engine_comm_region_bytes(self._h))
+            dev = torch.device("cuda", torch.cuda.current_device())
+            region = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+            region.zero_()
+            torch.cuda.synchronize()
+            name = (group or dist.group.WORLD).group_name
+            handle = symm_mem.rendezvous(region, name)
+            peers = (ctypes.c_void_p * self.config.tp_size)(*[int(p) for p in handle.buffer_ptrs])
+            mc = int(handle.multicast_ptr) if handle.multicast_ptr else None
+            call("b200_engine_comm_attach", self._h, region.data_ptr(), peers, mc)
+            self._symmetric_region = (region, handle)   # the memory must outlive the engine
+            dist.barrier(group=group)
+            return
         from .tp import exchange_handles
 
         n = _lib.load().b200_comm_handle_bytes()

@@ -83,12 +83,23 @@ def cpu_oracle_worker(rank, world, port, out_path, kind="llama"):
     dist.destroy_process_group()
 
 
-def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
-    """Two processes, one GPU each: the engine with tp_size = 2 (fused all-reduce over peer memory)
-    against the unsharded oracle, prefill then decode."""
+def _init_group(rank, world, port, symmetric):
+    """gloo for the host-side exchanges; with `symmetric` also NCCL, whose group torch's symmetric-memory
+    rendezvous (peer and multicast addresses of the exchange buffers) runs on."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if symmetric:
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def gpu_engine_worker(rank, world, port, out_path, kind="llama", symmetric=False):
+    """Two processes, one GPU each: the engine with tp_size = 2 (fused all-reduce over peer memory)
+    against the unsharded oracle, prefill then decode.  symmetric: the exchange buffers are a
+    symmetric-memory allocation and the all-reduce is summed in the NVLink switch."""
+    _init_group(rank, world, port, symmetric)
     import __graft_entry__ as entry
     from oracle import token_loop_oracle as O
 
@@ -102,7 +113,12 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     w = O.init_weights(cfg, seed=0, std=0.02, router_std=1.0 if kind.startswith("moe") else None)
     eng = Engine(cfg, EngineConfig(16, 32, 4, 256, 512, rank, world, ep))
     eng.load_weights(w, rank, world)
-    eng.connect_tp()
+    eng.connect_tp(symmetric=symmetric)
+    if symmetric and rank == 0:
+        from sglang_cpp_b200._lib import load as _load_lib
+        import ctypes as _ct
+        _load_lib().b200_engine_comm.restype = _ct.c_void_p
+        res_multicast = bool(_load_lib().b200_comm_uses_multicast(_ct.c_void_p(_load_lib().b200_engine_comm(eng._h))))
     hb = HostBatcher(eng, 32, 16, 4, enable_prefix_cache=False)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.int32) for n in (7, 19)]
@@ -110,6 +126,8 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     out = hb.prefill(reqs)
     out.synchronize()
     res = {"prefill": eng.logits(2).clone()}
+    if symmetric and rank == 0:
+        res["multicast"] = res_multicast
     toks = [out.next_tokens_cpu.clone()]
     decode_logits = []
     for _ in range(3):
@@ -153,13 +171,11 @@ def gpu_engine_worker(rank, world, port, out_path, kind="llama"):
     dist.destroy_process_group()
 
 
-def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0):
+def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0, symmetric=False):
     """The all-reduce calls of the C ABI on their own (tensor_model_parallel_all_reduce and its
     fusion with add + norm), several calls in a row so that both buffer parities and the call
     numbering are exercised; rank 0 saves what it got and what the sums should be."""
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _init_group(rank, world, port, symmetric)
     import ctypes
     import __graft_entry__ as entry
     from oracle import token_loop_oracle as O
@@ -171,11 +187,24 @@ def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0):
 
     rows, hidden = 37, 1024
     comm = ctypes.c_void_p()
-    call("b200_comm_create", rank, world, rows * hidden * 2, ctypes.byref(comm))
-    n = lib.b200_comm_handle_bytes()
-    buf = ctypes.create_string_buffer(n)
-    call("b200_comm_export", comm, buf)
-    call("b200_comm_connect", comm, exchange_handles(buf.raw, rank, world))
+    if symmetric:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        nbytes = int(lib.b200_comm_region_bytes(rows * hidden * 2))
+        region = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", rank))
+        region.zero_()
+        torch.cuda.synchronize()
+        handle = symm_mem.rendezvous(region, dist.group.WORLD.group_name)
+        call("b200_comm_create_on", rank, world, rows * hidden * 2, region.data_ptr(), ctypes.byref(comm))
+        peers = (ctypes.c_void_p * world)(*[int(p) for p in handle.buffer_ptrs])
+        call("b200_comm_connect_pointers", comm, peers, int(handle.multicast_ptr) if handle.multicast_ptr else None)
+        dist.barrier()
+    else:
+        call("b200_comm_create", rank, world, rows * hidden * 2, ctypes.byref(comm))
+        n = lib.b200_comm_handle_bytes()
+        buf = ctypes.create_string_buffer(n)
+        call("b200_comm_export", comm, buf)
+        call("b200_comm_connect", comm, exchange_handles(buf.raw, rank, world))
     gen = torch.Generator().manual_seed(17)
     res = {"plain": [], "want_plain": [], "fused_x": [], "fused_res": [], "want_x": [], "want_res": []}
     weight = (torch.randn(hidden, generator=gen) * 0.1 + 1).to(torch.bfloat16)
@@ -211,6 +240,18 @@ def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0):
     # so a rank runs ahead of its peer whenever the protocol lets it.  Every sum is checked on the
     # device against the same fp32-in-rank-order sum computed locally; mismatching calls are counted.
     bad = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+    def differs(got, want, summed=None):
+        # peer-memory kernels: the fp32 sum in rank order rounded once, bit for bit.  In-switch sums
+        # (symmetric): the switch's own rounding of the sum, within one bf16 step of that sum (and,
+        # in the fused form, one more step of the residual it is added to).
+        if not symmetric:
+            return got != want
+        step = want.float().abs() * 2 ** -7 + 1e-6
+        if summed is not None:
+            step = step + summed.float().abs() * 2 ** -7
+        return (got.float() - want.float()).abs() > step
+
     from sglang_cpp_b200.engine import _as_cuda_tensor
     bufs = [_as_cuda_tensor(lib.b200_comm_buffer(comm, par), rows * hidden * 2).view(torch.bfloat16).view(rows, hidden)
             for par in (0, 1)]
@@ -226,16 +267,17 @@ def gpu_allreduce_worker(rank, world, port, out_path, stress_calls=0):
         bufs[c & 1].copy_(parts[rank])
         if c % 2 == 0:
             call("b200_allreduce", comm, c & 1, out.data_ptr(), rows, hidden, stream)
-            bad += (out != total).any().long()
+            bad += differs(out, total).any().long()
         else:
             before = residual.clone()
             call("b200_allreduce_fused_add_rmsnorm", comm, c & 1, out.data_ptr(), residual.data_ptr(),
                  w_dev.data_ptr(), rows, hidden, 1e-6, 1, stream)
-            bad += (residual != (total.float() + before.float()).to(torch.bfloat16)).any().long()
+            bad += differs(residual, (total.float() + before.float()).to(torch.bfloat16), total).any().long()
             residual.mul_(0.5)   # keep the running residual bounded
     torch.cuda.synchronize()
     res["stress_calls"] = stress_calls
     res["stress_bad"] = int(bad.item())
+    res["multicast"] = bool(lib.b200_comm_uses_multicast(comm))
     allbad = [None] * world
     dist.all_gather_object(allbad, res["stress_bad"])
     res["stress_bad_all_ranks"] = allbad
