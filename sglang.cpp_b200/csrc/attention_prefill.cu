@@ -305,10 +305,17 @@ int launch_attention_prefill(void* out, const void* q, int64_t q_st, int64_t q_s
     if (batch == 0 || max_extend_len == 0) return B200_OK;
     // The tensor-core kernel takes every call with 16-byte aligned query rows; the mma.sync kernel
     // below stays for the rest (and for comparison: B200_PREFILL_ATTN=mma).
-    static const bool force_mma = [] {
-        const char* v = getenv("B200_PREFILL_ATTN");
-        return v && v[0] == 'm';
+    static const char choice = [] {
+        const char* v = getenv("B200_PREFILL_ATTN");   // "mma": legacy path; "tc": one query tile per CTA
+        return v && v[0] ? v[0] : ' ';
     }();
+    const bool force_mma = choice == 'm';
+    // Two query tiles per CTA (attention_prefill_tc2.cu) once a request can fill more than one tile.
+    if (!force_mma && choice != 't' && attention_prefill_tc_supported(q, q_st, q_sh, out) &&
+        max_extend_len > 128 / (q_heads / kv_heads))
+        return launch_attention_prefill_tc2(out, q, q_st, q_sh, k_cache, v_cache, num_slots, page_table, pt_stride,
+                                            table_idx, seq_lens, qo_indptr, batch, max_extend_len, q_heads,
+                                            kv_heads, page_size, sm_scale, status, stream);
     if (!force_mma && attention_prefill_tc_supported(q, q_st, q_sh, out))
         return launch_attention_prefill_tc(out, q, q_st, q_sh, k_cache, v_cache, num_slots, page_table, pt_stride,
                                            table_idx, seq_lens, qo_indptr, batch, max_extend_len, q_heads,

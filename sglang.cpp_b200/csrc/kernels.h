@@ -102,6 +102,12 @@ int launch_attention_prefill_tc(void* out, const void* q, int64_t q_st, int64_t 
                                 const int32_t* qo_indptr, int batch, int max_extend_len, int q_heads,
                                 int kv_heads, int page_size, float sm_scale, int* status,
                                 cudaStream_t stream);
+int launch_attention_prefill_tc2(void* out, const void* q, int64_t q_st, int64_t q_sh, const void* k_cache,
+                                const void* v_cache, int64_t num_slots, const int32_t* page_table,
+                                int64_t pt_stride, const int32_t* table_idx, const int32_t* seq_lens,
+                                const int32_t* qo_indptr, int batch, int max_extend_len, int q_heads,
+                                int kv_heads, int page_size, float sm_scale, int* status,
+                                cudaStream_t stream);
 int launch_attention_prefill(void* out, const void* q, int64_t q_st, int64_t q_sh, const void* k_cache,
                              const void* v_cache, int64_t num_slots, const int32_t* page_table,
                              int64_t pt_stride, const int32_t* table_idx, const int32_t* seq_lens,
