@@ -41,7 +41,9 @@ act_and_mul_kernel(uint4* __restrict__ out, const uint4* __restrict__ in, int64_
 
 __global__ void __launch_bounds__(128)
 embedding_kernel(uint4* __restrict__ out, const uint4* __restrict__ table,
-                 const int32_t* __restrict__ ids, int vec_per_row, int vocab, int* status) {
+                 const int32_t* __restrict__ ids, int vec_per_row, int vocab, int* status,
+                 unsigned long long* __restrict__ ssq, int ssq_slots, int ssq_stride) {
+    __shared__ float warp_part[4];
     pdl_launch_dependents();
     pdl_wait_prior();
     const int64_t t = blockIdx.x;
@@ -50,8 +52,35 @@ embedding_kernel(uint4* __restrict__ out, const uint4* __restrict__ table,
     if (!ok && threadIdx.x == 0) atomicExch(&status[kStatusBadIndex], id + 1);
     const uint4* src = table + static_cast<int64_t>(ok ? id : 0) * vec_per_row;
     uint4* dst = out + t * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x)
-        dst[v] = ok ? src[v] : make_uint4(0, 0, 0, 0);
+    float part = 0.f;
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+        const uint4 u = ok ? src[v] : make_uint4(0, 0, 0, 0);
+        dst[v] = u;
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part += bf16_lo(w4[j]) * bf16_lo(w4[j]) + bf16_hi(w4[j]) * bf16_hi(w4[j]);
+    }
+    if (ssq == nullptr) return;
+    // start of a step's residual stream: this row's statistic, and a clean slate for the GEMMs that add to the others
+    for (int s = 1 + threadIdx.x; s < ssq_slots; s += blockDim.x) ssq[static_cast<int64_t>(s) * ssq_stride + t] = 0ull;
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        ssq[t] = static_cast<unsigned long long>((warp_part[0] + warp_part[1] + warp_part[2] + warp_part[3]) * 16777216.0f);
+}
+
+__global__ void scale_columns_kernel(uint4* __restrict__ out, const uint4* __restrict__ w,
+                                     const uint4* __restrict__ scale, int64_t total_vec, int vec_per_row) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const uint4 a = w[i], b = scale[i % vec_per_row];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = pack_bf16(bf16_lo(aw[j]) * bf16_lo(bw[j]), bf16_hi(aw[j]) * bf16_hi(bw[j]));
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 __global__ void gather_int32_2d_kernel(int32_t* __restrict__ out, const int32_t* __restrict__ table,
@@ -93,11 +122,23 @@ int launch_act_and_mul(void* out, const void* in, int tokens, int d, bool gelu,
 }
 
 int launch_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
-                     int vocab, int* status, cudaStream_t stream) {
+                     int vocab, int* status, cudaStream_t stream, unsigned long long* ssq, int ssq_slots,
+                     int ssq_stride) {
     if (tokens == 0) return B200_OK;
     B200_CHECK_CUDA(launch_kernel(embedding_kernel, dim3(tokens), dim3(128), 0, stream, dim3(1, 1, 1),
                                   static_cast<uint4*>(out), static_cast<const uint4*>(table), ids,
-                                  hidden / 8, vocab, status));
+                                  hidden / 8, vocab, status, ssq, ssq_slots, ssq_stride));
+    return B200_OK;
+}
+
+int launch_scale_columns(void* out, const void* w, const void* scale, int64_t rows, int K, cudaStream_t stream) {
+    const int64_t total = rows * (K / 8);
+    if (total == 0) return B200_OK;
+    const int64_t want = div_ceil64(total, 256);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    scale_columns_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, stream>>>(
+        static_cast<uint4*>(out), static_cast<const uint4*>(w), static_cast<const uint4*>(scale), total, K / 8);
+    B200_CHECK_LAUNCH();
     return B200_OK;
 }
 

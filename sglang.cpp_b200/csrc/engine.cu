@@ -114,6 +114,9 @@ struct LayerWeights {
     __nv_bfloat16 *qkv = nullptr, *qkv_bias = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;
     __nv_bfloat16 *input_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
     __nv_bfloat16 *router = nullptr, *experts_gate_up = nullptr, *experts_down = nullptr;
+    // qkv and gate_up with the norm weight in front of them folded into their columns (decode steps
+    // whose GEMMs carry the add + norm in their epilogues)
+    __nv_bfloat16 *qkv_folded = nullptr, *gate_up_folded = nullptr;
     CUtensorMap tmap_k, tmap_v;
 };
 
@@ -223,6 +226,14 @@ struct b200_engine {
     // two paths (each of its phases pays several ~1 us round trips to L2 that separate launches hide
     // behind one another under programmatic dependent launch).
     bool use_chain = false;
+    // Decode steps of a dense, unsharded model of at most 256 tokens: no add + norm kernels.  o_proj and
+    // down_proj add the residual in their split-K epilogue and accumulate each row's sum of squares;
+    // qkv_proj and gate_up_proj read the un-normalised residual against weights with the norm weight
+    // folded in, and scale their accumulator by the row's 1 / rms.  B200_FOLD_NORM=0 turns it off.
+    bool use_fold = true;
+    bool folded_valid = false;          // the folded copies match qkv / gate_up / the norm weights
+    unsigned long long* ssq = nullptr;  // [2 * layers + 1, kSsqStride] sums of squares of the residual rows
+    static constexpr int kSsqStride = 256;
     bool use_pdl = true;  // B200_PDL=0 turns programmatic dependent launches off
     bool kv_evict_first = true;  // B200_KV_EVICT_FIRST=0: K/V loads with the default L2 policy
     // Seeds are 64-bit: keep them 8-byte aligned inside the int32 staging block.  The 64-bit step
@@ -283,6 +294,34 @@ int build_rope_tables(b200_engine* e) {
     return B200_OK;
 }
 
+// Can this step run with the add + norm kernels folded into the GEMMs around them?
+bool fold_supported(const b200_engine* e, int phase, int T) {
+    const b200_model_config& m = e->m;
+    if (!e->use_fold || e->ssq == nullptr || phase != B200_PHASE_DECODE || e->c.tp_size > 1 || m.num_experts > 0 ||
+        T > b200_engine::kSsqStride)
+        return false;
+    // every one of the four GEMMs must split along K: the fusions live in the split-K epilogue
+    const int H = m.hidden_size, D = m.head_dim;
+    return skinny_gemm_split(T, e->qkv_dim, H, B200_EPILOGUE_NONE) > 1 &&
+           skinny_gemm_split(T, H, e->hq * D, B200_EPILOGUE_NONE) > 1 &&
+           skinny_gemm_split(T, 2 * e->inter, H, B200_EPILOGUE_SWIGLU) > 1 &&
+           skinny_gemm_split(T, H, e->inter, B200_EPILOGUE_NONE) > 1;
+}
+
+// Rebuilds the folded weight copies after a weight was loaded.  Enqueued on the engine's stream, never
+// inside a graph capture (the callers run it first).
+int ensure_folded(b200_engine* e) {
+    if (e->ssq == nullptr || e->folded_valid) return B200_OK;
+    const int H = e->m.hidden_size;
+    for (LayerWeights& L : e->layers) {
+        B200_TRY(launch_scale_columns(L.qkv_folded, L.qkv, L.input_norm, e->qkv_dim, H, e->stream));
+        B200_TRY(launch_scale_columns(L.gate_up_folded, L.gate_up, L.post_norm, 2 * static_cast<int64_t>(e->inter), H,
+                                      e->stream));
+    }
+    e->folded_valid = true;
+    return B200_OK;
+}
+
 // The layer stack on `T` tokens of `Bp` requests; everything is enqueued on e->stream.
 int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_extend,
                     bool sampling = false, uint64_t step_index = 0) {
@@ -293,9 +332,11 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     const int32_t* meta_table_idx = e->meta_dev;
     const int32_t* meta_qo = e->meta_dev + 2 * Bp;
 
+    const bool fold = fold_supported(e, phase, T);
     // The residual stream starts at zero, so the first fused add+norm leaves residual = embedding
-    // (what the reference's layer 0 does with `residual = x`).
-    B200_CHECK_CUDA(cudaMemsetAsync(e->residual, 0, static_cast<size_t>(T) * hidden * 2, s));
+    // (what the reference's layer 0 does with `residual = x`).  With the norms folded into the GEMMs
+    // the embedding is written into the residual directly.
+    if (!fold) B200_CHECK_CUDA(cudaMemsetAsync(e->residual, 0, static_cast<size_t>(T) * hidden * 2, s));
     // From here on the step is an unbroken chain of kernels.  With programmatic dependent
     // launches each kernel's prologue (barrier set-up, TMEM allocation, weight-tile TMA loads)
     // overlaps the tail of its predecessor; every kernel waits (griddepcontrol.wait) before it
@@ -317,7 +358,11 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     // The embedding is launched as an ordinary dependent of the prepare kernel: every later kernel
     // of the step can then rely on seq_lens / positions / out_loc being complete even in code it
     // runs ahead of griddepcontrol.wait (a kernel can only start after the embedding has).
-    B200_TRY(launch_embedding(e->x, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s));
+    if (fold)
+        B200_TRY(launch_embedding(e->residual, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s, e->ssq,
+                                  2 * m.num_layers + 1, b200_engine::kSsqStride));
+    else
+        B200_TRY(launch_embedding(e->x, e->embed, e->input_ids, T, hidden, m.vocab_size, e->status, s));
     set_pdl_launches(e->use_pdl && !(e->profile_attention && !e->capturing));
     const bool round_first = m.fused_residual == 0;
     // Under tensor parallelism the row-parallel projections (o_proj, down_proj, the MoE output)
@@ -359,7 +404,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
 
     // Decode batches of at most 64 tokens of a dense, unsharded model: everything between two attention
     // launches is one persistent kernel (decode_chain.cu) instead of seven launches.
-    const bool chain = phase == B200_PHASE_DECODE && e->use_chain && !tp && m.num_experts == 0 &&
+    const bool chain = !fold && phase == B200_PHASE_DECODE && e->use_chain && !tp && m.num_experts == 0 &&
                        decode_chain_supported(T, hidden, e->hq, e->hkv, d, e->inter, m.attention_bias != 0);
     if (chain) {
         auto caches = [&](int l, __nv_bfloat16** kc, __nv_bfloat16** vc) {
@@ -435,7 +480,51 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         }
     }
 
-    for (int l = 0; l < (chain ? 0 : m.num_layers); ++l) {
+    for (int l = 0; l < (fold ? m.num_layers : 0); ++l) {
+        LayerWeights& L = e->layers[l];
+        unsigned long long* ssq_l = e->ssq + static_cast<int64_t>(2 * l) * b200_engine::kSsqStride;
+        SkinnyFusion normed, into_residual;
+        normed.eps = m.rms_norm_eps;
+        normed.norm_width = hidden;
+        into_residual.residual = e->residual;
+        into_residual.ssq_of_rounded = round_first;
+        normed.ssq_in = ssq_l;
+        B200_TRY(launch_linear(e->qkv, e->residual, L.qkv_folded, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                               B200_EPILOGUE_NONE, e->status, s, &normed));
+        __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
+        __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
+        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin, e->positions,
+                                          e->out_loc, k_cache, v_cache, T, e->hq, e->hkv, d, m.max_position,
+                                          e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        const bool timed = e->profile_attention && !e->capturing;
+        if (timed) {
+            while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
+                cudaEvent_t ev = nullptr;
+                B200_CHECK_CUDA(cudaEventCreate(&ev));
+                e->prof_events.push_back(ev);
+            }
+            B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l], s));
+        }
+        B200_TRY(launch_attention_decode(e->attn_out, e->qkv, e->qkv_dim, d, L.tmap_k, L.tmap_v, e->num_slots,
+                                         e->page_table, e->pt_cols, meta_table_idx, e->seq_lens, Bp, e->hq, e->hkv,
+                                         e->c.page_size, e->sm_scale, e->attn_ws, e->attn_ws_bytes, e->status, s,
+                                         e->kv_evict_first));
+        if (timed) {
+            B200_CHECK_CUDA(cudaEventRecord(e->prof_events[2 * l + 1], s));
+            e->prof_pairs_recorded = l + 1;
+        }
+        into_residual.ssq_out = ssq_l + b200_engine::kSsqStride;
+        B200_TRY(launch_linear(nullptr, e->attn_out, L.o, nullptr, T, hidden, e->hq * d, e->hq * d,
+                               B200_EPILOGUE_NONE, e->status, s, &into_residual));
+        normed.ssq_in = ssq_l + b200_engine::kSsqStride;
+        B200_TRY(launch_linear(e->h, e->residual, L.gate_up_folded, nullptr, T, 2 * e->inter, hidden, hidden, epi,
+                               e->status, s, &normed));
+        into_residual.ssq_out = ssq_l + 2 * b200_engine::kSsqStride;
+        B200_TRY(launch_linear(nullptr, e->h, L.down, nullptr, T, hidden, e->inter, e->inter, B200_EPILOGUE_NONE,
+                               e->status, s, &into_residual));
+    }
+
+    for (int l = 0; l < (chain || fold ? 0 : m.num_layers); ++l) {
         LayerWeights& L = e->layers[l];
         B200_TRY(add_norm(L.input_norm));
         B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
@@ -487,7 +576,10 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         B200_TRY(launch_linear(proj_out(), e->h, L.down, nullptr, T, hidden, e->inter, e->inter,
                                    B200_EPILOGUE_NONE, e->status, s));
     }
-    B200_TRY(add_norm(e->final_norm));
+    if (fold)
+        B200_TRY(launch_rmsnorm(e->x, e->residual, e->final_norm, T, hidden, m.rms_norm_eps, s));
+    else
+        B200_TRY(add_norm(e->final_norm));
     const __nv_bfloat16* head_in = e->x;
     if (phase == B200_PHASE_PREFILL) {
         B200_CHECK_CUDA(launch_kernel(select_last_rows_kernel, dim3(Bp), dim3(128), 0, s, dim3(1, 1, 1),
@@ -711,6 +803,19 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
                                             e->moe_inter),
                         false));
     }
+    if (const char* v = getenv("B200_FOLD_NORM")) e->use_fold = atoi(v) != 0;
+    if (e->use_fold && c.tp_size == 1 && m.num_experts == 0) {
+        for (LayerWeights& L : e->layers) {
+            void* p = nullptr;
+            E_TRY(dev_alloc(e, &p, static_cast<int64_t>(e->qkv_dim) * H * 2, false));
+            L.qkv_folded = static_cast<__nv_bfloat16*>(p);
+            E_TRY(dev_alloc(e, &p, 2 * static_cast<int64_t>(e->inter) * H * 2, false));
+            L.gate_up_folded = static_cast<__nv_bfloat16*>(p);
+        }
+        void* p = nullptr;
+        E_TRY(dev_alloc(e, &p, static_cast<int64_t>(2 * m.num_layers + 1) * b200_engine::kSsqStride * 8, true));
+        e->ssq = static_cast<unsigned long long*>(p);
+    }
     E_TRY(dev_alloc(e, &e->chain_scratch, decode_chain_scratch_bytes(m.hidden_size), true));
     e->attn_ws_bytes = decode_workspace_bytes(e->max_batch, e->hq, e->hkv);
     E_TRY(dev_alloc(e, &e->attn_ws, e->attn_ws_bytes, true));
@@ -793,6 +898,10 @@ int b200_engine_tensor(b200_engine* e, const char* name, int layer, void** devic
     }
     if (device_ptr) *device_ptr = it->second.ptr;
     if (nbytes) *nbytes = it->second.bytes;
+    // A caller that asks for one of these may write it: the folded copies are rebuilt before the next step.
+    const std::string stem = key.substr(0, key.find('.'));
+    if (device_ptr && (stem == "qkv" || stem == "gate_up" || stem == "input_norm" || stem == "post_norm"))
+        e->folded_valid = false;
     return B200_OK;
 }
 
@@ -876,6 +985,7 @@ int b200_engine_capture_graphs(b200_engine* e, const int32_t* batch_sizes, int c
             B200_TRY(stage_step(e, &st, Bp, &T, &max_ext));
             const size_t bytes = (variant ? b200_engine::step_index_offset(Bp) + 2 : 4 * Bp + 1) * sizeof(int32_t);
             B200_CHECK_CUDA(cudaMemcpyAsync(e->meta_dev, e->meta_host, bytes, cudaMemcpyHostToDevice, e->stream));
+            B200_TRY(ensure_folded(e));
             B200_TRY(enqueue_forward(e, B200_PHASE_DECODE, Bp, Bp, Bp, 1, variant != 0));  // eager warm-up
             B200_CHECK_CUDA(cudaStreamSynchronize(e->stream));
             cudaGraph_t graph = nullptr;
@@ -928,6 +1038,7 @@ static int run_step(b200_engine* e, const b200_step* st, int32_t* next_tokens_ho
         B200_CHECK_ARG(T == Bg, "engine_step: a decode step runs exactly one token per request");
 
     cudaStream_t s = e->stream;
+    B200_TRY(ensure_folded(e));
     B200_CHECK_CUDA(cudaEventRecord(e->ev_step_begin, s));
     const size_t meta_bytes =
         (sampling ? b200_engine::step_index_offset(Bg) + 2 : 4 * Bg + 1) * sizeof(int32_t);

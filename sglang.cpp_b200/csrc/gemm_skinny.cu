@@ -104,7 +104,15 @@ struct SkinnyParams {
     const int32_t* group_counts;
     const int32_t* group_offsets;
     int w_rows_per_group;
+    // Fusions with the residual stream (split-K launches of the decode step; see SkinnyFusion in kernels.h).
+    const unsigned long long* ssq_in;   // "normalised input": accumulator x rsqrt(ssq_in[m] / 2^24 / norm_width + eps)
+    float norm_eps;
+    int norm_width;
+    __nv_bfloat16* residual;            // "residual output": residual[m, n] = bf16(bf16(acc) + residual[m, n]), y unused
+    unsigned long long* ssq_out;        // ... and ssq_out[m] += (that sum)^2 in 2^-24 fixed point
+    int ssq_of_rounded;                 // square the stored (bf16) sum instead of the fp32 one
 };
+constexpr float kSsqScale = 16777216.0f;   // 2^24
 
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -119,6 +127,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tmem_full_bar;
     __shared__ uint32_t tmem_base_slot;
+    __shared__ float s_rstd[256];   // per token column, "normalised input" launches only
 
     // Let the next kernel in the stream become resident right away: its set-up and weight loads
     // then overlap this kernel (it still waits for this grid to finish before touching its input).
@@ -246,6 +255,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
     } else {
         pdl_wait_prior();
+        if (p.ssq_in != nullptr) {
+            // the row statistics come from the kernel before this one; the cluster barrier of the first
+            // exchange round orders these writes before their first use
+            for (int m = static_cast<int>(threadIdx.x) - 64; m < nt; m += kThreads - 64)
+                s_rstd[m] = m < rows ? rsqrtf(static_cast<float>(p.ssq_in[x_row0 + m]) * (1.0f / kSsqScale) /
+                                                  static_cast<float>(p.norm_width) + p.norm_eps)
+                                     : 0.f;
+        }
     }
     __syncwarp();
 
@@ -362,9 +379,42 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 }
                 const int m = r * cpr + col;
                 const int n = n0 + static_cast<int>(rank) * F + f;
-                if (m < rows && n < p.n_out) {
-                    float v[4] = {sg.x, sg.y, sg.z, sg.w};
-                    const float uu[4] = {su.x, su.y, su.z, su.w};
+                const bool valid = m < rows && n < p.n_out;
+                float v[4] = {sg.x, sg.y, sg.z, sg.w};
+                float uu[4] = {su.x, su.y, su.z, su.w};
+                if (p.ssq_in != nullptr) {
+                    const float rs = s_rstd[m];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v[e] *= rs;
+                        uu[e] *= rs;
+                    }
+                }
+                if (p.residual != nullptr) {
+                    // the residual stream ends here: add, store, and hand the row's sum of squares to the next GEMM
+                    float part = 0.f;
+                    if (valid) {
+                        __nv_bfloat16* rp = p.residual + static_cast<int64_t>(x_row0 + m) * p.n_out + n;
+                        const uint2 rr = *reinterpret_cast<const uint2*>(rp);
+                        const float r4[4] = {bf16_lo(rr.x), bf16_hi(rr.x), bf16_lo(rr.y), bf16_hi(rr.y)};
+                        float s4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) s4[e] = round_bf16(v[e]) + r4[e];
+                        const uint2 packed = make_uint2(pack_bf16(s4[0], s4[1]), pack_bf16(s4[2], s4[3]));
+                        *reinterpret_cast<uint2*>(rp) = packed;
+                        if (p.ssq_of_rounded) {
+                            s4[0] = bf16_lo(packed.x); s4[1] = bf16_hi(packed.x);
+                            s4[2] = bf16_lo(packed.y); s4[3] = bf16_hi(packed.y);
+                        }
+                        part = s4[0] * s4[0] + s4[1] * s4[1] + s4[2] * s4[2] + s4[3] * s4[3];
+                    }
+                    // the F / 4 neighbouring lanes hold the other features of the same token column
+                    for (int o = F / 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                    if ((i & (F / 4 - 1)) == 0 && m < rows)
+                        atomicAdd(p.ssq_out + x_row0 + m, static_cast<unsigned long long>(part * kSsqScale));
+                    continue;
+                }
+                if (valid) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         if (NUM_A == 2) {
@@ -428,14 +478,40 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t out
     return B200_OK;
 }
 
+static void set_fusion(SkinnyParams* p, const SkinnyFusion* f) {
+    p->ssq_in = f ? f->ssq_in : nullptr;
+    p->norm_eps = f ? f->eps : 0.f;
+    p->norm_width = f ? f->norm_width : 1;
+    p->residual = f ? static_cast<__nv_bfloat16*>(f->residual) : nullptr;
+    p->ssq_out = f ? f->ssq_out : nullptr;
+    p->ssq_of_rounded = f && f->ssq_of_rounded ? 1 : 0;
+}
+
 static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return (v && *v) ? atoi(v) : dflt;
 }
 
+// K split of a slab: up to one CTA per SM in total, at most 8 ranks (portable cluster size).
+int skinny_gemm_split(int M, int N, int K, int epilogue) {
+    (void)M;
+    const int n_out = epilogue != B200_EPILOGUE_NONE ? N / 2 : N;
+    const int kb_total = K / kBlockK;
+    const int n_tiles = div_ceil(n_out, kTileN);
+    const int forced = env_int("B200_GEMM_SPLIT", 0);
+    if (forced > 0) return forced;
+    // One CTA per SM at most: a CTA holds its whole K slice plus the exchange buffer, so two
+    // rarely fit on an SM, and a second wave would double the kernel's time.
+    int split = 1;
+    const int budget = sm_count();
+    while (split < 8 && n_tiles * split * 2 <= budget && split * 2 <= kb_total) split *= 2;
+    return split;
+}
+
 // One slab of at most 256 rows.
 int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, int M, int N,
-                       int K, int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
+                       int K, int64_t ldx, int epilogue, int* status, cudaStream_t stream,
+                       const SkinnyFusion* fuse = nullptr) {
     const bool gated = epilogue != B200_EPILOGUE_NONE;
     const int n_out = gated ? N / 2 : N;
     // accumulator columns: 32, or a multiple of the 64-column exchange round (the epilogue walks whole rounds)
@@ -443,17 +519,10 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     const int kb_total = K / kBlockK;
     const int n_tiles = div_ceil(n_out, kTileN);
     const int num_a = gated ? 2 : 1;
-
-    // K split: up to one CTA per SM in total, at most 8 ranks (portable cluster size).
-    int split = 1;
-    int forced = env_int("B200_GEMM_SPLIT", 0);
-    if (forced > 0) {
-        split = forced;
-    } else {
-        // One CTA per SM at most: a CTA holds its whole K slice plus the exchange buffer, so two
-        // rarely fit on an SM, and a second wave would double the kernel's time.
-        const int budget = sm_count();
-        while (split < 8 && n_tiles * split * 2 <= budget && split * 2 <= kb_total) split *= 2;
+    const int split = skinny_gemm_split(M, N, K, epilogue);
+    if (fuse != nullptr && split == 1) {
+        set_last_error("linear: the residual-stream fusions live in the split-K epilogue; this shape does not split");
+        return B200_ERR_UNSUPPORTED;
     }
     const int kbp = div_ceil(kb_total, split);
 
@@ -498,6 +567,7 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.group_counts = nullptr;
     p.group_offsets = nullptr;
     p.w_rows_per_group = 0;
+    set_fusion(&p, fuse);
 
     auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -562,6 +632,7 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
     p.group_counts = counts;
     p.group_offsets = offsets;
     p.w_rows_per_group = N;
+    set_fusion(&p, nullptr);
     auto kernel = skinny_kernel_for(epilogue);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
@@ -571,10 +642,15 @@ int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* co
 }
 
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
-                  int64_t ldx, int epilogue, int* status, cudaStream_t stream) {
+                  int64_t ldx, int epilogue, int* status, cudaStream_t stream, const SkinnyFusion* fuse) {
     // Few rows: stream the weights once (swap-AB, split-K).  Many rows: tensor-bound tiles.
-    if (M >= env_int("B200_GEMM_TILE_MIN_M", 257))
+    if (M >= env_int("B200_GEMM_TILE_MIN_M", 257)) {
+        if (fuse != nullptr) {
+            set_last_error("linear: the residual-stream fusions need at most 256 rows");
+            return B200_ERR_UNSUPPORTED;
+        }
         return launch_tile_gemm(y, x, w, bias, M, N, K, ldx, epilogue, status, stream);
+    }
     const int n_out = epilogue != B200_EPILOGUE_NONE ? N / 2 : N;
     const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
     __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
@@ -582,7 +658,7 @@ int launch_linear(void* y, const void* x, const void* w, const void* bias, int M
         const int rows = (M - m0) < 256 ? (M - m0) : 256;
         int err = launch_skinny_gemm(yp + static_cast<int64_t>(m0) * n_out,
                                      xp + static_cast<int64_t>(m0) * ldx, w, bias, rows, N, K, ldx,
-                                     epilogue, status, stream);
+                                     epilogue, status, stream, fuse);
         if (err != B200_OK) return err;
     }
     return B200_OK;

@@ -21,8 +21,13 @@ int launch_qknorm_rope_store(void* qkv, const void* q_weight, const void* k_weig
                              int max_pos, int64_t num_slots, float eps, int write_k_back,
                              int* status, cudaStream_t stream);
 int launch_act_and_mul(void* out, const void* in, int tokens, int d, bool gelu, cudaStream_t stream);
+// ssq (optional, [ssq_slots, ssq_stride]): slot 0 receives each row's sum of squares in 2^-24 fixed
+// point and the other slots are zeroed for the tokens of this call.
 int launch_embedding(void* out, const void* table, const int32_t* ids, int tokens, int hidden,
-                     int vocab, int* status, cudaStream_t stream);
+                     int vocab, int* status, cudaStream_t stream, unsigned long long* ssq = nullptr,
+                     int ssq_slots = 0, int ssq_stride = 0);
+// out[n, k] = bf16(w[n, k] * scale[k]): a norm weight folded into the columns of the matrix that follows it.
+int launch_scale_columns(void* out, const void* w, const void* scale, int64_t rows, int K, cudaStream_t stream);
 // step_index_dev (optional): the step index is read from device memory instead of the argument, so a
 // captured graph replays with a new value.
 int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
@@ -45,9 +50,28 @@ int launch_grouped_tile_gemm(void* y, const void* x, const void* w, const int32_
                              const int32_t* offsets, int num_groups, int64_t total_rows, int N, int K,
                              int epilogue, int* status, cudaStream_t stream);
 
+// Fusions of a split-K GEMM of at most 256 rows with the residual stream of a decode step.  Row
+// statistics travel as sums of squares in 2^-24 fixed point (integer atomics: the same bits whatever
+// order the CTAs finish in).
+//  - ssq_in: the rows of x are un-normalised and w has the norm weight folded into its columns; the
+//    accumulator of row m is multiplied by rsqrt(ssq_in[m] / 2^24 / norm_width + eps).
+//  - residual: y is not written; residual[m, n] becomes bf16(bf16(acc) + residual[m, n]) and
+//    ssq_out[m] grows by the squares of those sums (of the stored bf16 values if ssq_of_rounded).
+struct SkinnyFusion {
+    const unsigned long long* ssq_in = nullptr;
+    float eps = 0.f;
+    int norm_width = 1;
+    void* residual = nullptr;
+    unsigned long long* ssq_out = nullptr;
+    bool ssq_of_rounded = false;
+};
+// The K split launch_linear picks for a slab of this shape (the fusions need it above 1).
+int skinny_gemm_split(int M, int N, int K, int epilogue);
+
 // y[M, n_out] = x[M, K] w[N, K]^T (+bias / gated epilogue); any M (slabs of 256 rows).
 int launch_linear(void* y, const void* x, const void* w, const void* bias, int M, int N, int K,
-                  int64_t ldx, int epilogue, int* status, cudaStream_t stream);
+                  int64_t ldx, int epilogue, int* status, cudaStream_t stream,
+                  const SkinnyFusion* fuse = nullptr);
 
 int launch_grouped_gemm(void* y, const void* x, const void* w, const int32_t* counts,
                         const int32_t* offsets, int num_groups, int max_rows_per_group,

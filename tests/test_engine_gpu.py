@@ -140,6 +140,7 @@ def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_p
     lens = rng.integers(3, 70, size=nreq)
     prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).astype(np.int32) for n in lens]
     outs = {}
+    monkeypatch.setenv("B200_FOLD_NORM", "0")   # the chain is compared with the plain one-kernel-per-operator path
     for chain in ("0", "1"):
         monkeypatch.setenv("B200_DECODE_CHAIN", chain)
         pr = Pair(pkg, cfg, 16, num_pages=nreq * 6 + 8, max_running_req=max(nreq, 8))
@@ -178,6 +179,70 @@ def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_p
     assert outs["1"][1] == 9 + 3 * cfg.num_layers, outs["1"][1]
     d = (outs["1"][0].float() - outs["0"][0].float()).abs()
     assert float(d.max()) <= MAX_ABS and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
+
+
+@pytest.mark.parametrize("kind,nreq", [("qwen3", 3), ("qwen3", 64), ("llama", 5), ("qwen2", 37), ("qwen3", 200)])
+def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq):
+    """Decode steps of dense, unsharded models have no add + norm kernels: o_proj and down_proj add the
+    residual and accumulate each row's sum of squares in their split-K epilogue, qkv_proj and
+    gate_up_proj multiply un-normalised rows by weights with the norm weight folded in and scale by
+    1 / rms afterwards.  The same requests with that (the default) and without (B200_FOLD_NORM=0, read
+    when the engine is created): each against the oracle at the usual bars, and against one another
+    (the folded form rounds the normalised activation at a different point: about one bf16 step of a logit)."""
+    cfg = small_cfg(kind)
+    rng = np.random.default_rng(23)
+    lens = rng.integers(3, 40, size=nreq)
+    prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).astype(np.int32) for n in lens]
+    outs = {}
+    for fold in ("0", "1"):
+        monkeypatch.setenv("B200_FOLD_NORM", fold)
+        pr = Pair(pkg, cfg, 16, num_pages=nreq * 4 + 8, max_running_req=max(nreq, 8))
+        reqs = [pr.hb.add_request(p, 6) for p in prompts]
+        pr.host_tokens = {r.table_idx: list(p) + [0] * 16 for r, p in zip(reqs, prompts)}
+        for i in range(0, nreq, 16):
+            pr.hb.allocate(reqs[i:i + 16])
+            ob, pt = pr.oracle_batch(reqs[i:i + 16], True)
+            want = pr.oracle.forward(ob, pr.kv, pt)
+            out = pr.hb.prefill(reqs[i:i + 16])
+            out.synchronize()
+            tok = want.argmax(-1).tolist()
+            for r, t in zip(reqs[i:i + 16], tok):
+                pr.host_tokens[r.table_idx][r.cached_len] = t
+            pr.engine.write_token_pool([r.table_idx for r in reqs[i:i + 16]], [r.cached_len for r in reqs[i:i + 16]], tok)
+        steps = []
+        for step in range(3):
+            pr.hb.allocate(reqs)
+            ob, pt = pr.oracle_batch(reqs, False)
+            want = pr.oracle.forward(ob, pr.kv, pt)
+            out = pr.hb.decode(reqs, padded_size=min(nreq + (step % 2), 256))
+            out.synchronize()
+            got = pr.engine.logits(nreq)
+            check_logits(got, want, f"{kind} fold={fold} decode step {step}")
+            steps.append(got.clone())
+            tok = want.argmax(-1).tolist()
+            for r, t in zip(reqs, tok):
+                pr.host_tokens[r.table_idx][r.cached_len] = t
+            pr.engine.write_token_pool([r.table_idx for r in reqs], [r.cached_len for r in reqs], tok)
+        # norm weights loaded after steps have run must reach the folded copies: one more step, compared
+        # between the two engines only
+        g = torch.Generator().manual_seed(5)
+        for l in range(cfg.num_layers):
+            for name in ("input_norm", "post_norm"):
+                pr.engine.load(name, l, (0.5 + torch.rand(cfg.hidden_size, generator=g)).to(torch.bfloat16))
+        pr.hb.allocate(reqs)
+        out = pr.hb.decode(reqs)
+        out.synchronize()
+        steps.append(pr.engine.logits(nreq).clone())
+        _, _, launches = pr.engine.read_profile()
+        outs[fold] = (torch.stack(steps), launches)
+        assert pr.engine_status_clean()
+        pr.engine.close()
+    # prepare, embedding, (qkv, rope, attention, merge, o, gate_up, down) per layer, final norm, lm_head, argmax, write-back
+    assert outs["1"][1] == 6 + 7 * cfg.num_layers, outs["1"][1]
+    assert outs["0"][1] == 6 + 9 * cfg.num_layers, outs["0"][1]
+    d = (outs["1"][0].float() - outs["0"][0].float()).abs()
+    rms = float(outs["0"][0].float().pow(2).mean().sqrt())
+    assert float(d.max()) <= MAX_ABS and float(d.mean()) <= MEAN_ABS + rms * 2 ** -8, (float(d.max()), float(d.mean()))
 
 
 def test_engine_writes_its_own_tokens_back(pkg):
