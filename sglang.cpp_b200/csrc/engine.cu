@@ -231,6 +231,7 @@ struct b200_engine {
     // qkv_proj and gate_up_proj read the un-normalised residual against weights with the norm weight
     // folded in, and scale their accumulator by the row's 1 / rms.  B200_FOLD_NORM=0 turns it off.
     bool use_fold = true;
+    bool use_fold_heads = true;         // B200_FOLD_HEADS=0: QK-norm + RoPE + K/V store stay a kernel of their own
     bool folded_valid = false;          // the folded copies match qkv / gate_up / the norm weights
     unsigned long long* ssq = nullptr;  // [2 * layers + 1, kSsqStride] sums of squares of the residual rows
     static constexpr int kSsqStride = 256;
@@ -489,13 +490,35 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         into_residual.residual = e->residual;
         into_residual.ssq_of_rounded = round_first;
         normed.ssq_in = ssq_l;
-        B200_TRY(launch_linear(e->qkv, e->residual, L.qkv_folded, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
-                               B200_EPILOGUE_NONE, e->status, s, &normed));
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
         __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
-        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin, e->positions,
-                                          e->out_loc, k_cache, v_cache, T, e->hq, e->hkv, d, m.max_position,
-                                          e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        if (e->use_fold_heads && d == 128) {
+            // ... and the QK-norm, the rotation and the K/V store ride in the qkv projection's epilogue
+            HeadEpilogue he;
+            he.q_norm_w = L.q_norm;
+            he.k_norm_w = L.k_norm;
+            he.cos_t = e->rope_cos;
+            he.sin_t = e->rope_sin;
+            he.positions = e->positions;
+            he.out_loc = e->out_loc;
+            he.k_cache = k_cache;
+            he.v_cache = v_cache;
+            he.q_heads = e->hq;
+            he.kv_heads = e->hkv;
+            he.max_pos = m.max_position;
+            he.num_slots = e->num_slots;
+            he.eps = m.rms_norm_eps;
+            normed.heads = &he;
+            B200_TRY(launch_linear(e->qkv, e->residual, L.qkv_folded, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                                   B200_EPILOGUE_NONE, e->status, s, &normed));
+            normed.heads = nullptr;
+        } else {
+            B200_TRY(launch_linear(e->qkv, e->residual, L.qkv_folded, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                                   B200_EPILOGUE_NONE, e->status, s, &normed));
+            B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin, e->positions,
+                                              e->out_loc, k_cache, v_cache, T, e->hq, e->hkv, d, m.max_position,
+                                              e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        }
         const bool timed = e->profile_attention && !e->capturing;
         if (timed) {
             while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
@@ -804,6 +827,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
                         false));
     }
     if (const char* v = getenv("B200_FOLD_NORM")) e->use_fold = atoi(v) != 0;
+    if (const char* v = getenv("B200_FOLD_HEADS")) e->use_fold_heads = atoi(v) != 0;
     if (e->use_fold && c.tp_size == 1 && m.num_experts == 0) {
         for (LayerWeights& L : e->layers) {
             void* p = nullptr;

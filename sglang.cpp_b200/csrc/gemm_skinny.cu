@@ -111,6 +111,20 @@ struct SkinnyParams {
     __nv_bfloat16* residual;            // "residual output": residual[m, n] = bf16(bf16(acc) + residual[m, n]), y unused
     unsigned long long* ssq_out;        // ... and ssq_out[m] += (that sum)^2 in 2^-24 fixed point
     int ssq_of_rounded;                 // square the stored (bf16) sum instead of the fp32 one
+    // "attention heads": every 128-feature tile is one head of a packed qkv projection; the epilogue
+    // applies the per-head RMS norm and the NeoX rotation and stores K / V into the pool.
+    int head_mode;
+    const __nv_bfloat16* q_norm_w;      // [128] or NULL
+    const __nv_bfloat16* k_norm_w;
+    const float* cos_t;                 // [max_pos, 64]
+    const float* sin_t;
+    const int32_t* positions;           // [M]
+    const int32_t* out_loc;             // [M]
+    __nv_bfloat16* k_cache;             // [num_slots, kv_heads, 128]
+    __nv_bfloat16* v_cache;
+    int q_heads, kv_heads, max_pos;
+    long long num_slots;
+    float qk_eps;
 };
 constexpr float kSsqScale = 16777216.0f;   // 2^24
 
@@ -163,6 +177,22 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int kb_begin = static_cast<int>(rank) * kbp;
     const int my_kb = max(0, min(kb_begin + kbp, p.kb_total) - kb_begin);
     const int n0 = blockIdx.x * kTileN;
+    const int F = kTileN / static_cast<int>(split);     // features owned by one rank
+    const int cpr = nt < kRoundCols ? nt : kRoundCols;  // token columns per exchange round
+    // Head epilogue: the exchange is by token instead of by feature - a rank owns cpr / split token
+    // columns of a round with all 128 features, so a head's sum of squares and both elements of every
+    // rotation pair are in one CTA.  Its scratch sits behind the exchange buffers: cos | sin
+    // [nt / split][64] for the owned tokens, then their pool slots [nt / split].
+    const int cpl = cpr / static_cast<int>(split);      // token columns of a round owned by one rank
+    const int head_kind = (NUM_A != 1 || !p.head_mode) ? -1 : (static_cast<int>(blockIdx.x) < p.q_heads ? 0
+                          : static_cast<int>(blockIdx.x) < p.q_heads + p.kv_heads ? 1 : 2);   // q, k, v
+    const __nv_bfloat16* head_w = head_kind == 0 ? p.q_norm_w : head_kind == 1 ? p.k_norm_w : nullptr;
+    const uint32_t head_off = static_cast<uint32_t>(p.stages) * (NUM_A * kTileN * kBlockK * 2 + static_cast<uint32_t>(nt) * kBlockK * 2) +
+                              (nt > cpr ? 2u : 1u) * NUM_A * cpr * kTileN * 4u;
+    const int owned_tokens = nt / static_cast<int>(split);
+    float* s_cos = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + head_off);
+    float* s_sin = s_cos + owned_tokens * (kTileN / 2);
+    int* s_slot = reinterpret_cast<int*>(s_sin + owned_tokens * (kTileN / 2));
 
     // TMEM columns: NUM_A accumulators of nt columns, rounded up to a power of two >= 32.
     uint32_t tmem_cols = 32;
@@ -254,6 +284,38 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 mbar_arrive(smem_u32(&tmem_full_bar));
         }
     } else {
+        if (head_kind >= 0) {
+            // positions, slots and the rotation table are complete before the layer stack starts:
+            // fetched ahead of the wait, under the weight stream
+            const int te = static_cast<int>(threadIdx.x) - 64;
+            // owned token lm of round r is column r * cpr + rank * cpl + lm % cpl of the accumulator
+            auto token_of = [&](int lm) { return (lm / cpl) * cpr + static_cast<int>(rank) * cpl + lm % cpl; };
+            if (head_kind < 2) {
+                for (int idx = te; idx < owned_tokens * (kTileN / 8); idx += kThreads - 64) {
+                    const int lm = idx / (kTileN / 8), j4 = idx % (kTileN / 8) * 4;
+                    const int m = token_of(lm);
+                    int pos = m < rows ? p.positions[x_row0 + m] : 0;
+                    if (pos < 0 || pos >= p.max_pos) {
+                        if (j4 == 0) atomicExch(&p.status[kStatusBadIndex], pos + 1);
+                        pos = min(max(pos, 0), p.max_pos - 1);
+                    }
+                    const int64_t at = static_cast<int64_t>(pos) * (kTileN / 2) + j4;
+                    *reinterpret_cast<float4*>(s_cos + lm * (kTileN / 2) + j4) = *reinterpret_cast<const float4*>(p.cos_t + at);
+                    *reinterpret_cast<float4*>(s_sin + lm * (kTileN / 2) + j4) = *reinterpret_cast<const float4*>(p.sin_t + at);
+                }
+            }
+            if (head_kind > 0) {
+                for (int lm = te; lm < owned_tokens; lm += kThreads - 64) {
+                    const int m = token_of(lm);
+                    int slot = m < rows ? p.out_loc[x_row0 + m] : -1;
+                    if (m < rows && (slot < 0 || slot >= p.num_slots)) {
+                        atomicExch(&p.status[kStatusBadIndex], slot + 1);
+                        slot = -1;
+                    }
+                    s_slot[lm] = slot;
+                }
+            }
+        }
         pdl_wait_prior();
         if (p.ssq_in != nullptr) {
             // the row statistics come from the kernel before this one; the cluster barrier of the first
@@ -277,9 +339,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const bool is_epi = warp >= 2;
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
     const int feat_local = q * 32 + lane;         // feature row inside the tile
-    const int cpr = nt < kRoundCols ? nt : kRoundCols;  // token columns per exchange round
     const int nrounds = nt / cpr;
-    const int F = kTileN / static_cast<int>(split);     // features owned by one rank
     const uint32_t round_bytes = static_cast<uint32_t>(NUM_A) * cpr * kTileN * 4u;
     const uint32_t xbuf_addr = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
     const float* xbuf = reinterpret_cast<const float*>(smem_raw + (xbuf_addr - smem_u32(smem_raw)));
@@ -333,6 +393,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             }
                         }
                     }
+                } else if (head_kind >= 0) {
+                    // owner layout: [source rank][owned column][feature]; the owner changes every cpl columns
+                    const int cpl_shift = 31 - __clz(cpl);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = cc * kChunkCols + j;
+                        const uint32_t local = xbuf_addr + buf_off +
+                                               ((rank * cpl + (col & (cpl - 1))) * kTileN + feat_local) * 4u;
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col >> cpl_shift));
+                        st_dsmem_f32(remote, __uint_as_float(g[j]));
+                    }
                 } else {
                     // owner layout: [source rank][accumulator][column][owned feature]
                     const uint32_t dst0 = remote_base + buf_off +
@@ -349,6 +421,94 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (split == 1) continue;
 
         cluster_sync_all();
+        if (head_kind >= 0) {
+            // ---- head epilogue (plain projection only): eight lanes per owned token, lane `sub` holds
+            // features [8 sub, 8 sub + 8) of each half of the head, so a rotation pair is in one lane ----
+            if (is_epi) {
+                const int te = (warp - 2) * 32 + lane;
+                const float* rb = xbuf + buf_off / 4u;
+                for (int base = 0; base < cpl * 8; base += 128) {
+                    const int i = base + te;
+                    const bool active = i < cpl * 8;          // (whole groups of eight lanes)
+                    const int tl = active ? i >> 3 : 0, sub = i & 7;
+                    const int m = r * cpr + static_cast<int>(rank) * cpl + tl;
+                    const int lm = r * cpl + tl;
+                    float x1[8], x2[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x1[e] = x2[e] = 0.f;
+#pragma unroll
+                    for (uint32_t rr = 0; rr < 8; ++rr) {
+                        if (rr < split) {
+                            const float* src = rb + (rr * cpl + tl) * kTileN + sub * 8;
+                            const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
+                            const float4 b0 = *reinterpret_cast<const float4*>(src + 64), b1 = *reinterpret_cast<const float4*>(src + 68);
+                            x1[0] += a0.x; x1[1] += a0.y; x1[2] += a0.z; x1[3] += a0.w;
+                            x1[4] += a1.x; x1[5] += a1.y; x1[6] += a1.z; x1[7] += a1.w;
+                            x2[0] += b0.x; x2[1] += b0.y; x2[2] += b0.z; x2[3] += b0.w;
+                            x2[4] += b1.x; x2[5] += b1.y; x2[6] += b1.z; x2[7] += b1.w;
+                        }
+                    }
+                    // the projection's own output, as the unfused path stores it: bf16(acc * rstd + bias)
+                    const float rs = p.ssq_in != nullptr ? s_rstd[m] : 1.0f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        x1[e] *= rs;
+                        x2[e] *= rs;
+                        if (p.bias) {
+                            x1[e] += __bfloat162float(p.bias[n0 + sub * 8 + e]);
+                            x2[e] += __bfloat162float(p.bias[n0 + 64 + sub * 8 + e]);
+                        }
+                        x1[e] = round_bf16(x1[e]);
+                        x2[e] = round_bf16(x2[e]);
+                    }
+                    const bool live = active && m < rows;
+                    __nv_bfloat16* dst = nullptr;
+                    if (head_kind == 0) {
+                        dst = p.y + static_cast<int64_t>(x_row0 + m) * p.n_out + n0;
+                    } else if (live && s_slot[lm] >= 0) {
+                        const int kvh = static_cast<int>(blockIdx.x) - p.q_heads - (head_kind == 2 ? p.kv_heads : 0);
+                        dst = (head_kind == 1 ? p.k_cache : p.v_cache) +
+                              (static_cast<int64_t>(s_slot[lm]) * p.kv_heads + kvh) * kTileN;
+                    }
+                    if (head_kind < 2) {
+                        if (head_w != nullptr) {
+                            float ss = 0.f;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                            const float scale = rsqrtf(ss / static_cast<float>(kTileN) + p.qk_eps);
+                            const uint4 wa = *reinterpret_cast<const uint4*>(head_w + sub * 8);
+                            const uint4 wb = *reinterpret_cast<const uint4*>(head_w + 64 + sub * 8);
+                            const uint32_t wa4[4] = {wa.x, wa.y, wa.z, wa.w}, wb4[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                x1[2 * e] = round_bf16(x1[2 * e] * scale * bf16_lo(wa4[e]));
+                                x1[2 * e + 1] = round_bf16(x1[2 * e + 1] * scale * bf16_hi(wa4[e]));
+                                x2[2 * e] = round_bf16(x2[2 * e] * scale * bf16_lo(wb4[e]));
+                                x2[2 * e + 1] = round_bf16(x2[2 * e + 1] * scale * bf16_hi(wb4[e]));
+                            }
+                        }
+                        const float* cs = s_cos + lm * (kTileN / 2) + sub * 8;
+                        const float* sn = s_sin + lm * (kTileN / 2) + sub * 8;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float a = x1[e], b = x2[e];
+                            x1[e] = a * cs[e] - b * sn[e];
+                            x2[e] = b * cs[e] + a * sn[e];
+                        }
+                    }
+                    if (live && dst != nullptr) {
+                        *reinterpret_cast<uint4*>(dst + sub * 8) = make_uint4(pack_bf16(x1[0], x1[1]), pack_bf16(x1[2], x1[3]),
+                                                                            pack_bf16(x1[4], x1[5]), pack_bf16(x1[6], x1[7]));
+                        *reinterpret_cast<uint4*>(dst + 64 + sub * 8) = make_uint4(pack_bf16(x2[0], x2[1]), pack_bf16(x2[2], x2[3]),
+                                                                                 pack_bf16(x2[4], x2[5]), pack_bf16(x2[6], x2[7]));
+                    }
+                }
+            }
+            continue;
+        }
         if (is_epi) {
             // F / 4 is a power of two (split is 2, 4 or 8): shifts instead of divisions.
             const int f4_shift = 31 - __clz(F / 4);
@@ -485,6 +645,21 @@ static void set_fusion(SkinnyParams* p, const SkinnyFusion* f) {
     p->residual = f ? static_cast<__nv_bfloat16*>(f->residual) : nullptr;
     p->ssq_out = f ? f->ssq_out : nullptr;
     p->ssq_of_rounded = f && f->ssq_of_rounded ? 1 : 0;
+    const HeadEpilogue* h = f ? f->heads : nullptr;
+    p->head_mode = h ? 1 : 0;
+    p->q_norm_w = h ? static_cast<const __nv_bfloat16*>(h->q_norm_w) : nullptr;
+    p->k_norm_w = h ? static_cast<const __nv_bfloat16*>(h->k_norm_w) : nullptr;
+    p->cos_t = h ? h->cos_t : nullptr;
+    p->sin_t = h ? h->sin_t : nullptr;
+    p->positions = h ? h->positions : nullptr;
+    p->out_loc = h ? h->out_loc : nullptr;
+    p->k_cache = h ? static_cast<__nv_bfloat16*>(h->k_cache) : nullptr;
+    p->v_cache = h ? static_cast<__nv_bfloat16*>(h->v_cache) : nullptr;
+    p->q_heads = h ? h->q_heads : 0;
+    p->kv_heads = h ? h->kv_heads : 0;
+    p->max_pos = h ? h->max_pos : 1;
+    p->num_slots = h ? h->num_slots : 0;
+    p->qk_eps = h ? h->eps : 0.f;
 }
 
 static int env_int(const char* name, int dflt) {
@@ -528,7 +703,19 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
 
     const uint32_t stage_bytes = num_a * kTileN * kBlockK * 2 + nt * kBlockK * 2;
     const int cpr = nt < kRoundCols ? nt : kRoundCols;
-    const uint32_t exch_bytes = split > 1 ? (nt > cpr ? 2u : 1u) * num_a * cpr * kTileN * 4u : 0u;
+    uint32_t exch_bytes = split > 1 ? (nt > cpr ? 2u : 1u) * num_a * cpr * kTileN * 4u : 0u;
+    if (fuse != nullptr && fuse->heads != nullptr) {
+        if (gated || N != (fuse->heads->q_heads + 2 * fuse->heads->kv_heads) * kTileN) {
+            set_last_error("linear: the head epilogue wants a plain projection of (q_heads + 2 kv_heads) x 128 features");
+            return B200_ERR_INVALID_ARGUMENT;
+        }
+        if (cpr % split != 0) {
+            set_last_error("linear: the head epilogue needs the K split (%d) to divide the %d token columns of a round", split, cpr);
+            return B200_ERR_UNSUPPORTED;
+        }
+        // cos | sin [nt / split][64] and the slots [nt / split] of the tokens a rank owns
+        exch_bytes += static_cast<uint32_t>(nt / split) * (kTileN * 4u + 4u) + 16u;
+    }
     const uint32_t smem_limit = 200 * 1024;
     int stages = kbp < kMaxStages ? kbp : kMaxStages;
     // More tiles than SMs (lm_head): keep the ring small enough for two CTAs per SM, so one CTA's

@@ -57,6 +57,22 @@ int launch_grouped_tile_gemm(void* y, const void* x, const void* w, const int32_
 //    accumulator of row m is multiplied by rsqrt(ssq_in[m] / 2^24 / norm_width + eps).
 //  - residual: y is not written; residual[m, n] becomes bf16(bf16(acc) + residual[m, n]) and
 //    ssq_out[m] grows by the squares of those sums (of the stored bf16 values if ssq_of_rounded).
+//  - heads: the projection is a packed qkv projection with 128-wide heads; instead of y[:, all] the
+//    epilogue writes the rotated (and, with norm weights, RMS-normalised) q heads into y and the k / v
+//    heads into the pool at out_loc - what launch_qknorm_rope_store does after a plain projection.
+struct HeadEpilogue {
+    const void* q_norm_w = nullptr;   // [128] bf16 or NULL
+    const void* k_norm_w = nullptr;
+    const float* cos_t = nullptr;     // [max_pos, 64]
+    const float* sin_t = nullptr;
+    const int32_t* positions = nullptr;
+    const int32_t* out_loc = nullptr;
+    void* k_cache = nullptr;          // [num_slots, kv_heads, 128] bf16
+    void* v_cache = nullptr;
+    int q_heads = 0, kv_heads = 0, max_pos = 1;
+    int64_t num_slots = 0;
+    float eps = 0.f;
+};
 struct SkinnyFusion {
     const unsigned long long* ssq_in = nullptr;
     float eps = 0.f;
@@ -64,6 +80,7 @@ struct SkinnyFusion {
     void* residual = nullptr;
     unsigned long long* ssq_out = nullptr;
     bool ssq_of_rounded = false;
+    const HeadEpilogue* heads = nullptr;
 };
 // The K split launch_linear picks for a slab of this shape (the fusions need it above 1).
 int skinny_gemm_split(int M, int N, int K, int epilogue);

@@ -181,15 +181,19 @@ def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_p
     assert float(d.max()) <= MAX_ABS and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
 
 
+@pytest.mark.parametrize("fold_heads", ["1", "0"])
 @pytest.mark.parametrize("kind,nreq", [("qwen3", 3), ("qwen3", 64), ("llama", 5), ("qwen2", 37), ("qwen3", 200)])
-def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq):
+def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq, fold_heads):
     """Decode steps of dense, unsharded models have no add + norm kernels: o_proj and down_proj add the
     residual and accumulate each row's sum of squares in their split-K epilogue, qkv_proj and
     gate_up_proj multiply un-normalised rows by weights with the norm weight folded in and scale by
     1 / rms afterwards.  The same requests with that (the default) and without (B200_FOLD_NORM=0, read
     when the engine is created): each against the oracle at the usual bars, and against one another
-    (the folded form rounds the normalised activation at a different point: about one bf16 step of a logit)."""
+    (the folded form rounds the normalised activation at a different point: about one bf16 step of a logit).
+    fold_heads: the qkv projection's epilogue also applies the QK-norm and the rotation to whole heads and
+    stores K / V into the pool (B200_FOLD_HEADS=0 keeps that a kernel of its own)."""
     cfg = small_cfg(kind)
+    monkeypatch.setenv("B200_FOLD_HEADS", fold_heads)
     rng = np.random.default_rng(23)
     lens = rng.integers(3, 40, size=nreq)
     prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).astype(np.int32) for n in lens]
@@ -237,8 +241,9 @@ def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq):
         outs[fold] = (torch.stack(steps), launches)
         assert pr.engine_status_clean()
         pr.engine.close()
-    # prepare, embedding, (qkv, rope, attention, merge, o, gate_up, down) per layer, final norm, lm_head, argmax, write-back
-    assert outs["1"][1] == 6 + 7 * cfg.num_layers, outs["1"][1]
+    # prepare, embedding, (qkv [+ rope], attention, merge, o, gate_up, down) per layer, final norm, lm_head, argmax, write-back
+    per_layer = 7 if fold_heads == "0" else 6
+    assert outs["1"][1] == 6 + per_layer * cfg.num_layers, outs["1"][1]
     assert outs["0"][1] == 6 + 9 * cfg.num_layers, outs["0"][1]
     d = (outs["1"][0].float() - outs["0"][0].float()).abs()
     rms = float(outs["0"][0].float().pow(2).mean().sqrt())
