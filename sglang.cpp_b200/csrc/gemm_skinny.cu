@@ -128,7 +128,9 @@ struct SkinnyParams {
 };
 constexpr float kSsqScale = 16777216.0f;   // 2^24
 
-template <int EPI>
+// HEADS: the attention-head epilogue (plain projections only) is compiled into an instance of its own;
+// it needs about 90 registers more than the rest, which would cost lm_head its second CTA per SM.
+template <int EPI, bool HEADS = false>
 __global__ void __launch_bounds__(kThreads, 1)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_x,
@@ -184,7 +186,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // rotation pair are in one CTA.  Its scratch sits behind the exchange buffers: cos | sin
     // [nt / split][64] for the owned tokens, then their pool slots [nt / split].
     const int cpl = cpr / static_cast<int>(split);      // token columns of a round owned by one rank
-    const int head_kind = (NUM_A != 1 || !p.head_mode) ? -1 : (static_cast<int>(blockIdx.x) < p.q_heads ? 0
+    const int head_kind = !HEADS ? -1 : (static_cast<int>(blockIdx.x) < p.q_heads ? 0
                           : static_cast<int>(blockIdx.x) < p.q_heads + p.kv_heads ? 1 : 2);   // q, k, v
     const __nv_bfloat16* head_w = head_kind == 0 ? p.q_norm_w : head_kind == 1 ? p.k_norm_w : nullptr;
     const uint32_t head_off = static_cast<uint32_t>(p.stages) * (NUM_A * kTileN * kBlockK * 2 + static_cast<uint32_t>(nt) * kBlockK * 2) +
@@ -597,7 +599,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 using SkinnyKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, SkinnyParams);
-SkinnyKernel skinny_kernel_for(int epilogue) {
+SkinnyKernel skinny_kernel_for(int epilogue, bool heads = false) {
+    if (heads) return skinny_gemm_kernel<B200_EPILOGUE_NONE, true>;
     switch (epilogue) {
         case B200_EPILOGUE_SWIGLU: return skinny_gemm_kernel<B200_EPILOGUE_SWIGLU>;
         case B200_EPILOGUE_GEGLU: return skinny_gemm_kernel<B200_EPILOGUE_GEGLU>;
@@ -756,7 +759,7 @@ int launch_skinny_gemm(void* y, const void* x, const void* w, const void* bias, 
     p.w_rows_per_group = 0;
     set_fusion(&p, fuse);
 
-    auto kernel = skinny_kernel_for(epilogue);
+    auto kernel = skinny_kernel_for(epilogue, p.head_mode != 0);
     B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem_bytes)));
     B200_CHECK_CUDA(launch_kernel(kernel, dim3(n_tiles, split, 1), dim3(kThreads), smem_bytes, stream,
