@@ -32,6 +32,7 @@ for a profiler's launch list.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import math
 import os
@@ -613,8 +614,14 @@ def run_gpu_tp(args, dist_ready=False, as_record=False):
     engine = Engine(cfg, EngineConfig(PAGE_SIZE, num_pages, B, PROMPT + total_new + 1, MAX_EXTEND_TOKENS, rank, world,
                                       expert_parallel=moe and world > 1))
     engine.fill_random(seed=0)
+    in_switch = False
     if world > 1:
         engine.connect_tp()
+        lib = pkg.load_library()
+        in_switch = bool(lib.b200_comm_uses_multicast(ctypes.c_void_p(lib.b200_engine_comm(engine._h))))
+    data_path = ("allreduce kernels of csrc/allreduce.cu, sums formed inside the NVLink switch (multimem.ld_reduce / "
+                 "multimem.st on a symmetric-memory multicast address); NCCL only for the rendezvous" if in_switch else
+                 "allreduce kernels of csrc/allreduce.cu over CUDA-IPC peer memory; NCCL only for the rendezvous")
     hb = HostBatcher(engine, num_pages, PAGE_SIZE, B, enable_prefix_cache=False)
     reqs, batch = [], []
     t0 = time.perf_counter()
@@ -702,7 +709,7 @@ def run_gpu_tp(args, dist_ready=False, as_record=False):
                                 if moe else
                          "c4: Llama-3-8B decode, batch 128, prompts of 1024 random tokens, page size 16, greedy"),
                    "parallelism": (f"ep{world}+tp{world}" if moe else f"tp{world}"), "mean_context": mean_ctx,
-                   "ranks_in_lockstep": lockstep},
+                   "ranks_in_lockstep": lockstep, "data_path": data_path if world > 1 else "single GPU"},
         "step_roofline": {"algorithmic_bytes_per_step_per_gpu": int(bytes_gpu),
                           "frac_of_measured_hbm": round(bytes_gpu / (dev_ms / K * 1e-3) / 1e9 / peak, 4)},
         "prefill": {"tokens": B * PROMPT, "seconds": round(prefill_s, 3)},
@@ -722,7 +729,7 @@ def run_gpu_tp(args, dist_ready=False, as_record=False):
                 "attention_us_per_launch": line["kernels"]["attention_us_per_launch"],
                 "allreduce_us_per_launch": line["kernels"]["allreduce_us_per_launch"],
                 "allreduce_launches_per_step": line["kernels"]["allreduce_launches_per_step"],
-                "data_path": "allreduce kernels of csrc/allreduce.cu over CUDA-IPC peer memory; NCCL only for the rendezvous"}
+                "data_path": data_path}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -295,18 +295,20 @@ int build_rope_tables(b200_engine* e) {
     return B200_OK;
 }
 
-// Can this step run with the add + norm kernels folded into the GEMMs around them?
+// Do the four projections of a layer all split along K (the fusions live in the split-K epilogue; the
+// split does not depend on the number of tokens)?
+bool fold_shapes_ok(const b200_engine* e) {
+    const int H = e->m.hidden_size, D = e->m.head_dim;
+    return skinny_gemm_split(1, e->qkv_dim, H, B200_EPILOGUE_NONE) > 1 &&
+           skinny_gemm_split(1, H, e->hq * D, B200_EPILOGUE_NONE) > 1 &&
+           skinny_gemm_split(1, 2 * e->inter, H, B200_EPILOGUE_SWIGLU) > 1 &&
+           skinny_gemm_split(1, H, e->inter, B200_EPILOGUE_NONE) > 1;
+}
+
+// Can this step run with the add + norm kernels folded into the GEMMs around them?  (The statistics
+// buffer exists only for dense, unsharded engines whose shapes qualify.)
 bool fold_supported(const b200_engine* e, int phase, int T) {
-    const b200_model_config& m = e->m;
-    if (!e->use_fold || e->ssq == nullptr || phase != B200_PHASE_DECODE || e->c.tp_size > 1 || m.num_experts > 0 ||
-        T > b200_engine::kSsqStride)
-        return false;
-    // every one of the four GEMMs must split along K: the fusions live in the split-K epilogue
-    const int H = m.hidden_size, D = m.head_dim;
-    return skinny_gemm_split(T, e->qkv_dim, H, B200_EPILOGUE_NONE) > 1 &&
-           skinny_gemm_split(T, H, e->hq * D, B200_EPILOGUE_NONE) > 1 &&
-           skinny_gemm_split(T, 2 * e->inter, H, B200_EPILOGUE_SWIGLU) > 1 &&
-           skinny_gemm_split(T, H, e->inter, B200_EPILOGUE_NONE) > 1;
+    return e->ssq != nullptr && phase == B200_PHASE_DECODE && T <= b200_engine::kSsqStride;
 }
 
 // Rebuilds the folded weight copies after a weight was loaded.  Enqueued on the engine's stream, never
@@ -402,6 +404,10 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         return launch_fused_add_rmsnorm(e->x, e->residual, w, T, hidden, m.rms_norm_eps, round_first, s);
     };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
+    // The head epilogue of the qkv projection wants the split-K form of the small-batch kernel; beyond
+    // two exchange rounds (128 tokens) the separate kernel is the faster of the two.
+    const bool heads_in_qkv = e->use_fold_heads && d == 128 && T <= 128 &&
+                              skinny_gemm_split(T, e->qkv_dim, hidden, B200_EPILOGUE_NONE) > 1;
 
     // Decode batches of at most 64 tokens of a dense, unsharded model: everything between two attention
     // launches is one persistent kernel (decode_chain.cu) instead of seven launches.
@@ -492,7 +498,7 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
         normed.ssq_in = ssq_l;
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
         __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
-        if (e->use_fold_heads && d == 128) {
+        if (heads_in_qkv) {
             // ... and the QK-norm, the rotation and the K/V store ride in the qkv projection's epilogue
             HeadEpilogue he;
             he.q_norm_w = L.q_norm;
@@ -550,13 +556,35 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     for (int l = 0; l < (chain || fold ? 0 : m.num_layers); ++l) {
         LayerWeights& L = e->layers[l];
         B200_TRY(add_norm(L.input_norm));
-        B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
-                                   B200_EPILOGUE_NONE, e->status, s));
         __nv_bfloat16* k_cache = e->kv_cache + static_cast<int64_t>(l) * e->num_slots * e->hkv * d;
         __nv_bfloat16* v_cache = k_cache + static_cast<int64_t>(m.num_layers) * e->num_slots * e->hkv * d;
-        B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
+        if (heads_in_qkv) {
+            // (sharded and MoE engines, short prefill batches: the head epilogue alone, on normalised rows)
+            HeadEpilogue he;
+            he.q_norm_w = L.q_norm;
+            he.k_norm_w = L.k_norm;
+            he.cos_t = e->rope_cos;
+            he.sin_t = e->rope_sin;
+            he.positions = e->positions;
+            he.out_loc = e->out_loc;
+            he.k_cache = k_cache;
+            he.v_cache = v_cache;
+            he.q_heads = e->hq;
+            he.kv_heads = e->hkv;
+            he.max_pos = m.max_position;
+            he.num_slots = e->num_slots;
+            he.eps = m.rms_norm_eps;
+            SkinnyFusion with_heads;
+            with_heads.heads = &he;
+            B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden, B200_EPILOGUE_NONE,
+                                   e->status, s, &with_heads));
+        } else {
+            B200_TRY(launch_linear(e->qkv, e->x, L.qkv, L.qkv_bias, T, e->qkv_dim, hidden, hidden,
+                                   B200_EPILOGUE_NONE, e->status, s));
+            B200_TRY(launch_qknorm_rope_store(e->qkv, L.q_norm, L.k_norm, e->rope_cos, e->rope_sin,
                                               e->positions, e->out_loc, k_cache, v_cache, T, e->hq, e->hkv,
                                               d, m.max_position, e->num_slots, m.rms_norm_eps, 0, e->status, s));
+        }
         const bool timed = e->profile_attention && !e->capturing;
         if (timed) {
             while (static_cast<int>(e->prof_events.size()) < 2 * m.num_layers) {
@@ -828,7 +856,7 @@ int b200_engine_create(const b200_model_config* model, const b200_engine_config*
     }
     if (const char* v = getenv("B200_FOLD_NORM")) e->use_fold = atoi(v) != 0;
     if (const char* v = getenv("B200_FOLD_HEADS")) e->use_fold_heads = atoi(v) != 0;
-    if (e->use_fold && c.tp_size == 1 && m.num_experts == 0) {
+    if (e->use_fold && c.tp_size == 1 && m.num_experts == 0 && fold_shapes_ok(e)) {
         for (LayerWeights& L : e->layers) {
             void* p = nullptr;
             E_TRY(dev_alloc(e, &p, static_cast<int64_t>(e->qkv_dim) * H * 2, false));
