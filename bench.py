@@ -290,7 +290,8 @@ def run_gpu(args):
     # ---- phase B: end to end, the host waits for every step's tokens ----
     # Driven the way the scheduler's decode loop drives the engine: per step the host arrays cross
     # the C ABI, the metadata goes host-to-device from pinned memory, the tokens, finish flags and
-    # status words land in the engine's pinned result ring and the host waits on that step's event.
+    # status words land in the engine's pinned result ring and the host waits on that step's event
+    # after it has launched the step behind it.
     # (DecodeSession keeps the per-step host bookkeeping in vector form.)
     from sglang_cpp_b200.host_batch import DecodeSession
     e2e_ms_all, step_ms = [], []
@@ -301,11 +302,20 @@ def run_gpu(args):
         barrier()
         session = DecodeSession(hb, reqs, ring=True)
         t0 = time.perf_counter()
+        pending = None
         for _ in range(K):
             ts = time.perf_counter()
-            toks, finished = session.wait(session.step())   # this step's event only; tokens and flags in pinned memory
-            _ = int(toks[0]) + int(finished[0])
+            # the order of the reference's default decode loop (Scheduler::step_overlap,
+            # src/scheduler/scheduler.cc:636-675): launch the next forward, then process the previous
+            # step's output (its event only; tokens and finish flags are in pinned memory)
+            ticket = session.step()
+            if pending is not None:
+                toks, finished = session.wait(pending)
+                _ = int(toks[0]) + int(finished[0])
+            pending = ticket
             step_ms.append((time.perf_counter() - ts) * 1e3)
+        toks, finished = session.wait(pending)   # the last step's output, still inside the timed region
+        _ = int(toks[0]) + int(finished[0])
         barrier()
         ms = (time.perf_counter() - t0) * 1e3
         session.sync_back()
