@@ -232,7 +232,13 @@ def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq, f
         g = torch.Generator().manual_seed(5)
         for l in range(cfg.num_layers):
             for name in ("input_norm", "post_norm"):
-                pr.engine.load(name, l, (0.5 + torch.rand(cfg.hidden_size, generator=g)).to(torch.bfloat16))
+                w = (0.5 + torch.rand(cfg.hidden_size, generator=g)).to(torch.bfloat16)
+                if l % 2 == 0:
+                    pr.engine.load(name, l, w)
+                else:   # written on the device through the tensor's pointer, as Engine.fill_random does
+                    pr.engine.synchronize()
+                    pr.engine.device_view(name, l).view(torch.bfloat16).copy_(w.cuda())
+                    torch.cuda.synchronize()
         pr.hb.allocate(reqs)
         out = pr.hb.decode(reqs)
         out.synchronize()
