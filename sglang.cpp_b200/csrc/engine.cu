@@ -405,8 +405,10 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     };
     const int epi = m.hidden_act == 1 ? B200_EPILOGUE_GEGLU : B200_EPILOGUE_SWIGLU;
     // The head epilogue of the qkv projection wants the split-K form of the small-batch kernel; beyond
-    // two exchange rounds (128 tokens) the separate kernel is the faster of the two.
-    const bool heads_in_qkv = e->use_fold_heads && d == 128 && T <= 128 &&
+    // two exchange rounds (128 tokens) the separate kernel is the faster of the two, and on a sharded
+    // engine (few heads per rank) it is no gain: Llama-3-8B at batch 128 ran 7.21 against 7.44 ms with it
+    // on one GPU, 5.52 against 5.51 on two, 3.33 against 3.31 on eight.
+    const bool heads_in_qkv = e->use_fold_heads && d == 128 && T <= 128 && !tp &&
                               skinny_gemm_split(T, e->qkv_dim, hidden, B200_EPILOGUE_NONE) > 1;
 
     // Decode batches of at most 64 tokens of a dense, unsharded model: everything between two attention
