@@ -642,6 +642,15 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
     }
     B200_TRY(launch_linear(e->logits, head_in, e->lm_head, nullptr, Bp, m.vocab_size, hidden, hidden,
                            B200_EPILOGUE_NONE, e->status, s));
+    // Token write-back, token_pool[table_idx[i], write_pos[i]] = next_tokens[i], by the kernel that picks the token.
+    TokenWriteBack wb;
+    wb.pool = e->token_pool;
+    wb.rows = e->pt_rows;
+    wb.stride = e->pt_cols;
+    wb.cols = e->pt_cols;
+    wb.table_idx = meta_table_idx;
+    wb.write_pos = e->meta_dev + 3 * Bp + 1;
+    wb.count = B;
     if (sampling) {
         // meta layout after write_pos[Bp]: temperatures | top_k | top_p | seeds (2 ints each)
         const int32_t* sp = e->meta_dev + 4 * Bp + 1;
@@ -650,18 +659,9 @@ int enqueue_forward(b200_engine* e, int phase, int B, int Bp, int T, int max_ext
                                reinterpret_cast<const float*>(sp + 2 * Bp),
                                reinterpret_cast<const uint64_t*>(e->meta_dev + e->seed_offset(Bp)), step_index,
                                nullptr, s,
-                               reinterpret_cast<const uint64_t*>(e->meta_dev + e->step_index_offset(Bp))));
+                               reinterpret_cast<const uint64_t*>(e->meta_dev + e->step_index_offset(Bp)), &wb));
     } else {
-        B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s));
-    }
-    // Token write-back: token_pool[table_idx[i], write_pos[i]] = next_tokens[i].
-    if (B > 0) {
-        const int32_t* write_pos = e->meta_dev + 3 * Bp + 1;
-        B200_CHECK_CUDA(launch_kernel(scatter_int32_kernel, dim3(div_ceil(B, 256)), dim3(256), 0, s,
-                                      dim3(1, 1, 1), e->token_pool, static_cast<int64_t>(e->pt_rows),
-                                      static_cast<int64_t>(e->pt_cols), static_cast<int64_t>(e->pt_cols),
-                                      meta_table_idx, write_pos, static_cast<const int32_t*>(e->next_tokens),
-                                      static_cast<int64_t>(B)));
+        B200_TRY(launch_argmax(e->next_tokens, e->logits, B, m.vocab_size, m.vocab_size, s, &wb));
     }
     e->launches_last_step = static_cast<int>(kernel_launch_count() - launches_before);
     return B200_OK;

@@ -28,14 +28,24 @@ int launch_embedding(void* out, const void* table, const int32_t* ids, int token
                      int ssq_slots = 0, int ssq_stride = 0);
 // out[n, k] = bf16(w[n, k] * scale[k]): a norm weight folded into the columns of the matrix that follows it.
 int launch_scale_columns(void* out, const void* w, const void* scale, int64_t rows, int K, cudaStream_t stream);
+// Optional write-back of the chosen tokens into the token pool by the kernel that chooses them
+// (token_pool[table_idx[i], write_pos[i]] = token[i] for i < count, positions outside the table
+// skipped): what a separate scatter launch would do behind it.
+struct TokenWriteBack {
+    int32_t* pool = nullptr;
+    int64_t rows = 0, stride = 0, cols = 0;
+    const int32_t* table_idx = nullptr;
+    const int32_t* write_pos = nullptr;
+    int count = 0;
+};
 // step_index_dev (optional): the step index is read from device memory instead of the argument, so a
 // captured graph replays with a new value.
 int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   const float* temperatures, const int32_t* top_k, const float* top_p,
                   const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream,
-                  const uint64_t* step_index_dev = nullptr);
+                  const uint64_t* step_index_dev = nullptr, const TokenWriteBack* write_back = nullptr);
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
-                  cudaStream_t stream);
+                  cudaStream_t stream, const TokenWriteBack* write_back = nullptr);
 
 // Tensor map of a 2-D bf16 tensor [outer, inner] copied in [box_outer, box_inner] boxes with the
 // 128-byte swizzle, from a small per-thread cache (the same buffers come back every layer).

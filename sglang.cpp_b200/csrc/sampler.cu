@@ -22,9 +22,17 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 // first index on ties, so the result does not depend on how the row is cut.
 constexpr int kArgmaxCluster = 8;
 
+__device__ __forceinline__ void emit_token(int32_t* out, const TokenWriteBack& wb, int row, int tok) {
+    out[row] = tok;
+    if (wb.pool != nullptr && row < wb.count) {
+        const int64_t r = wb.table_idx[row], p = wb.write_pos[row];
+        if (r >= 0 && r < wb.rows && p >= 0 && p < wb.cols) wb.pool[r * wb.stride + p] = tok;
+    }
+}
+
 __global__ void __launch_bounds__(512)
 argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logits, int vocab,
-                   int64_t ld, int ncta) {
+                   int64_t ld, int ncta, const TokenWriteBack wb) {
     __shared__ float s_v[16];
     __shared__ int s_i[16];
     __shared__ float s_cv[kArgmaxCluster];
@@ -70,7 +78,7 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
             best = better(best, other);
         }
         if (ncta == 1) {
-            if (lane == 0) out[row_id] = best.i == 0x7fffffff ? 0 : best.i;
+            if (lane == 0) emit_token(out, wb, row_id, best.i == 0x7fffffff ? 0 : best.i);
         } else if (lane == 0) {
             // hand this slice's winner to the first CTA of the cluster
             uint32_t rv_addr, ri_addr;
@@ -86,7 +94,7 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
         if (rank == 0 && threadIdx.x == 0) {
             MaxIdx b0{-INFINITY, 0x7fffffff};
             for (int r = 0; r < ncta; ++r) b0 = better(b0, MaxIdx{s_cv[r], s_ci[r]});
-            out[row_id] = b0.i == 0x7fffffff ? 0 : b0.i;
+            emit_token(out, wb, row_id, b0.i == 0x7fffffff ? 0 : b0.i);
         }
     }
 }
@@ -94,11 +102,12 @@ argmax_bf16_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ 
 }  // namespace
 
 int launch_argmax(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const TokenWriteBack* write_back) {
     if (rows == 0) return B200_OK;
     const int ncta = vocab >= 32768 ? kArgmaxCluster : 1;
     B200_CHECK_CUDA(launch_kernel(argmax_bf16_kernel, dim3(rows * ncta), dim3(512), 0, stream, dim3(ncta, 1, 1),
-                                  out, static_cast<const __nv_bfloat16*>(logits), vocab, ld, ncta));
+                                  out, static_cast<const __nv_bfloat16*>(logits), vocab, ld, ncta,
+                                  write_back ? *write_back : TokenWriteBack{}));
     return B200_OK;
 }
 
@@ -216,7 +225,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
               int64_t ld, const float* __restrict__ temps, const int32_t* __restrict__ top_k,
               const float* __restrict__ top_p, const uint64_t* __restrict__ seeds,
               const uint64_t* __restrict__ step_index_ptr, uint64_t step_index_arg,
-              uint8_t* __restrict__ mask) {
+              uint8_t* __restrict__ mask, const TokenWriteBack wb) {
     extern __shared__ __align__(16) uint32_t s_hist[];   // kHistWords counters; bin b lives at b + b / 32
     __shared__ SampleMeet meet;
     __shared__ u64 s_wm[kSampleWarps];
@@ -317,7 +326,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
             }
         }
         if (idx == 0x7fffffff) idx = 0;
-        if (tid == 0) out[row] = idx;
+        if (tid == 0) emit_token(out, wb, row, idx);
         if (mrow)
             for (int i = tid; i < vocab; i += kSampleThreads) mrow[i] = i == idx ? 1 : 0;
         return;
@@ -524,7 +533,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
                                  make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32)));
     const double u01 = static_cast<double>(rnd.x >> 8) * (1.0 / 16777216.0);  // [0, 1)
     const u64 target = static_cast<u64>(u01 * static_cast<double>(Zf));       // < Zf: u01 <= 1 - 2^-24
-    if (Zf == 0ull && rank == 0 && tid == 0) out[row] = 0;                    // a row of NaNs: nothing to draw from
+    if (Zf == 0ull && rank == 0 && tid == 0) emit_token(out, wb, row, 0);                    // a row of NaNs: nothing to draw from
     if (my_kept > 0 && target >= lo && target < lo + my_kept) {
         // this thread's run holds the target: walk it
         u64 c = lo;
@@ -543,7 +552,7 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
                 }
             }
         }
-        if (pick >= 0) out[row] = pick;
+        if (pick >= 0) emit_token(out, wb, row, pick);
     }
     if (mrow) {   // candidate mask (tests): membership of every key of the run
         int er = eq_rank;
@@ -561,14 +570,15 @@ sample_kernel(int32_t* __restrict__ out, const __nv_bfloat16* __restrict__ logit
 int launch_sample(int32_t* out, const void* logits, int rows, int vocab, int64_t ld,
                   const float* temperatures, const int32_t* top_k, const float* top_p,
                   const uint64_t* seeds, uint64_t step_index, uint8_t* mask, cudaStream_t stream,
-                  const uint64_t* step_index_dev) {
+                  const uint64_t* step_index_dev, const TokenWriteBack* write_back) {
     if (rows == 0) return B200_OK;
     const size_t smem = kHistWords * sizeof(uint32_t);
     B200_CHECK_CUDA(cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)));
     B200_CHECK_CUDA(launch_kernel(sample_kernel, dim3(rows * kSampleCluster), dim3(kSampleThreads), smem, stream,
                                   dim3(kSampleCluster, 1, 1), out, static_cast<const __nv_bfloat16*>(logits), vocab,
-                                  ld, temperatures, top_k, top_p, seeds, step_index_dev, step_index, mask));
+                                  ld, temperatures, top_k, top_p, seeds, step_index_dev, step_index, mask,
+                                  write_back ? *write_back : TokenWriteBack{}));
     return B200_OK;
 }
 

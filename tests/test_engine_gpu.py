@@ -175,8 +175,8 @@ def test_decode_layer_chain_against_oracle_and_against_the_kernel_per_operator_p
         assert pr.engine_status_clean()
         pr.engine.close()
     assert outs["1"][1] < outs["0"][1], "the chain path must launch fewer kernels"
-    # prepare, embedding, layer 0's norm / qkv / rope, (attention + merge + chain) per layer, final norm, lm_head, argmax, write-back
-    assert outs["1"][1] == 9 + 3 * cfg.num_layers, outs["1"][1]
+    # prepare, embedding, layer 0's norm / qkv / rope, (attention + merge + chain) per layer, final norm, lm_head, argmax (which writes the token back)
+    assert outs["1"][1] == 8 + 3 * cfg.num_layers, outs["1"][1]
     d = (outs["1"][0].float() - outs["0"][0].float()).abs()
     assert float(d.max()) <= MAX_ABS and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
 
@@ -247,10 +247,10 @@ def test_decode_with_norms_folded_into_the_gemms(pkg, monkeypatch, kind, nreq, f
         outs[fold] = (torch.stack(steps), launches)
         assert pr.engine_status_clean()
         pr.engine.close()
-    # prepare, embedding, (qkv [+ rope], attention, merge, o, gate_up, down) per layer, final norm, lm_head, argmax, write-back
+    # prepare, embedding, (qkv [+ rope], attention, merge, o, gate_up, down) per layer, final norm, lm_head, argmax (which also writes the token back)
     heads = fold_heads == "1" and nreq <= 128     # the head epilogue serves steps of at most 128 tokens
-    assert outs["1"][1] == 6 + (6 if heads else 7) * cfg.num_layers, outs["1"][1]
-    assert outs["0"][1] == 6 + (8 if heads else 9) * cfg.num_layers, outs["0"][1]
+    assert outs["1"][1] == 5 + (6 if heads else 7) * cfg.num_layers, outs["1"][1]
+    assert outs["0"][1] == 5 + (8 if heads else 9) * cfg.num_layers, outs["0"][1]
     d = (outs["1"][0].float() - outs["0"][0].float()).abs()
     rms = float(outs["0"][0].float().pow(2).mean().sqrt())
     assert float(d.max()) <= MAX_ABS and float(d.mean()) <= MEAN_ABS + rms * 2 ** -8, (float(d.max()), float(d.mean()))
